@@ -1,0 +1,15 @@
+"""batchlas_b200 — B200 (sm_100a) batched GEMM behind BatchLAS's gemm call.
+
+The product is `libbatchlas_b200.so` (hand-written CUDA kernels + a C ABI, see include/blb200.h);
+this package is its Python host side: a ctypes binding (`_lib`), a torch-tensor convenience layer
+over device memory (`gemm`), and the batch-sharding helper used for multi-GPU runs (`sharding`).
+"""
+from . import _lib
+from ._lib import BlasError, GemmDesc, KERNEL_IDS
+from .gemm import (DTYPE_CODES, Transpose, device_status, fill, gemm, gemm_host, gemm_strided_batched,
+                   last_kernel_name, launch_count, make_desc)
+from .sharding import shard_range
+
+__all__ = ["_lib", "BlasError", "GemmDesc", "KERNEL_IDS", "DTYPE_CODES", "Transpose", "device_status",
+           "fill", "gemm", "gemm_host", "gemm_strided_batched", "last_kernel_name", "launch_count",
+           "make_desc", "shard_range"]

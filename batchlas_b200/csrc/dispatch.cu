@@ -1,0 +1,137 @@
+// C-ABI entry points of libbatchlas_b200.so: validation, shape/dtype dispatch, diagnostics.
+// The device-pointer launcher allocates nothing and never synchronises.
+#include <mutex>
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace blb200 {
+
+static thread_local const char* t_last_kernel = "";
+static thread_local uint64_t t_launches = 0;
+
+void note_launch(const char* kernel_name) {
+  t_last_kernel = kernel_name;
+  ++t_launches;
+}
+
+const DeviceInfo& device_info() {
+  static DeviceInfo infos[64];
+  static std::once_flag flags[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  std::call_once(flags[dev], [dev] {
+    DeviceInfo& d = infos[dev];
+    int v = 0;
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    d.sm_count = v > 0 ? v : 148;
+    cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+    cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    d.smem_optin = (size_t)v;
+  });
+  return infos[dev];
+}
+
+static int validate(const blb200_gemm_desc* d) {
+  if (!d) return BLB200_E_NULL;
+  if (d->dtype < BLB200_S || d->dtype > BLB200_Z) return BLB200_E_DTYPE;
+  if (d->op_a < BLB200_N || d->op_a > BLB200_H || d->op_b < BLB200_N || d->op_b > BLB200_H)
+    return BLB200_E_DTYPE;
+  if (d->m < 0 || d->n < 0 || d->k < 0 || d->batch < 0) return BLB200_E_SHAPE;
+  const int64_t a_rows = d->op_a == BLB200_N ? d->m : d->k;
+  const int64_t b_rows = d->op_b == BLB200_N ? d->k : d->n;
+  if (d->lda < (a_rows > 1 ? a_rows : 1)) return BLB200_E_SHAPE;
+  if (d->ldb < (b_rows > 1 ? b_rows : 1)) return BLB200_E_SHAPE;
+  if (d->ldc < (d->m > 1 ? d->m : 1)) return BLB200_E_SHAPE;
+  if (d->stride_a < 0 || d->stride_b < 0 || d->stride_c < 0) return BLB200_E_SHAPE;
+  if (d->kernel_hint < BLB200_K_AUTO || d->kernel_hint > BLB200_K_TILED_TMA) return BLB200_E_UNSUPPORTED;
+  const bool has_work = d->m > 0 && d->n > 0 && d->batch > 0;
+  if (has_work) {
+    if (!d->c) return BLB200_E_NULL;
+    if (d->k > 0 && (!d->a || !d->b)) return BLB200_E_NULL;
+  }
+  return BLB200_OK;
+}
+
+static GemmParams to_params(const blb200_gemm_desc* d) {
+  GemmParams p;
+  p.a = d->a;
+  p.b = d->b;
+  p.c = d->c;
+  p.m = d->m;
+  p.n = d->n;
+  p.k = d->k;
+  p.batch = d->batch;
+  p.lda = d->lda;
+  p.ldb = d->ldb;
+  p.ldc = d->ldc;
+  p.sa = d->stride_a;
+  p.sb = d->stride_b;
+  p.sc = d->stride_c;
+  const bool cplx = d->dtype >= BLB200_C;
+  p.alpha[0] = d->alpha[0];
+  p.alpha[1] = cplx ? d->alpha[1] : 0.0;
+  p.beta[0] = d->beta[0];
+  p.beta[1] = cplx ? d->beta[1] : 0.0;
+  p.op_a = d->op_a;
+  p.op_b = d->op_b;
+  if (!cplx) {  // conjugation is the identity on real data
+    if (p.op_a == BLB200_H) p.op_a = BLB200_T;
+    if (p.op_b == BLB200_H) p.op_b = BLB200_T;
+  }
+  return p;
+}
+
+int dispatch(const blb200_gemm_desc* d, cudaStream_t stream) {
+  int rc = validate(d);
+  if (rc != BLB200_OK) return rc;
+  if (d->m == 0 || d->n == 0 || d->batch == 0) return BLB200_OK;
+  const GemmParams p = to_params(d);
+  switch (d->kernel_hint) {
+    case BLB200_K_GENERIC: return launch_generic(p, d->dtype, stream);
+    case BLB200_K_SMALL32: return launch_small32(p, d->dtype, stream);
+    case BLB200_K_SMALL64: return launch_small64(p, d->dtype, stream);
+    case BLB200_K_TILED:
+    case BLB200_K_TILED_TMA: return launch_tiled(p, d->dtype, stream);
+    default: break;
+  }
+  if (small32_supported(p, d->dtype)) return launch_small32(p, d->dtype, stream);
+  if (small64_supported(p, d->dtype)) return launch_small64(p, d->dtype, stream);
+  if (tiled_supported(p, d->dtype)) return launch_tiled(p, d->dtype, stream);
+  return launch_generic(p, d->dtype, stream);
+}
+
+}  // namespace blb200
+
+extern "C" {
+
+int blb200_gemm_validate(const blb200_gemm_desc* desc) { return blb200::validate(desc); }
+
+int blb200_gemm_strided_batched(const blb200_gemm_desc* desc, void* cuda_stream) {
+  return blb200::dispatch(desc, (cudaStream_t)cuda_stream);
+}
+
+const char* blb200_last_kernel_name(void) { return blb200::t_last_kernel; }
+uint64_t blb200_launch_count(void) { return blb200::t_launches; }
+const char* blb200_version(void) { return "0.1"; }
+
+const char* blb200_status_string(int status) {
+  switch (status) {
+    case BLB200_OK: return "ok";
+    case BLB200_E_NULL: return "null pointer";
+    case BLB200_E_SHAPE: return "GEMM: incompatible matrix dimensions";
+    case BLB200_E_DTYPE: return "dtype or transpose out of range";
+    case BLB200_E_UNSUPPORTED: return "requested kernel does not support this problem";
+    case BLB200_E_NO_DEVICE: return "no usable CUDA device";
+    case BLB200_E_TOO_LARGE: return "problem exceeds the fixed capacity of this entry point";
+    case BLB200_E_INTERNAL: return "internal error";
+    default: break;
+  }
+  if (status > 0) return cudaGetErrorString((cudaError_t)status);
+  return "unknown status";
+}
+
+}  // extern "C"

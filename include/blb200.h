@@ -1,0 +1,148 @@
+/*
+ * blb200.h — C ABI of the B200 (sm_100a) batched-GEMM library `libbatchlas_b200.so`.
+ *
+ * This is the seam a BatchLAS maintainer binds to replace
+ *     template Event batchlas::gemm<Backend::CUDA, T>(Queue&, const MatrixView<T>&,
+ *         const MatrixView<T>&, const MatrixView<T>&, T, T, Transpose, Transpose,
+ *         ComputePrecision)
+ * (BatchLAS src/backends/cublas.cc:1574-1585 -> gemm_vendor, :152-179 -> gemm_vendor_impl,
+ * :106-150, which ends in one cublasGemmStridedBatchedEx call).  The reference has no C ABI
+ * of its own for gemm; the closest precedent is its POD launch descriptor
+ * `GemmLaunchDescriptor` + `cudaError_t launch_float(variant, desc, cudaStream_t)`
+ * (BatchLAS src/backends/gemm_cublasdx_kernels.hh:21-48).  The descriptor below keeps that
+ * shape and widens it to four dtypes, three transposes and 64-bit strides.
+ *
+ * Plain pointers and sizes only: no C++ types, no torch types.
+ */
+#ifndef BLB200_API_H_INCLUDED
+#define BLB200_API_H_INCLUDED
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element type.  Complex values are interleaved (re, im) pairs, as std::complex<T>. */
+typedef enum { BLB200_S = 0, BLB200_D = 1, BLB200_C = 2, BLB200_Z = 3 } blb200_dtype;
+
+/* Operand transform.  Same ordinals as batchlas::Transpose {NoTrans, Trans, ConjTrans}
+ * (BatchLAS include/blas/enums.hh:78-82).  For real dtypes H behaves as T. */
+typedef enum { BLB200_N = 0, BLB200_T = 1, BLB200_H = 2 } blb200_op;
+
+/* Status codes.  0 = success, > 0 = a cudaError_t from the runtime, < 0 = one of these. */
+enum {
+  BLB200_OK = 0,
+  BLB200_E_NULL = -1,        /* null descriptor, or null A/B/C with work to do          */
+  BLB200_E_SHAPE = -2,       /* negative dim, ld smaller than the stored row count      */
+  BLB200_E_DTYPE = -3,       /* dtype / op out of range                                 */
+  BLB200_E_UNSUPPORTED = -4, /* forced kernel cannot run this problem                   */
+  BLB200_E_NO_DEVICE = -5,   /* no sm_100 device current                                */
+  BLB200_E_TOO_LARGE = -6,   /* problem exceeds a fixed capacity of the entry point     */
+  BLB200_E_INTERNAL = -7
+};
+
+/* Kernel ids for `kernel_hint` (0 = let the dispatcher choose). */
+enum {
+  BLB200_K_AUTO = 0,
+  BLB200_K_GENERIC = 1, /* any dtype/op/ld/alignment; predicated scalar loads              */
+  BLB200_K_SMALL32 = 2, /* whole 32x32x32 matrices per warp, bulk-copy pipeline (S and D)   */
+  BLB200_K_SMALL64 = 3, /* whole 64x64x64 float matrices per warp pair, bulk-copy pipeline  */
+  BLB200_K_TILED = 4,   /* register-blocked smem tiles fed by 16-byte async copies          */
+  BLB200_K_TILED_TMA = 5 /* register-blocked smem tiles fed by tensor-map TMA               */
+};
+
+/*
+ * One strided-batched GEMM:  C_b <- alpha * op_a(A_b) * op_b(B_b) + beta * C_b,  b in [0,batch).
+ * All matrices are column-major; element (i,j) of item b is at  base[b*stride + j*ld + i].
+ * m,n,k are the op-effective dims: op_a(A) is m x k, op_b(B) is k x n, C is m x n.
+ * Stored shapes: A is (op_a==N ? m x k : k x m), B is (op_b==N ? k x n : n x k).
+ *
+ * Semantics follow BLAS, as the reference's host path does (BatchLAS
+ * src/backends/netlib_lapack.cc:141-168): m==0||n==0 is a no-op; k==0 scales C by beta;
+ * beta==0 never reads C (C may hold NaN/garbage); padding rows (>= m within ldc) and the
+ * gap between ldc*n and stride_c are never written.
+ */
+typedef struct blb200_gemm_desc {
+  const void* a;
+  const void* b;
+  void* c;
+  int32_t m, n, k, batch;
+  int64_t lda, ldb, ldc;                /* elements */
+  int64_t stride_a, stride_b, stride_c; /* elements between consecutive batch items */
+  double alpha[2], beta[2];             /* re, im; im ignored for real dtypes; rounded to T */
+  int32_t dtype, op_a, op_b;            /* blb200_dtype, blb200_op, blb200_op */
+  int32_t kernel_hint;                  /* BLB200_K_* ; 0 = auto */
+} blb200_gemm_desc;
+
+/* Validate the descriptor (shape rules of BatchLAS src/backends/gemm_variant.hh:19-44 in their
+ * strided form: non-negative dims, ld >= stored rows).  Touches no device. */
+int blb200_gemm_validate(const blb200_gemm_desc* desc);
+
+/* Launch on `cuda_stream` (a cudaStream_t; NULL = the legacy default stream) of the current
+ * device, with a/b/c DEVICE pointers.  Asynchronous; allocates nothing.  Replaces
+ * gemm_vendor_impl's cublasGemmStridedBatchedEx (BatchLAS src/backends/cublas.cc:126-147). */
+int blb200_gemm_strided_batched(const blb200_gemm_desc* desc, void* cuda_stream);
+
+/* Same operation with a/b/c HOST pointers (pinned for full speed; pageable works, slower).
+ * The batch is cut into chunks; chunk i+1's host->device copies and chunk i-1's device->host
+ * copy overlap chunk i's kernel on three streams of `device`.  Device staging comes from the
+ * device's stream-ordered memory pool and is returned to it before the call returns.
+ * Synchronous: C is complete in host memory on return.  This is the path that stands in for
+ * the reference's host-visible (USM shared) Matrix storage (BatchLAS src/matrix.cc:150-166),
+ * where operands live on the host side and move to the GPU on use.
+ * `chunk_items` = batch items per chunk, 0 = choose automatically. */
+int blb200_gemm_strided_batched_host(const blb200_gemm_desc* desc, int device, int32_t chunk_items);
+
+/* Name of the kernel the calling thread's most recent launch used ("" before any). */
+const char* blb200_last_kernel_name(void);
+/* Number of kernels this library has launched from the calling thread so far. */
+uint64_t blb200_launch_count(void);
+/* Text for a status code (library codes and cudaError_t values). */
+const char* blb200_status_string(int status);
+/* Library version, "major.minor". */
+const char* blb200_version(void);
+/* Synchronises the current device and reports whether any kernel of this library ever gave up
+ * on one of its bounded waits: *out = 0 when none did, else a small code naming the wait. */
+int blb200_device_status(int* out);
+
+/* ---- per-queue workspace arena -------------------------------------------------------
+ * Bump/LIFO arena with the lease semantics of BatchLAS's WorkspaceArena (src/queue.hh:41-226,
+ * include/util/workspace.hh:70-162), re-backed by cudaMallocAsync on the queue's stream:
+ * blocks grow geometrically (max(request, 2*last, 64 KiB)), an innermost release rewinds the
+ * cursor, an out-of-order release is only marked and reclaimed once it becomes innermost,
+ * trim refuses while anything is leased.  One arena belongs to one stream and, like the
+ * reference's Queue, is not thread-safe. */
+typedef struct blb200_arena blb200_arena;
+typedef struct blb200_lease {
+  void* ptr;
+  size_t bytes;
+  size_t block, offset;
+  uint64_t seq; /* 0 = empty lease */
+} blb200_lease;
+
+/* `device` < 0 builds a host-memory arena (malloc-backed) with identical bookkeeping: it exists
+ * so the lease logic can be exercised where no GPU is present. */
+int blb200_arena_create(int device, void* cuda_stream, blb200_arena** out);
+int blb200_arena_destroy(blb200_arena* arena);
+int blb200_arena_acquire(blb200_arena* arena, size_t bytes, blb200_lease* out);
+int blb200_arena_release(blb200_arena* arena, const blb200_lease* lease);
+/* 1 = memory returned to the pool, 0 = refused because a lease is outstanding, <0 error. */
+int blb200_arena_trim(blb200_arena* arena);
+size_t blb200_arena_capacity(const blb200_arena* arena);
+size_t blb200_arena_block_count(const blb200_arena* arena);
+size_t blb200_arena_alignment(const blb200_arena* arena);
+
+/* ---- synthetic inputs ------------------------------------------------------------------
+ * Counter-based generator: element `i` of tensor `tensor_id` under `seed` depends only on
+ * (seed, tensor_id, first_index + i), so any shard on any GPU count reproduces the same data.
+ * dist 0: uniform[-1,1]; dist 1: normal(0,1)*scale.  Complex dtypes fill re and im
+ * independently (count = number of complex elements).  Device pointer, asynchronous. */
+int blb200_fill(void* dst, int32_t dtype, uint64_t count, uint64_t first_index, uint64_t seed,
+                uint32_t tensor_id, int32_t dist, double scale, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BLB200_API_H_INCLUDED */

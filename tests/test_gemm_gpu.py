@@ -1,0 +1,225 @@
+"""Parity tests proper: the CUDA path, called through the C ABI, against the CPU oracle on the
+same seeded inputs.  Acceptance rule (written here because it is the contract):
+
+    |C_gpu - (alpha*S + beta*C0)| <= 4 * K * eps_T * (|alpha| * (|A|*|B|) + |beta| * |C0|)   entrywise
+
+with S and the bound accumulated in long double by the oracle, eps_T = 2^-23 (float, complex<float>)
+or 2^-52 (double, complex<double>).  Everything outside the m x n windows of C must come back
+bit-identical (padding rows within ldc, stride gaps)."""
+import ctypes
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+from oracle import oracle  # noqa: E402
+from tests._cases import DTYPE_NAMES, EDGE_SHAPES, REFERENCE_SHAPES, make_inputs, scalar_for  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+TORCH_DT = {0: torch.float32, 1: torch.float64, 2: torch.complex64, 3: torch.complex128}
+
+
+@pytest.fixture(scope="module")
+def bl(lib):
+    if not torch.cuda.is_available():
+        pytest.fail("marked gpu but no CUDA device is visible")
+    import batchlas_b200
+    return batchlas_b200
+
+
+def run_device(bl, p, A, B, C0, kernel="auto", offset_elems=0):
+    """Upload, launch through the C ABI, download.  offset_elems shifts every base pointer to
+    exercise unaligned views (slices)."""
+    def up(x):
+        buf = torch.empty(x.size + offset_elems, dtype=TORCH_DT[p.dtype], device="cuda")
+        buf[offset_elems:] = torch.from_numpy(x).cuda()
+        return buf
+    dA, dB, dC = up(A), up(B), up(C0)
+    es = dA.element_size()
+    desc = bl.make_desc(dA.data_ptr() + offset_elems * es, dB.data_ptr() + offset_elems * es,
+                        dC.data_ptr() + offset_elems * es, p.dtype, p.op_a, p.op_b, p.m, p.n, p.k, p.batch,
+                        p.lda, p.ldb, p.ldc, p.stride_a, p.stride_b, p.stride_c, p.alpha, p.beta, kernel)
+    bl.gemm_strided_batched(desc)
+    torch.cuda.synchronize()
+    return dC[offset_elems:].cpu().numpy(), bl.last_kernel_name()
+
+
+def assert_parity(p, A, B, C0, C, items=None, what=""):
+    bad, worst = oracle.check(p, A, B, C0, C, items)
+    assert bad == 0, f"{what}: {bad} entries beyond the bound, worst ratio {worst:.3g}"
+    assert oracle.untouched_outside_window(p, C0, C), f"{what}: wrote outside the m x n windows"
+
+
+@pytest.mark.parametrize("dt", DTYPE_NAMES)
+@pytest.mark.parametrize("case", REFERENCE_SHAPES + EDGE_SHAPES, ids=lambda c: "x".join(map(str, c[:4])) + c[4] + c[5])
+def test_reference_test_shapes_padded(bl, dt, case):
+    m, n, k, batch, oa, ob, alpha, beta = case
+    code = oracle.DTYPES[dt]
+    ar = m if oa == "N" else k
+    br = k if ob == "N" else n
+    p = oracle.make_problem(dt, oa, ob, m, n, k, batch, lda=ar + 3, ldb=br + 1, ldc=m + 5,
+                            alpha=scalar_for(code, alpha), beta=scalar_for(code, beta))
+    p.stride_c += 11
+    A, B, C0 = make_inputs(p)
+    C, kern = run_device(bl, p, A, B, C0)
+    assert_parity(p, A, B, C0, C, what=f"{dt} {case} via {kern}")
+
+
+@pytest.mark.parametrize("dt", DTYPE_NAMES)
+@pytest.mark.parametrize("oa", ["N", "T", "C"])
+@pytest.mark.parametrize("ob", ["N", "T", "C"])
+def test_all_nine_op_pairs_packed_and_generic_agree(bl, dt, oa, ob):
+    code = oracle.DTYPES[dt]
+    for (m, n, k, batch) in [(32, 32, 32, 5), (64, 64, 64, 3), (48, 40, 24, 2), (128, 64, 96, 2)]:
+        p = oracle.make_problem(dt, oa, ob, m, n, k, batch, alpha=scalar_for(code, 1.5), beta=scalar_for(code, -0.5))
+        A, B, C0 = make_inputs(p)
+        C, kern = run_device(bl, p, A, B, C0)
+        assert_parity(p, A, B, C0, C, what=f"{dt} {oa}{ob} {m}x{n}x{k} via {kern}")
+        Cg, kg = run_device(bl, p, A, B, C0, kernel="generic")
+        assert kg == "generic"
+        assert_parity(p, A, B, C0, Cg, what=f"{dt} {oa}{ob} {m}x{n}x{k} via generic")
+
+
+@pytest.mark.parametrize("dt", DTYPE_NAMES)
+def test_beta_zero_never_reads_c(bl, dt):
+    # linalg::matmul hands in uninitialised C on that promise (BatchLAS include/blas/linalg-ops.hh:168-184).
+    for (m, n, k, batch) in [(32, 32, 32, 9), (64, 64, 64, 3), (50, 30, 20, 2), (256, 128, 64, 1)]:
+        p = oracle.make_problem(dt, "N", "T", m, n, k, batch, alpha=2.0, beta=0.0)
+        A, B, C0 = make_inputs(p)
+        Cnan = C0.copy()
+        Cnan[:] = np.nan
+        C, kern = run_device(bl, p, A, B, Cnan)
+        assert not np.isnan(C[: p.alloc_len("c")]).any(), kern
+        bad, worst = oracle.check(p, A, B, C0, C)
+        assert bad == 0, (kern, worst)
+
+
+@pytest.mark.parametrize("dt", DTYPE_NAMES)
+def test_identity_product_is_exact(bl, dt):
+    # BatchLAS tests/gemm_tests.cc:355-396
+    for batch in (1, 3):
+        p = oracle.make_problem(dt, "N", "N", 10, 10, 10, batch)
+        A, B, C0 = make_inputs(p, tail=0)
+        B[:] = np.tile(np.eye(10, dtype=A.dtype).ravel(), batch)
+        C, _ = run_device(bl, p, A, B, C0)
+        assert np.array_equal(C, A)
+
+
+@pytest.mark.parametrize("dt", ["s", "z"])
+def test_unaligned_views_take_a_safe_path(bl, dt):
+    # Views can be slices (BatchLAS include/blas/matrix.hh:855-869): base pointers need not be 16-byte
+    # aligned and ld need not be a multiple of the vector width; fast paths must decline them.
+    for (m, n, k, batch, ld_extra) in [(32, 32, 32, 4, 0), (64, 64, 64, 2, 1), (130, 66, 40, 2, 1)]:
+        ar = m
+        p = oracle.make_problem(dt, "N", "N", m, n, k, batch, lda=ar + ld_extra, ldb=k + ld_extra,
+                                ldc=m + ld_extra, alpha=1.0, beta=1.0)
+        A, B, C0 = make_inputs(p)
+        C, kern = run_device(bl, p, A, B, C0, offset_elems=1)
+        assert_parity(p, A, B, C0, C, what=f"offset view via {kern}")
+
+
+def test_forced_kernel_that_cannot_run_reports_unsupported(bl):
+    p = oracle.make_problem("d", "N", "N", 20, 20, 20, 1)
+    A, B, C0 = make_inputs(p)
+    with pytest.raises(bl.BlasError) as e:
+        run_device(bl, p, A, B, C0, kernel="small32")
+    assert e.value.status == bl._lib.E_UNSUPPORTED
+
+
+def test_tensor_front_end_and_shape_errors(bl):
+    # Argument meaning of batchlas::gemm(ctx, A, B, C, {.alpha,.beta,.transA,.transB}).
+    from batchlas_b200.gemm import col_major_view
+    p = oracle.make_problem("d", "T", "N", 24, 20, 16, 3, alpha=2.0, beta=0.5)
+    A, B, C0 = make_inputs(p, tail=0)
+    dA, dB, dC = (torch.from_numpy(x).cuda() for x in (A, B, C0))
+    vA = col_major_view(dA, 16, 24, batch=3)
+    vB = col_major_view(dB, 16, 20, batch=3)
+    vC = col_major_view(dC, 24, 20, batch=3)
+    bl.gemm(vA, vB, vC, alpha=2.0, beta=0.5, transA=bl.Transpose.Trans)
+    torch.cuda.synchronize()
+    assert_parity(p, A, B, C0, dC.cpu().numpy(), what="tensor front end")
+    with pytest.raises(bl.BlasError, match="GEMM: incompatible matrix dimensions"):
+        bl.gemm(vA, vB, vC)  # without transA the inner dimensions disagree
+    with pytest.raises(RuntimeError):
+        bl.gemm(vA.cpu(), vB.cpu(), vC.cpu())  # no CPU path
+
+
+def test_config_shapes_sampled(bl):
+    """The five benchmark configurations at reduced batch, every item checked."""
+    cfgs = [
+        ("s", "N", "N", 64, 64, 64, 37, 1.0, 0.0, {}, "uniform", "uniform", 1.0),
+        ("s", "N", "T", 32, 32, 32, 1000, 1.5, -0.5, {}, "uniform", "uniform", 1.0),
+        ("s", "T", "N", 32, 32, 32, 1000, 1.5, -0.5, {}, "uniform", "uniform", 1.0),
+        ("d", "N", "N", 256, 256, 256, 3, 2.0, 0.5, dict(lda=264, ldb=264, ldc=264), "normal", "uniform", 1.0),
+        ("d", "N", "T", 256, 256, 256, 2, 2.0, 0.5, dict(lda=264, ldb=264, ldc=264), "normal", "uniform", 1.0),
+        ("d", "T", "N", 256, 256, 256, 2, 2.0, 0.5, dict(lda=264, ldb=264, ldc=264), "normal", "uniform", 1.0),
+        ("d", "T", "T", 256, 256, 256, 2, 2.0, 0.5, dict(lda=264, ldb=264, ldc=264), "normal", "uniform", 1.0),
+        ("z", "C", "N", 128, 64, 256, 4, 1.0 + 0.5j, 0.0, {}, "normal", "uniform", 1.0),
+        ("d", "N", "N", 1024, 1024, 1024, 1, 1.0, 1.0, {}, "normal", "uniform", 1.0 / 32.0),
+    ]
+    for dt, oa, ob, m, n, k, batch, alpha, beta, lds, dab, dc, scale in cfgs:
+        p = oracle.make_problem(dt, oa, ob, m, n, k, batch, alpha=alpha, beta=beta, **lds)
+        A, B, C0 = make_inputs(p, dist_ab=dab, dist_c=dc, scale=scale)
+        C, kern = run_device(bl, p, A, B, C0)
+        items = None if m < 1024 else [0]
+        if m >= 1024:  # the long-double arbiter is O(mnk): check a 96-column slab of the big item
+            p_chk = oracle.make_problem(dt, oa, ob, m, 96, k, 1, lda=p.lda, ldb=p.ldb, ldc=p.ldc, alpha=alpha, beta=beta)
+            bad, worst = oracle.check(p_chk, A, B, C0, C)
+            assert bad == 0, (kern, worst)
+            ref = C0.copy()
+            assert oracle.gemm_netlib(p, A, B, ref, provider=1 if oracle.load_cblas() else 0) == 0
+            assert np.max(np.abs(ref - C)) < 1e-11
+        else:
+            assert_parity(p, A, B, C0, C, items, what=f"{dt} {oa}{ob} {m}x{n}x{k} via {kern}")
+
+
+def test_host_buffer_entry_matches_device_entry(bl):
+    for (dt, m, n, k, batch, beta, ldc_extra) in [("s", 32, 32, 32, 3000, -0.5, 0), ("d", 48, 40, 24, 50, 0.0, 3),
+                                                  ("z", 20, 10, 30, 7, 0.0, 0), ("s", 64, 64, 64, 100, 0.0, 0)]:
+        p = oracle.make_problem(dt, "N", "T", m, n, k, batch, ldc=m + ldc_extra, alpha=1.5, beta=beta)
+        A, B, C0 = make_inputs(p)
+        hA, hB = torch.from_numpy(A).pin_memory(), torch.from_numpy(B).pin_memory()
+        hC = torch.from_numpy(C0.copy()).pin_memory()
+        desc = bl.make_desc(hA.data_ptr(), hB.data_ptr(), hC.data_ptr(), p.dtype, p.op_a, p.op_b, m, n, k, batch,
+                            p.lda, p.ldb, p.ldc, p.stride_a, p.stride_b, p.stride_c, p.alpha, p.beta)
+        for chunk in (0, 7):
+            hC.copy_(torch.from_numpy(C0))
+            bl._lib.check(bl._lib.load().blb200_gemm_strided_batched_host(desc, 0, chunk))
+            assert_parity(p, A, B, C0, hC.numpy(), what=f"host entry {dt} chunk={chunk}")
+
+
+def test_device_fill_matches_numpy_statement(bl):
+    t = torch.empty(5000, dtype=torch.float32, device="cuda")
+    bl.fill(t, 42, 1, "uniform", first_index=123)
+    assert np.array_equal(t.cpu().numpy(), oracle.fill(0, 5000, 42, 1, "uniform", first=123))
+    z = torch.empty(3000, dtype=torch.complex128, device="cuda")
+    bl.fill(z, 7, 4, "normal", scale=0.5)
+    ref = oracle.fill(3, 3000, 7, 4, "normal", scale=0.5)
+    assert np.allclose(z.cpu().numpy(), ref, rtol=1e-12, atol=1e-14)
+
+
+def test_device_arena_lifecycle(bl):
+    L = bl._lib.load()
+    h = ctypes.c_void_p()
+    s = torch.cuda.Stream()
+    assert L.blb200_arena_create(0, s.cuda_stream, ctypes.byref(h)) == 0
+    a, b = bl._lib.Lease(), bl._lib.Lease()
+    assert L.blb200_arena_acquire(h, 1 << 20, ctypes.byref(a)) == 0
+    assert L.blb200_arena_acquire(h, 1 << 10, ctypes.byref(b)) == 0
+    assert a.ptr % 256 == 0 and b.ptr >= a.ptr + (1 << 20)
+    cap = L.blb200_arena_capacity(h)
+    assert L.blb200_arena_trim(h) == 0
+    L.blb200_arena_release(h, ctypes.byref(b))
+    L.blb200_arena_release(h, ctypes.byref(a))
+    c = bl._lib.Lease()
+    assert L.blb200_arena_acquire(h, 1 << 20, ctypes.byref(c)) == 0
+    assert c.ptr == a.ptr and L.blb200_arena_capacity(h) == cap  # repeated calls do not grow the arena
+    L.blb200_arena_release(h, ctypes.byref(c))
+    assert L.blb200_arena_trim(h) == 1 and L.blb200_arena_capacity(h) == 0
+    assert L.blb200_arena_destroy(h) == 0
+
+
+def test_no_wait_was_abandoned(bl):
+    assert bl.device_status() == 0
