@@ -47,13 +47,37 @@ def _compile(src: str, force: bool, log_dir: str) -> str:
     return obj
 
 
+def _source_hash() -> str:
+    import hashlib
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    files = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".cuh", ".h")))
+    files.append(os.path.join(HERE, os.pardir, "include", "blb200.h"))
+    for f in files:
+        h.update(os.path.basename(f).encode())
+        with open(f, "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()
+
+
 def build(force: bool = False) -> str:
+    # A library whose recorded source hash matches is current, whatever the file times say
+    # (a copied tree does not keep them).
+    stamp = LIB + ".srchash"
+    digest = _source_hash()
+    if not force and os.path.exists(LIB) and os.path.exists(stamp) and open(stamp).read().strip() == digest:
+        return LIB
+    _build_objects_and_link(force)
+    with open(stamp, "w") as f:
+        f.write(digest)
+    return LIB
+
+
+def _build_objects_and_link(force: bool) -> None:
     os.makedirs(OBJ, exist_ok=True)
     with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as ex:
         objs = list(ex.map(lambda s: _compile(s, force, OBJ), SOURCES))
     if force or not os.path.exists(LIB) or any(os.path.getmtime(o) > os.path.getmtime(LIB) for o in objs):
         subprocess.check_call([_nvcc(), "-shared", "-o", LIB, *objs, "-cudart", "static", "-lpthread", "-ldl"])
-    return LIB
 
 
 if __name__ == "__main__":
