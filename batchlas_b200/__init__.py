@@ -7,9 +7,9 @@ over device memory (`gemm`), and the batch-sharding helper used for multi-GPU ru
 from . import _lib
 from ._lib import BlasError, GemmDesc, KERNEL_IDS
 from .gemm import (DTYPE_CODES, Transpose, device_status, fill, gemm, gemm_host, gemm_strided_batched,
-                   last_kernel_name, launch_count, make_desc)
+                   last_kernel_name, launch_count, make_desc, measure_pipe_peak)
 from .sharding import shard_range
 
 __all__ = ["_lib", "BlasError", "GemmDesc", "KERNEL_IDS", "DTYPE_CODES", "Transpose", "device_status",
            "fill", "gemm", "gemm_host", "gemm_strided_batched", "last_kernel_name", "launch_count",
-           "make_desc", "shard_range"]
+           "make_desc", "measure_pipe_peak", "shard_range"]

@@ -57,6 +57,7 @@ SIGNATURES = {
     "blb200_arena_capacity": (ctypes.c_size_t, [ctypes.c_void_p]),
     "blb200_arena_block_count": (ctypes.c_size_t, [ctypes.c_void_p]),
     "blb200_arena_alignment": (ctypes.c_size_t, [ctypes.c_void_p]),
+    "blb200_measure_pipe_peak": (ctypes.c_int, [ctypes.c_int32, ctypes.POINTER(ctypes.c_double)]),
     "blb200_fill": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.c_uint64, ctypes.c_uint64,
                                    ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int32, ctypes.c_double,
                                    ctypes.c_void_p]),

@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libbatchlas_b200.so")
 SOURCES = ["dispatch.cu", "gemm_generic.cu", "gemm_small.cu", "gemm_tiled.cu", "arena.cu", "fill.cu",
-           "host_pipeline.cu", "status.cu"]
+           "host_pipeline.cu", "status.cu", "peak.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 

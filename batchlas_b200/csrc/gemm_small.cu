@@ -205,6 +205,193 @@ int launch32(const GemmParams& p, cudaStream_t stream) {
   return (int)cudaGetLastError();
 }
 
+
+// ---- small64 ---------------------------------------------------------------------------------
+// m = n = k = 64, float, packed (ld = 64).  Two consumer warps share one matrix: warp half hw owns
+// columns 32*hw .. 32*hw+31 and each lane an 8 x 8 block of C (64 accumulators), which is what
+// lets the FP32 pipe rather than shared memory set the pace (16 fragment floats per 64 FMAs).
+//
+// A K-major operand cannot be read 128 bits at a time without bank conflicts when its rows sit
+// 256 bytes apart, so it is brought in row by row — 64 bulk copies of 256 bytes — into rows
+// pitched 272 bytes apart, and its rows (or columns) are dealt to lanes round-robin:
+//   A K-major: lane rows ti + 8r        (r = 0..7);   else rows 4ti..4ti+3 and 32+4ti..32+4ti+3
+//   B K-major: lane cols 32hw + tj + 4c (c = 0..7);   else cols 32hw + 8tj + c
+// With that, every fragment request of a warp touches each 16-byte bank group at most once.
+constexpr int kPairs64 = 4;
+constexpr int kThreads64 = 32 * (1 + 2 * kPairs64);
+constexpr int kMatBytes64 = 64 * 64 * 4;
+constexpr int kPitch64 = 272;                    // bytes between rows of a K-major operand
+constexpr int kPadBytes64 = 64 * kPitch64;       // 17408
+
+template <bool A_KMAJOR, bool B_KMAJOR>
+__device__ __forceinline__ void mma64(const unsigned char* __restrict__ As, const unsigned char* __restrict__ Bs,
+                                      int ti, int tj, int hw, float (&acc)[8][8]) {
+  const float4* As4 = reinterpret_cast<const float4*>(As);
+  const float4* Bs4 = reinterpret_cast<const float4*>(Bs);
+#pragma unroll 2
+  for (int kc = 0; kc < 16; ++kc) {
+    float af[8][4], bf[8][4];  // [row or col][kk]
+    if (A_KMAJOR) {
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float4 v = As4[(ti + 8 * r) * (kPitch64 / 16) + kc];
+        af[r][0] = v.x; af[r][1] = v.y; af[r][2] = v.z; af[r][3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const float4 lo = As4[(4 * kc + kk) * 16 + ti];
+        const float4 hi = As4[(4 * kc + kk) * 16 + 8 + ti];
+        af[0][kk] = lo.x; af[1][kk] = lo.y; af[2][kk] = lo.z; af[3][kk] = lo.w;
+        af[4][kk] = hi.x; af[5][kk] = hi.y; af[6][kk] = hi.z; af[7][kk] = hi.w;
+      }
+    }
+    if (B_KMAJOR) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float4 v = Bs4[(32 * hw + tj + 4 * c) * (kPitch64 / 16) + kc];
+        bf[c][0] = v.x; bf[c][1] = v.y; bf[c][2] = v.z; bf[c][3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const float4 v0 = Bs4[(4 * kc + kk) * 16 + 8 * hw + 2 * tj];
+        const float4 v1 = Bs4[(4 * kc + kk) * 16 + 8 * hw + 2 * tj + 1];
+        bf[0][kk] = v0.x; bf[1][kk] = v0.y; bf[2][kk] = v0.z; bf[3][kk] = v0.w;
+        bf[4][kk] = v1.x; bf[5][kk] = v1.y; bf[6][kk] = v1.z; bf[7][kk] = v1.w;
+      }
+    }
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[r][c] = fmaf(af[r][kk], bf[c][kk], acc[r][c]);
+  }
+}
+
+template <bool A_KMAJOR, bool B_KMAJOR, bool HAS_C>
+__global__ void __launch_bounds__(kThreads64, 1)
+    gemm_small64_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
+                        long long sa, long long sb, long long sc, int batch, float alpha, float beta,
+                        int stages) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int kABytes = A_KMAJOR ? kPadBytes64 : kMatBytes64;
+  constexpr int kBBytes = B_KMAJOR ? kPadBytes64 : kMatBytes64;
+  constexpr int kStageBytes = kABytes + kBBytes + (HAS_C ? kMatBytes64 : 0);
+  constexpr uint32_t kTxBytes = (uint32_t)(2 + (HAS_C ? 1 : 0)) * kMatBytes64;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)stages * kStageBytes);
+  uint64_t* empty_bar = full_bar + stages;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 2);  // one arrival per warp of the pair
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  const int my_items = (batch > (int)blockIdx.x) ? (batch - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+
+  if (warp == 0) {
+    for (int j = 0; j < my_items; ++j) {
+      const int s = j % stages;
+      const uint32_t round = (uint32_t)(j / stages);
+      if (!mbar_wait(&empty_bar[s], (round & 1u) ^ 1u, kWaitEmpty)) return;
+      const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
+      unsigned char* st = smem + (size_t)s * kStageBytes;
+      if (lane == 0) mbar_arrive_expect_tx(&full_bar[s], kTxBytes);
+      __syncwarp();
+      const float* Ai = A + item * sa;
+      const float* Bi = B + item * sb;
+      if (A_KMAJOR) {
+        for (int r = lane; r < 64; r += 32) bulk_g2s(st + r * kPitch64, Ai + r * 64, 256, &full_bar[s]);
+      } else if (lane == 0) {
+        bulk_g2s(st, Ai, kMatBytes64, &full_bar[s]);
+      }
+      if (B_KMAJOR) {
+        for (int r = lane; r < 64; r += 32) bulk_g2s(st + kABytes + r * kPitch64, Bi + r * 64, 256, &full_bar[s]);
+      } else if (lane == 0) {
+        bulk_g2s(st + kABytes, Bi, kMatBytes64, &full_bar[s]);
+      }
+      if (HAS_C && lane == 0) bulk_g2s(st + kABytes + kBBytes, C + item * sc, kMatBytes64, &full_bar[s]);
+    }
+    return;
+  }
+
+  const int pair = (warp - 1) >> 1, hw = (warp - 1) & 1;
+  const int ti = lane & 7, tj = lane >> 3;
+  for (int j = pair; j < my_items; j += kPairs64) {
+    const int s = j % stages;
+    const uint32_t round = (uint32_t)(j / stages);
+    if (!mbar_wait(&full_bar[s], round & 1u, kWaitFull)) return;
+    const unsigned char* st = smem + (size_t)s * kStageBytes;
+
+    float acc[8][8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+#pragma unroll
+      for (int c = 0; c < 8; ++c) acc[r][c] = 0.f;
+    mma64<A_KMAJOR, B_KMAJOR>(st, st + kABytes, ti, tj, hw, acc);
+
+    const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
+    float* Cg = C + item * sc;
+    const float* Cs = reinterpret_cast<const float*>(st + kABytes + kBBytes);
+    // alpha*acc (+ beta*prior from shared memory) in place, then release the stage, then store.
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int col = B_KMAJOR ? (32 * hw + tj + 4 * c) : (32 * hw + 8 * tj + c);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const int row = A_KMAJOR ? (ti + 8 * r) : ((r < 4 ? 0 : 32) + 4 * ti + (r & 3));
+        float o = alpha * acc[r][c];
+        if (HAS_C) o = fmaf(beta, Cs[col * 64 + row], o);
+        acc[r][c] = o;
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[s]);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int col = B_KMAJOR ? (32 * hw + tj + 4 * c) : (32 * hw + 8 * tj + c);
+      if (A_KMAJOR) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) Cg[col * 64 + ti + 8 * r] = acc[r][c];
+      } else {
+        float4* dst = reinterpret_cast<float4*>(Cg + col * 64);
+        dst[ti] = make_float4(acc[0][c], acc[1][c], acc[2][c], acc[3][c]);
+        dst[8 + ti] = make_float4(acc[4][c], acc[5][c], acc[6][c], acc[7][c]);
+      }
+    }
+  }
+}
+
+template <bool AK, bool BK, bool HC>
+int launch64(const GemmParams& p, cudaStream_t stream) {
+  const DeviceInfo& dev = device_info();
+  constexpr int kStageBytes = (AK ? kPadBytes64 : kMatBytes64) + (BK ? kPadBytes64 : kMatBytes64) + (HC ? kMatBytes64 : 0);
+  const size_t budget = dev.smem_optin > 8192 ? dev.smem_optin - 4096 : 0;
+  int stages = (int)(budget / (size_t)kStageBytes);
+  if (stages > 8) stages = 8;
+  if (stages < 2) return BLB200_E_UNSUPPORTED;
+  const size_t smem = (size_t)stages * kStageBytes + (size_t)stages * 2 * sizeof(uint64_t);
+  auto kern = gemm_small64_kernel<AK, BK, HC>;
+  static thread_local int configured_for = -1;
+  int cur = 0;
+  cudaGetDevice(&cur);
+  if (configured_for != cur) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured_for = cur;
+  }
+  const int grid = p.batch < dev.sm_count ? p.batch : dev.sm_count;
+  kern<<<grid, kThreads64, smem, stream>>>((const float*)p.a, (const float*)p.b, (float*)p.c, p.sa, p.sb, p.sc,
+                                           p.batch, (float)p.alpha[0], (float)p.beta[0], stages);
+  return (int)cudaGetLastError();
+}
+
 inline bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
 
 }  // namespace
@@ -235,8 +422,31 @@ int launch_small32(const GemmParams& p, int dtype, cudaStream_t stream) {
   return rc;
 }
 
-bool small64_supported(const GemmParams&, int) { return false; }
-int launch_small64(const GemmParams&, int, cudaStream_t) { return BLB200_E_UNSUPPORTED; }
+bool small64_supported(const GemmParams& p, int dtype) {
+  if (dtype != BLB200_S) return false;
+  if (p.m != 64 || p.n != 64 || p.k != 64) return false;
+  if (p.lda != 64 || p.ldb != 64 || p.ldc != 64) return false;
+  if ((p.sa & 3) || (p.sb & 3) || (p.sc & 3)) return false;
+  if (p.batch > 1 && p.sc < 4096) return false;
+  if (!aligned16(p.a) || !aligned16(p.b) || !aligned16(p.c)) return false;
+  return true;
+}
+
+int launch_small64(const GemmParams& p, int dtype, cudaStream_t stream) {
+  if (!small64_supported(p, dtype)) return BLB200_E_UNSUPPORTED;
+  const bool ak = p.op_a != BLB200_N;
+  const bool bk = p.op_b == BLB200_N;
+  const bool hc = (float)p.beta[0] != 0.f;
+  int rc;
+#define BLB_CASE(a, b)                                                              \
+  if (ak == a && bk == b) {                                                         \
+    rc = hc ? launch64<a, b, true>(p, stream) : launch64<a, b, false>(p, stream);   \
+  } else
+  BLB_CASE(false, false) BLB_CASE(false, true) BLB_CASE(true, false) BLB_CASE(true, true) { rc = BLB200_E_INTERNAL; }
+#undef BLB_CASE
+  if (rc == BLB200_OK) note_launch("small64");
+  return rc;
+}
 
 int small_device_status(int* out) { return read_device_status_word(out); }
 

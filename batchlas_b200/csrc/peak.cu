@@ -1,0 +1,69 @@
+// FMA issue-rate microbenchmarks: the measured FP32 / FP64 pipe peaks that the compute-bound
+// configurations are judged against (the nominal figures are SMs x lanes x 2 x max clock).
+// Each thread runs 16 independent dependent-chains of FMAs held in registers; nothing touches memory
+// until one value is written at the end so the loop cannot be removed.
+#include "common.cuh"
+
+namespace blb200 {
+namespace {
+
+template <typename R>
+__global__ void __launch_bounds__(256) fma_rate_kernel(R* sink, int iters, R a, R b) {
+  R acc[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) acc[i] = (R)(threadIdx.x + i);
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int rep = 0; rep < 4; ++rep)
+#pragma unroll
+      for (int i = 0; i < 16; ++i) acc[i] = acc[i] * a + b;  // contracted to one FMA
+  }
+  R total = 0;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) total += acc[i];
+  if (total == (R)123456789) sink[0] = total;  // practically never true; keeps the chain live
+}
+
+template <typename R>
+int measure(double* tflops, double* ms_out) {
+  const DeviceInfo& dev = device_info();
+  R* sink = nullptr;
+  cudaError_t e = cudaMalloc(&sink, sizeof(R));
+  if (e != cudaSuccess) return (int)e;
+  const int iters = 4096, blocks = dev.sm_count * 8, threads = 256;
+  cudaEvent_t t0, t1;
+  cudaEventCreate(&t0);
+  cudaEventCreate(&t1);
+  fma_rate_kernel<R><<<blocks, threads>>>(sink, 64, (R)0.999, (R)0.001);  // warm-up
+  float best = 1e30f;
+  for (int rep = 0; rep < 5; ++rep) {
+    cudaEventRecord(t0);
+    fma_rate_kernel<R><<<blocks, threads>>>(sink, iters, (R)0.999, (R)0.001);
+    cudaEventRecord(t1);
+    e = cudaEventSynchronize(t1);
+    if (e != cudaSuccess) break;
+    float ms = 0;
+    cudaEventElapsedTime(&ms, t0, t1);
+    if (ms < best) best = ms;
+  }
+  cudaEventDestroy(t0);
+  cudaEventDestroy(t1);
+  cudaFree(sink);
+  if (e != cudaSuccess) return (int)e;
+  const double flops = 2.0 * 64.0 * iters * (double)blocks * threads;
+  *tflops = flops / (best * 1e-3) / 1e12;
+  if (ms_out) *ms_out = best;
+  return BLB200_OK;
+}
+
+}  // namespace
+}  // namespace blb200
+
+// Measures the FMA issue rate of the current device for float (dtype S) or double (dtype D) in
+// TFLOP/s (2 flops per FMA).  Synchronous; allocates a few bytes; a diagnostic, not a data path.
+extern "C" int blb200_measure_pipe_peak(int32_t dtype, double* tflops) {
+  if (!tflops) return BLB200_E_NULL;
+  if (dtype == BLB200_S) return blb200::measure<float>(tflops, nullptr);
+  if (dtype == BLB200_D) return blb200::measure<double>(tflops, nullptr);
+  return BLB200_E_DTYPE;
+}

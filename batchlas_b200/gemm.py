@@ -148,3 +148,11 @@ def device_status() -> int:
     out = ctypes.c_int(0)
     check(load().blb200_device_status(ctypes.byref(out)))
     return out.value
+
+
+def measure_pipe_peak(dtype: str = "s") -> float:
+    """Measured FFMA ("s") or DFMA ("d") issue rate of the current device, TFLOP/s."""
+    import ctypes
+    out = ctypes.c_double(0.0)
+    check(load().blb200_measure_pipe_peak({"s": _lib.S, "d": _lib.D}[dtype], ctypes.byref(out)))
+    return out.value

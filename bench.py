@@ -188,9 +188,6 @@ def alloc_config(bl, torch, c, batch, first_item, device):
     """Device operands for `batch` items of configuration c starting at global item `first_item`."""
     dt = {"s": torch.float32, "d": torch.float64, "c": torch.complex64, "z": torch.complex128}[c["dtype"]]
     pad = c["pad"]
-    shapes = {}
-    for which in "abc":
-        shapes[which] = None
     tensors, meta = {}, {}
     for tid, which in ((1, "a"), (2, "b"), (3, "c")):
         if which == "c":
@@ -351,6 +348,10 @@ def run_ours(args, rank, local_rank, world):
     flops_step = flops_per_item(c2) * batch * len(c2["ops"]) * world
     value = flops_step / (ms_per_step * 1e-3) / 1e9
 
+    per_op_ms = {}
+    for (oa, ob), d in zip(c2["ops"], descs):
+        per_op_ms[oa + ob] = max_over_ranks(time_launches(torch, lambda d=d: bl.gemm_strided_batched(d), max(3, args.steps)))
+
     # parity spot-check on the exact buffers that were timed (restores C first)
     worst = max(verify_sample(bl, torch, c2, op, tensors, meta, batch, first_item) for op in c2["ops"])
 
@@ -363,6 +364,7 @@ def run_ours(args, rank, local_rank, world):
                 "peak_source": f"{peak_kind} STREAM-style copy (burst; kernel timed alone)",
                 "traffic": (NCU_TRAFFIC_BYTES_PER_ITEM * batch if NCU_TRAFFIC_BYTES_PER_ITEM else None),
                 "algorithmic_bytes_per_launch": bytes_launch, "kernel": kernel_name, "launch_ms": launch_ms,
+                "launch_ms_by_op": per_op_ms,
                 "frac_of_8TBs_definition": achieved / NOMINAL_HBM_GBS}
 
     # ---- end to end: host buffers through the C ABI, copies inside the timed region ----------------
@@ -411,7 +413,10 @@ def run_ours(args, rank, local_rank, world):
 
     # ---- the other configurations, device-timed, batch sharded over the ranks (strong) ------------
     extra = {}
+    pipe_peaks = None
     if not args.no_extra:
+        pipe_peaks = {"fp32_tflops_measured": bl.measure_pipe_peak("s"), "fp64_tflops_measured": bl.measure_pipe_peak("d"),
+                      "fp32_tflops_nominal": PIPE_PEAK_TFLOPS["s"], "fp64_tflops_nominal": PIPE_PEAK_TFLOPS["d"]}
         for name in ("C1", "C3", "C4", "C5"):
             c = cfgs[name]
             b0, nb = shard_range(c["batch"], rank, world)
@@ -426,9 +431,16 @@ def run_ours(args, rank, local_rank, world):
                     launch()
                 torch.cuda.synchronize()
                 one = time_launches(torch, launch, 1)
-                reps = int(max(3, min(200, 60.0 / max(one, 1e-3))))
+                reps = int(max(3, min(2000, 400.0 / max(one, 1e-3))))
                 barrier()
+                smp = ClockSampler(local_rank)
+                smp.start()
+                time.sleep(0.15)
+                tw0 = time.time()
                 ms = max_over_ranks(time_launches(torch, launch, reps))
+                tw1 = time.time()
+                smp.stop()
+                clk = smp.summary(tw0, tw1)
                 kern = bl.last_kernel_name()
                 w = verify_sample(bl, torch, c, op, tens, mt, nb, b0, n_check=2)
                 total_flops = flops_per_item(c) * c["batch"]
@@ -436,7 +448,8 @@ def run_ours(args, rank, local_rank, world):
                 ai = flops_per_item(c) / algorithmic_bytes_per_item(c)
                 roof = min(PIPE_PEAK_TFLOPS[c["dtype"]] * world, ai * NOMINAL_HBM_GBS * 1e9 / 1e12 * world)
                 per_op[op[0] + op[1]] = {"gflops": tfl * 1e3, "ms": ms, "kernel": kern,
-                                         "frac_of_roofline": tfl / roof, "worst_error_ratio": w,
+                                         "frac_of_roofline": tfl / roof, "worst_error_ratio": w, "reps": reps,
+                                         "sm_mhz": clk["sm_mhz"], "clock_reasons": clk["reasons"],
                                          "hbm_gbs": algorithmic_bytes_per_item(c) * c["batch"] / (ms * 1e-3) / 1e9}
             extra[name] = per_op
             del tens
@@ -461,9 +474,38 @@ def run_ours(args, rank, local_rank, world):
             line["cpu_baseline"] = cpu_baseline("C2")
         if extra:
             line["configs"] = extra
+            line["pipe_peaks"] = pipe_peaks
+            line["configs_note"] = ("device-timed, whole BASELINE batch sharded contiguously over the ranks; "
+                                    "frac_of_roofline = achieved / min(nominal pipe peak, AI x 8 TB/s)")
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_case(args):
+    """One configuration, one op, a chosen batch: the small case that ncu captures.
+    Prints one JSON line with the CUDA-event time per launch."""
+    import torch
+
+    import batchlas_b200 as bl
+    name, _, op = args.case.partition(":")
+    c = configs()[name]
+    ops = [tuple(op)] if op else c["ops"]
+    batch = args.batch or c["batch"]
+    torch.cuda.set_device(0)
+    tens, mt = alloc_config(bl, torch, c, batch, 0, torch.device("cuda", 0))
+    out = {"case": name, "batch": batch, "ops": {}}
+    for o in ops:
+        d = desc_for(bl, c, o, tens, mt, batch, kernel=args.kernel)
+        for _ in range(args.warmup):
+            bl.gemm_strided_batched(d)
+        torch.cuda.synchronize()
+        ms = time_launches(torch, lambda: bl.gemm_strided_batched(d), args.steps)
+        w = verify_sample(bl, torch, c, o, tens, mt, batch, 0, n_check=2)
+        out["ops"][o[0] + o[1]] = {"ms": ms, "kernel": bl.last_kernel_name(), "worst_error_ratio": w,
+                                   "gflops": flops_per_item(c) * batch / (ms * 1e-3) / 1e9,
+                                   "hbm_gbs": algorithmic_bytes_per_item(c) * batch / (ms * 1e-3) / 1e9}
+    print(json.dumps(out), flush=True)
 
 
 def main():
@@ -475,12 +517,18 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the C1/C3/C4/C5 figures")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--case", default="", help="profiling mode: CONFIG[:OP], e.g. C2:NT or C3:TN (1 GPU)")
+    ap.add_argument("--batch", type=int, default=0, help="batch override for --case")
+    ap.add_argument("--kernel", default="auto", help="forced kernel for --case")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference_arm(args, rank)
+        return
+    if args.case:
+        run_case(args)
         return
     if world != args.gpus and world == 1 and args.gpus > 1:
         raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")

@@ -107,6 +107,11 @@ const char* blb200_version(void);
  * on one of its bounded waits: *out = 0 when none did, else a small code naming the wait. */
 int blb200_device_status(int* out);
 
+/* Diagnostic: measured FMA issue rate of the current device in TFLOP/s (2 flops per FMA) for
+ * dtype BLB200_S (FFMA) or BLB200_D (DFMA) — the pipe peak that compute-bound shapes are judged
+ * against, next to the nominal SMs x lanes x 2 x clock figure.  Synchronous. */
+int blb200_measure_pipe_peak(int32_t dtype, double* tflops);
+
 /* ---- per-queue workspace arena -------------------------------------------------------
  * Bump/LIFO arena with the lease semantics of BatchLAS's WorkspaceArena (src/queue.hh:41-226,
  * include/util/workspace.hh:70-162), re-backed by cudaMallocAsync on the queue's stream:
