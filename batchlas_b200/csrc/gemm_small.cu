@@ -1,34 +1,61 @@
 // Whole-matrix-per-warp kernels for packed small float matrices: the HBM-bound end of the family.
 //
-// small32: m = n = k = 32, float, ld = 32 on all three operands, batch strides that are multiples
-// of 4 elements, 16-byte aligned bases (BatchLAS's own fast paths are gated the same way:
-// src/sycl/gemm/load_policies.hh:18-34).  Each 4 KiB matrix is one contiguous run in memory, so an
-// item's operands are fetched by three untiled bulk copies (TMA, cp.async.bulk) issued by one
-// producer thread into a ring of shared-memory stages guarded by full/empty mbarriers.  Consumer
-// warps each own one matrix at a time: a lane keeps a 4 x 8 block of C in registers (rows
-// 4*ti..4*ti+3, columns 8*tj..8*tj+7, ti = lane & 7, tj = lane >> 3) and reads operands from shared
-// memory as 128-bit fragments, then writes C with 128-bit stores (8 lanes cover one 128-byte
-// column).  A persistent grid of one CTA per SM walks the batch round-robin.
+// Shared structure.  A persistent grid of one CTA per SM walks the batch round-robin.  Warp 0 is
+// the producer: each of its lanes owns one ring slot and, independently of the other lanes, waits
+// for that slot's "empty" mbarrier and issues the slot's TMA copies (a single thread doing this
+// for every slot is latency-bound at about 4 KiB per 250 ns per SM, well under HBM speed).  The
+// other warps are consumers.  Every slot is consumed by the same warp (or warp pair) in every
+// round — a consumer therefore never waits for round r of a slot before round r-1 has completed,
+// which is what makes the one-bit mbarrier phase parity sufficient.
 //
+// small32: m = n = k = 32, ld = 32 on all three operands, 16-byte aligned bases, strides multiples
+// of 4 elements (BatchLAS gates its own vector fast paths the same way:
+// src/sycl/gemm/load_policies.hh:18-34).  Each 4 KiB matrix is one contiguous run, fetched by one
+// untiled bulk copy per operand.  One consumer warp per matrix; a lane keeps a 4 x 8 block of C
+// (rows 4ti..4ti+3, columns 8tj..8tj+7; ti = lane & 7, tj = lane >> 3), reads 128-bit fragments
+// from shared memory and writes C with 128-bit stores (8 lanes cover one 128-byte column).
 // Operand orientation only changes how fragments are read; nothing is transposed in memory:
 //   M-major A (op N): float4 = 4 rows at one k.        K-major A (op T): float4 = 4 k at one row.
 //   N-major B (op T): float4 = 4 cols at one k.        K-major B (op N): float4 = 4 k at one col.
-// With a K-major operand, lanes walk the eight 4-wide k-chunks in a lane-dependent rotation so
-// that the lanes of one shared-memory request fall into different 16-byte bank groups; the sum
-// over k is the same set of products in a different order.
+// With a K-major operand, lanes walk the eight 4-wide k-chunks in a lane-dependent rotation so that
+// the lanes of one request fall into different 16-byte bank groups; the sum over k is the same
+// set of products in a different order.
 //
-// Algorithmic traffic per item: A + B (+ C when beta != 0) read and C written, 4 KiB each.
+// small64: m = n = k = 64, ld = 64, same alignment rules.  Two consumer warps share one matrix
+// (warp half hw owns columns 32hw..32hw+31, each lane an 8 x 8 block: 16 fragment floats per 64
+// FMAs, so the FP32 pipe rather than shared memory sets the pace).  The ring holds half-K slots of
+// 16 KiB (A half + B half); each of the 4 pairs owns 3 slots.  An M-major / N-major half is one
+// contiguous 8 KiB run (untiled bulk copy).  A K-major half is 64 rows of 128 bytes, 256 bytes
+// apart in memory: it is fetched by one tiled TMA copy (cp.async.bulk.tensor.3d, box 32 x 64 x 1)
+// with the 128-byte swizzle, which XORs the 16-byte chunk index with (row & 7); with rows (or
+// columns) dealt to lanes round-robin, every fragment request then touches each bank group once.
+//
+// Algorithmic traffic per item: A + B (+ C when beta != 0) read and C written.
+#include <cuda.h>
+#include <stdlib.h>
+#include <string.h>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
 namespace blb200 {
 namespace {
 
-constexpr int kConsumerWarps = 8;
-constexpr int kThreads32 = 32 * (1 + kConsumerWarps);
-constexpr int kMatBytes32 = 32 * 32 * 4;
+enum WaitCode { kWaitFull = 101, kWaitEmpty = 102 };
 
-enum WaitCode { kWaitFull = 101, kWaitEmpty = 102, kWaitDrain = 103 };
+inline bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
+
+int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return (v && *v) ? atoi(v) : dflt;
+}
+
+// =================================================================================================
+// small32
+// =================================================================================================
+constexpr int kConsumerWarps32 = 8;
+constexpr int kThreads32 = 32 * (1 + kConsumerWarps32);
+constexpr int kMatBytes32 = 32 * 32 * 4;
 
 // acc[r][c] += sum_k opA(4ti+r, k) * opB(k, 8tj+c) for one 32x32x32 item held in shared memory.
 template <bool A_KMAJOR, bool B_KMAJOR>
@@ -94,6 +121,7 @@ __device__ __forceinline__ void mma32(const float4* __restrict__ As4, const floa
 }
 
 // Shared memory: `stages` x {A, B[, C]} of 4 KiB each, then full[stages], empty[stages] barriers.
+// `stages` is a multiple of kConsumerWarps32 and at most 32 (one producer lane per stage).
 template <bool A_KMAJOR, bool B_KMAJOR, bool HAS_C>
 __global__ void __launch_bounds__(kThreads32, 1)
     gemm_small32_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
@@ -114,22 +142,20 @@ __global__ void __launch_bounds__(kThreads32, 1)
   }
   __syncthreads();
 
-  // Items of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...; the j-th one uses stage j % stages
-  // and consumer warp j % kConsumerWarps (stages is a multiple of kConsumerWarps).
+  // Items of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...; the j-th one uses stage j % stages.
   const int my_items = (batch > (int)blockIdx.x) ? (batch - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
   if (warp == 0) {
-    if (lane == 0) {
-      for (int j = 0; j < my_items; ++j) {
-        const int s = j % stages;
-        const uint32_t round = (uint32_t)(j / stages);
-        if (!mbar_wait(&empty_bar[s], (round & 1u) ^ 1u, kWaitEmpty)) return;
+    if (lane < stages) {  // lane == stage
+      unsigned char* st = smem + (size_t)lane * kStageBytes;
+      uint32_t round = 0;
+      for (int j = lane; j < my_items; j += stages, ++round) {
+        if (!mbar_wait(&empty_bar[lane], (round & 1u) ^ 1u, kWaitEmpty)) return;
         const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
-        unsigned char* st = smem + (size_t)s * kStageBytes;
-        mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
-        bulk_g2s(st, A + item * sa, kMatBytes32, &full_bar[s]);
-        bulk_g2s(st + kMatBytes32, B + item * sb, kMatBytes32, &full_bar[s]);
-        if (HAS_C) bulk_g2s(st + 2 * kMatBytes32, C + item * sc, kMatBytes32, &full_bar[s]);
+        mbar_arrive_expect_tx(&full_bar[lane], kStageBytes);
+        bulk_g2s(st, A + item * sa, kMatBytes32, &full_bar[lane]);
+        bulk_g2s(st + kMatBytes32, B + item * sb, kMatBytes32, &full_bar[lane]);
+        if (HAS_C) bulk_g2s(st + 2 * kMatBytes32, C + item * sc, kMatBytes32, &full_bar[lane]);
       }
     }
     return;
@@ -137,9 +163,9 @@ __global__ void __launch_bounds__(kThreads32, 1)
 
   const int cw = warp - 1;
   const int ti = lane & 7, tj = lane >> 3;
-  for (int j = cw; j < my_items; j += kConsumerWarps) {
-    const int s = j % stages;
-    const uint32_t round = (uint32_t)(j / stages);
+  int s = cw;          // stage of this warp's current item: (cw + 8*i) % stages
+  uint32_t round = 0;  // how many times this warp has been through stage `s` before
+  for (int j = cw; j < my_items; j += kConsumerWarps32) {
     if (!mbar_wait(&full_bar[s], round & 1u, kWaitFull)) return;
     const unsigned char* st = smem + (size_t)s * kStageBytes;
     const float4* As4 = reinterpret_cast<const float4*>(st);
@@ -159,7 +185,7 @@ __global__ void __launch_bounds__(kThreads32, 1)
       for (int c = 0; c < 8; ++c) prior[c] = Cs4[(8 * tj + c) * 8 + ti];
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(&empty_bar[s]);  // stage may be refilled while we store
+    if (lane == 0) mbar_arrive(&empty_bar[s]);  // the slot may be refilled while we store
 
     const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
     float4* Cg4 = reinterpret_cast<float4*>(C + item * sc);
@@ -178,6 +204,11 @@ __global__ void __launch_bounds__(kThreads32, 1)
       }
       Cg4[(8 * tj + c) * 8 + ti] = o;
     }
+    s += kConsumerWarps32;
+    if (s >= stages) {
+      s -= stages;
+      ++round;
+    }
   }
 }
 
@@ -186,16 +217,19 @@ int launch32(const GemmParams& p, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
   constexpr int kStageBytes = (HC ? 3 : 2) * kMatBytes32;
   const size_t budget = dev.smem_optin > 8192 ? dev.smem_optin - 4096 : 0;
-  int stages = (int)(budget / ((size_t)kStageBytes * kConsumerWarps)) * kConsumerWarps;
+  static const int want = env_int("BLB200_SMALL32_STAGES", 16);  // tuning knob; rounded to a legal value
+  int stages = (int)(budget / ((size_t)kStageBytes * kConsumerWarps32)) * kConsumerWarps32;
   if (stages > 32) stages = 32;
-  if (stages < kConsumerWarps) return BLB200_E_UNSUPPORTED;
+  if (want >= kConsumerWarps32 && want < stages) stages = want / kConsumerWarps32 * kConsumerWarps32;
+  if (stages < kConsumerWarps32) return BLB200_E_UNSUPPORTED;
   const size_t smem = (size_t)stages * kStageBytes + (size_t)stages * 2 * sizeof(uint64_t);
   auto kern = gemm_small32_kernel<AK, BK, HC>;
   static thread_local int configured_for = -1;  // per (instantiation, thread): device last configured
   int cur = 0;
   cudaGetDevice(&cur);
   if (configured_for != cur) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)(budget < smem ? smem : budget));
     if (e != cudaSuccess) return (int)e;
     configured_for = cur;
   }
@@ -205,39 +239,33 @@ int launch32(const GemmParams& p, cudaStream_t stream) {
   return (int)cudaGetLastError();
 }
 
-
-// ---- small64 ---------------------------------------------------------------------------------
-// m = n = k = 64, float, packed (ld = 64).  Two consumer warps share one matrix: warp half hw owns
-// columns 32*hw .. 32*hw+31 and each lane an 8 x 8 block of C (64 accumulators), which is what
-// lets the FP32 pipe rather than shared memory set the pace (16 fragment floats per 64 FMAs).
-//
-// A K-major operand cannot be read 128 bits at a time without bank conflicts when its rows sit
-// 256 bytes apart, so it is brought in row by row — 64 bulk copies of 256 bytes — into rows
-// pitched 272 bytes apart, and its rows (or columns) are dealt to lanes round-robin:
-//   A K-major: lane rows ti + 8r        (r = 0..7);   else rows 4ti..4ti+3 and 32+4ti..32+4ti+3
-//   B K-major: lane cols 32hw + tj + 4c (c = 0..7);   else cols 32hw + 8tj + c
-// With that, every fragment request of a warp touches each 16-byte bank group at most once.
+// =================================================================================================
+// small64
+// =================================================================================================
 constexpr int kPairs64 = 4;
+constexpr int kSlotsPerPair64 = 3;
+constexpr int kSlots64 = kPairs64 * kSlotsPerPair64;  // 12 half-K slots
 constexpr int kThreads64 = 32 * (1 + 2 * kPairs64);
-constexpr int kMatBytes64 = 64 * 64 * 4;
-constexpr int kPitch64 = 272;                    // bytes between rows of a K-major operand
-constexpr int kPadBytes64 = 64 * kPitch64;       // 17408
+constexpr int kHalfBytes64 = 32 * 64 * 4;             // one operand, half of K: 8 KiB
+constexpr int kSlotBytes64 = 2 * kHalfBytes64;        // A half + B half
+constexpr int kMatElems64 = 64 * 64;
 
+// One half-K (32 k) of the product for this lane's 8 x 8 block.
 template <bool A_KMAJOR, bool B_KMAJOR>
-__device__ __forceinline__ void mma64(const unsigned char* __restrict__ As, const unsigned char* __restrict__ Bs,
-                                      int ti, int tj, int hw, float (&acc)[8][8]) {
+__device__ __forceinline__ void mma64_half(const unsigned char* __restrict__ As, const unsigned char* __restrict__ Bs,
+                                           int ti, int tj, int hw, float (&acc)[8][8]) {
   const float4* As4 = reinterpret_cast<const float4*>(As);
   const float4* Bs4 = reinterpret_cast<const float4*>(Bs);
 #pragma unroll 2
-  for (int kc = 0; kc < 16; ++kc) {
+  for (int kc = 0; kc < 8; ++kc) {
     float af[8][4], bf[8][4];  // [row or col][kk]
-    if (A_KMAJOR) {
+    if (A_KMAJOR) {            // swizzled rows of 128 bytes: row i = ti + 8r, i & 7 == ti
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
-        const float4 v = As4[(ti + 8 * r) * (kPitch64 / 16) + kc];
+        const float4 v = As4[(ti + 8 * r) * 8 + (kc ^ ti)];
         af[r][0] = v.x; af[r][1] = v.y; af[r][2] = v.z; af[r][3] = v.w;
       }
-    } else {
+    } else {                   // k-rows of 256 bytes: rows 4ti..4ti+3 and 32+4ti..32+4ti+3
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
         const float4 lo = As4[(4 * kc + kk) * 16 + ti];
@@ -246,13 +274,14 @@ __device__ __forceinline__ void mma64(const unsigned char* __restrict__ As, cons
         af[4][kk] = hi.x; af[5][kk] = hi.y; af[6][kk] = hi.z; af[7][kk] = hi.w;
       }
     }
-    if (B_KMAJOR) {
+    if (B_KMAJOR) {            // swizzled: column j = 32hw + tj + 4c, j & 7 == (tj + 4c) & 7
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
-        const float4 v = Bs4[(32 * hw + tj + 4 * c) * (kPitch64 / 16) + kc];
+        const int j = 32 * hw + tj + 4 * c;
+        const float4 v = Bs4[j * 8 + (kc ^ (j & 7))];
         bf[c][0] = v.x; bf[c][1] = v.y; bf[c][2] = v.z; bf[c][3] = v.w;
       }
-    } else {
+    } else {                   // k-rows of 256 bytes: columns 32hw + 8tj + c
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
         const float4 v0 = Bs4[(4 * kc + kk) * 16 + 8 * hw + 2 * tj];
@@ -270,22 +299,31 @@ __device__ __forceinline__ void mma64(const unsigned char* __restrict__ As, cons
   }
 }
 
+// tiled TMA load of one (32 k) x (64 rows) x (1 item) box; x0 = first k (0 or 32), z = batch item.
+__device__ __forceinline__ void tma_load_3d(void* dst_smem, const CUtensorMap* map, int x0, int y0, int z,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
+          "r"(smem_u32(dst_smem)), "l"(map), "r"(x0), "r"(y0), "r"(z), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// Pair p's q-th half-item lives in slot p*3 + q % 3 (round q / 3); half-item q is half q & 1 of
+// the pair's (q >> 1)-th item.  Producer lane l < 12 owns slot l.
 template <bool A_KMAJOR, bool B_KMAJOR, bool HAS_C>
 __global__ void __launch_bounds__(kThreads64, 1)
     gemm_small64_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
                         long long sa, long long sb, long long sc, int batch, float alpha, float beta,
-                        int stages) {
-  extern __shared__ __align__(128) unsigned char smem[];
-  constexpr int kABytes = A_KMAJOR ? kPadBytes64 : kMatBytes64;
-  constexpr int kBBytes = B_KMAJOR ? kPadBytes64 : kMatBytes64;
-  constexpr int kStageBytes = kABytes + kBBytes + (HAS_C ? kMatBytes64 : 0);
-  constexpr uint32_t kTxBytes = (uint32_t)(2 + (HAS_C ? 1 : 0)) * kMatBytes64;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)stages * kStageBytes);
-  uint64_t* empty_bar = full_bar + stages;
+                        const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b) {
+  extern __shared__ unsigned char smem_raw[];
+  // the 128-byte swizzle is a function of the shared-memory address: slots must be 1024-byte aligned
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)kSlots64 * kSlotBytes64);
+  uint64_t* empty_bar = full_bar + kSlots64;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) {
+    for (int s = 0; s < kSlots64; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 2);  // one arrival per warp of the pair
     }
@@ -296,87 +334,130 @@ __global__ void __launch_bounds__(kThreads64, 1)
   const int my_items = (batch > (int)blockIdx.x) ? (batch - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
   if (warp == 0) {
-    for (int j = 0; j < my_items; ++j) {
-      const int s = j % stages;
-      const uint32_t round = (uint32_t)(j / stages);
-      if (!mbar_wait(&empty_bar[s], (round & 1u) ^ 1u, kWaitEmpty)) return;
-      const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
-      unsigned char* st = smem + (size_t)s * kStageBytes;
-      if (lane == 0) mbar_arrive_expect_tx(&full_bar[s], kTxBytes);
-      __syncwarp();
-      const float* Ai = A + item * sa;
-      const float* Bi = B + item * sb;
-      if (A_KMAJOR) {
-        for (int r = lane; r < 64; r += 32) bulk_g2s(st + r * kPitch64, Ai + r * 64, 256, &full_bar[s]);
-      } else if (lane == 0) {
-        bulk_g2s(st, Ai, kMatBytes64, &full_bar[s]);
+    if (lane < kSlots64) {
+      const int pair = lane / kSlotsPerPair64, i = lane % kSlotsPerPair64;
+      // items of this pair: pair, pair + 4, ...
+      const int pair_items = (my_items > pair) ? (my_items - 1 - pair) / kPairs64 + 1 : 0;
+      unsigned char* st = smem + (size_t)lane * kSlotBytes64;
+      uint32_t round = 0;
+      for (int q = i; q < 2 * pair_items; q += kSlotsPerPair64, ++round) {
+        if (!mbar_wait(&empty_bar[lane], (round & 1u) ^ 1u, kWaitEmpty)) return;
+        const int j = pair + (q >> 1) * kPairs64, half = q & 1;
+        const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
+        mbar_arrive_expect_tx(&full_bar[lane], kSlotBytes64);
+        if (A_KMAJOR) tma_load_3d(st, &map_a, 32 * half, 0, (int)item, &full_bar[lane]);
+        else bulk_g2s(st, A + item * sa + half * (kMatElems64 / 2), kHalfBytes64, &full_bar[lane]);
+        if (B_KMAJOR) tma_load_3d(st + kHalfBytes64, &map_b, 32 * half, 0, (int)item, &full_bar[lane]);
+        else bulk_g2s(st + kHalfBytes64, B + item * sb + half * (kMatElems64 / 2), kHalfBytes64, &full_bar[lane]);
       }
-      if (B_KMAJOR) {
-        for (int r = lane; r < 64; r += 32) bulk_g2s(st + kABytes + r * kPitch64, Bi + r * 64, 256, &full_bar[s]);
-      } else if (lane == 0) {
-        bulk_g2s(st + kABytes, Bi, kMatBytes64, &full_bar[s]);
-      }
-      if (HAS_C && lane == 0) bulk_g2s(st + kABytes + kBBytes, C + item * sc, kMatBytes64, &full_bar[s]);
     }
     return;
   }
 
   const int pair = (warp - 1) >> 1, hw = (warp - 1) & 1;
   const int ti = lane & 7, tj = lane >> 3;
+  int slot_i = 0;      // q % 3
+  uint32_t round = 0;  // q / 3
   for (int j = pair; j < my_items; j += kPairs64) {
-    const int s = j % stages;
-    const uint32_t round = (uint32_t)(j / stages);
-    if (!mbar_wait(&full_bar[s], round & 1u, kWaitFull)) return;
-    const unsigned char* st = smem + (size_t)s * kStageBytes;
-
     float acc[8][8];
 #pragma unroll
     for (int r = 0; r < 8; ++r)
 #pragma unroll
       for (int c = 0; c < 8; ++c) acc[r][c] = 0.f;
-    mma64<A_KMAJOR, B_KMAJOR>(st, st + kABytes, ti, tj, hw, acc);
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half) {
+      const int s = pair * kSlotsPerPair64 + slot_i;
+      if (!mbar_wait(&full_bar[s], round & 1u, kWaitFull)) return;
+      const unsigned char* st = smem + (size_t)s * kSlotBytes64;
+      mma64_half<A_KMAJOR, B_KMAJOR>(st, st + kHalfBytes64, ti, tj, hw, acc);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
+      if (++slot_i == kSlotsPerPair64) {
+        slot_i = 0;
+        ++round;
+      }
+    }
 
     const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
     float* Cg = C + item * sc;
-    const float* Cs = reinterpret_cast<const float*>(st + kABytes + kBBytes);
-    // alpha*acc (+ beta*prior from shared memory) in place, then release the stage, then store.
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      const int col = B_KMAJOR ? (32 * hw + tj + 4 * c) : (32 * hw + 8 * tj + c);
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const int row = A_KMAJOR ? (ti + 8 * r) : ((r < 4 ? 0 : 32) + 4 * ti + (r & 3));
-        float o = alpha * acc[r][c];
-        if (HAS_C) o = fmaf(beta, Cs[col * 64 + row], o);
-        acc[r][c] = o;
-      }
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty_bar[s]);
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
       const int col = B_KMAJOR ? (32 * hw + tj + 4 * c) : (32 * hw + 8 * tj + c);
       if (A_KMAJOR) {
 #pragma unroll
-        for (int r = 0; r < 8; ++r) Cg[col * 64 + ti + 8 * r] = acc[r][c];
+        for (int r = 0; r < 8; ++r) {
+          float* dst = Cg + col * 64 + ti + 8 * r;
+          float o = alpha * acc[r][c];
+          if (HAS_C) o = fmaf(beta, *dst, o);
+          *dst = o;
+        }
       } else {
         float4* dst = reinterpret_cast<float4*>(Cg + col * 64);
-        dst[ti] = make_float4(acc[0][c], acc[1][c], acc[2][c], acc[3][c]);
-        dst[8 + ti] = make_float4(acc[4][c], acc[5][c], acc[6][c], acc[7][c]);
+#pragma unroll
+        for (int hgh = 0; hgh < 2; ++hgh) {
+          float4 o = make_float4(alpha * acc[4 * hgh][c], alpha * acc[4 * hgh + 1][c], alpha * acc[4 * hgh + 2][c],
+                                 alpha * acc[4 * hgh + 3][c]);
+          if (HAS_C) {
+            const float4 pr = dst[8 * hgh + ti];
+            o.x = fmaf(beta, pr.x, o.x);
+            o.y = fmaf(beta, pr.y, o.y);
+            o.z = fmaf(beta, pr.z, o.z);
+            o.w = fmaf(beta, pr.w, o.w);
+          }
+          dst[8 * hgh + ti] = o;
+        }
       }
     }
   }
 }
 
+// cuTensorMapEncodeTiled, resolved from the driver at run time (no link-time libcuda dependency).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return (EncodeTiledFn)p;
+  }();
+  return fn;
+}
+
+// 3-D map over `batch` K-major 64 x 64 float matrices: dims (k, row, item), box 32 x 64 x 1,
+// 128-byte swizzle.
+int make_kmajor_map64(CUtensorMap* map, const float* base, long long stride_elems, int batch) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return BLB200_E_INTERNAL;
+  const cuuint64_t dims[3] = {64, 64, (cuuint64_t)(batch > 0 ? batch : 1)};
+  const cuuint64_t strides[2] = {64 * sizeof(float), (cuuint64_t)stride_elems * sizeof(float)};
+  const cuuint32_t box[3] = {32, 64, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? BLB200_OK : BLB200_E_INTERNAL;
+}
+
 template <bool AK, bool BK, bool HC>
 int launch64(const GemmParams& p, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
-  constexpr int kStageBytes = (AK ? kPadBytes64 : kMatBytes64) + (BK ? kPadBytes64 : kMatBytes64) + (HC ? kMatBytes64 : 0);
-  const size_t budget = dev.smem_optin > 8192 ? dev.smem_optin - 4096 : 0;
-  int stages = (int)(budget / (size_t)kStageBytes);
-  if (stages > 8) stages = 8;
-  if (stages < 2) return BLB200_E_UNSUPPORTED;
-  const size_t smem = (size_t)stages * kStageBytes + (size_t)stages * 2 * sizeof(uint64_t);
+  const size_t smem = (size_t)kSlots64 * kSlotBytes64 + (size_t)kSlots64 * 2 * sizeof(uint64_t) + 1024;
+  if (dev.smem_optin < smem) return BLB200_E_UNSUPPORTED;
+  alignas(64) CUtensorMap map_a, map_b;
+  memset(&map_a, 0, sizeof(map_a));
+  memset(&map_b, 0, sizeof(map_b));
+  if (AK) {
+    int rc = make_kmajor_map64(&map_a, (const float*)p.a, p.batch > 1 ? p.sa : kMatElems64, p.batch);
+    if (rc != BLB200_OK) return rc;
+  }
+  if (BK) {
+    int rc = make_kmajor_map64(&map_b, (const float*)p.b, p.batch > 1 ? p.sb : kMatElems64, p.batch);
+    if (rc != BLB200_OK) return rc;
+  }
   auto kern = gemm_small64_kernel<AK, BK, HC>;
   static thread_local int configured_for = -1;
   int cur = 0;
@@ -388,11 +469,9 @@ int launch64(const GemmParams& p, cudaStream_t stream) {
   }
   const int grid = p.batch < dev.sm_count ? p.batch : dev.sm_count;
   kern<<<grid, kThreads64, smem, stream>>>((const float*)p.a, (const float*)p.b, (float*)p.c, p.sa, p.sb, p.sc,
-                                           p.batch, (float)p.alpha[0], (float)p.beta[0], stages);
+                                           p.batch, (float)p.alpha[0], (float)p.beta[0], map_a, map_b);
   return (int)cudaGetLastError();
 }
-
-inline bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
 
 }  // namespace
 
@@ -427,9 +506,11 @@ bool small64_supported(const GemmParams& p, int dtype) {
   if (p.m != 64 || p.n != 64 || p.k != 64) return false;
   if (p.lda != 64 || p.ldb != 64 || p.ldc != 64) return false;
   if ((p.sa & 3) || (p.sb & 3) || (p.sc & 3)) return false;
-  if (p.batch > 1 && p.sc < 4096) return false;
+  if (p.batch > 1 && p.sc < kMatElems64) return false;
+  // a tensor map needs a positive item stride; a broadcast operand (stride 0) takes the tiled path
+  if (p.batch > 1 && (p.sa < kMatElems64 || p.sb < kMatElems64)) return false;
   if (!aligned16(p.a) || !aligned16(p.b) || !aligned16(p.c)) return false;
-  return true;
+  return encode_tiled_fn() != nullptr;
 }
 
 int launch_small64(const GemmParams& p, int dtype, cudaStream_t stream) {

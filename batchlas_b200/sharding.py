@@ -17,3 +17,28 @@ def shard_range(batch: int, rank: int, world: int) -> tuple[int, int]:
     b0 = (batch * rank) // world
     b1 = (batch * (rank + 1)) // world
     return b0, b1 - b0
+
+
+def shard_desc(desc, rank: int, world: int, elem_bytes: int):
+    """Copy of a GemmDesc restricted to `rank`'s contiguous batch range: base pointers advance by
+    b0*stride elements, ld/stride are unchanged, batch becomes the shard's item count."""
+    import ctypes
+    b0, nb = shard_range(desc.batch, rank, world)
+    sub = type(desc)()
+    ctypes.memmove(ctypes.byref(sub), ctypes.byref(desc), ctypes.sizeof(desc))
+    sub.a = (desc.a or 0) + b0 * desc.stride_a * elem_bytes
+    sub.b = (desc.b or 0) + b0 * desc.stride_b * elem_bytes
+    sub.c = (desc.c or 0) + b0 * desc.stride_c * elem_bytes
+    sub.batch = nb
+    return sub
+
+
+def max_over_ranks(value: float, device=None) -> float:
+    """Slowest rank's value (the time that bounds a sharded step); identity without a process group."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return float(value)
+    t = torch.tensor([float(value)], dtype=torch.float64, device=device or "cpu")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())

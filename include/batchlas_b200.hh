@@ -1,0 +1,505 @@
+// batchlas_b200.hh — C++ host side of the B200 batched-GEMM path, header-only over the C ABI in
+// blb200.h and the CUDA runtime.
+//
+// It keeps the spelling of BatchLAS's public surface for this one path, so code written as
+//
+//     Queue ctx(Device::default_device());
+//     Matrix<float> A = ..., B = ..., C = ...;
+//     gemm(ctx, A.view(), B.view(), C.view(), {.alpha = 2.0f, .transA = Transpose::Trans});
+//     ctx.wait();
+//
+// compiles and runs unchanged.  Types mirrored (dense subset only), with the reference location of
+// the interface each one replaces:
+//   Device, Event, Queue           BatchLAS include/util/sycl-device-queue.hh:70-233 (global namespace
+//                                  there too); a Queue is one in-order cudaStream_t on one device.
+//   batchlas::WorkspaceLease       include/util/workspace.hh:70-162, arena src/queue.hh:41-226.
+//   batchlas::Transpose/Backend/ComputePrecision/MatrixFormat   include/blas/enums.hh:37-82,269-276.
+//   batchlas::Slice, MatrixView, Matrix    include/blas/matrix.hh:33-41,327-665,669-1196.
+//   batchlas::GemmOptions, gemm(...)       include/blas/options.hh:39-46,210-222 and
+//                                          include/blas/functions/gemm.hh:22-88.
+//   batchlas::with_backend         include/blas/queue-dispatch.hh:29-57 (single CUDA arm here).
+// Matrix storage is CUDA managed memory — host-visible like the reference's shared USM
+// (src/util/sycl-util-impl.cc:36-46) — so tests can index elements on the host after ctx.wait().
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <complex>
+#include <cstddef>
+#include <cstdint>
+#include <limits>
+#include <memory>
+#include <random>
+#include <stdexcept>
+#include <string>
+#include <type_traits>
+#include <utility>
+#include <vector>
+
+#include "blb200.h"
+
+#define BATCHLAS_HAS_CUDA_BACKEND 1
+#define BATCHLAS_HAS_ROCM_BACKEND 0
+#define BATCHLAS_HAS_MKL_BACKEND 0
+#define BATCHLAS_HAS_HOST_BACKEND 0
+
+namespace batchlas {
+
+enum class MatrixFormat { Dense, CSR, CSC, COO, SELL, BSR, BLOCKED_ELL };
+enum class Backend { AUTO, CUDA, ROCM, MKL, MAGMA, SYCL, NETLIB };
+enum class Transpose { NoTrans, Trans, ConjTrans };
+enum class ComputePrecision { Default, F32, F64, F16, BF16, TF32 };
+
+template <typename T>
+struct base_type { using type = T; };
+template <typename T>
+struct base_type<std::complex<T>> { using type = T; };
+template <typename T>
+using float_t = typename base_type<T>::type;
+
+class WorkspaceLease;
+
+namespace detail {
+inline void cuda_check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+inline void status_check(int status) {
+  if (status != BLB200_OK) throw std::runtime_error(blb200_status_string(status));
+}
+template <typename T>
+constexpr int dtype_code() {
+  if constexpr (std::is_same_v<T, float>) return BLB200_S;
+  else if constexpr (std::is_same_v<T, double>) return BLB200_D;
+  else if constexpr (std::is_same_v<T, std::complex<float>>) return BLB200_C;
+  else {
+    static_assert(std::is_same_v<T, std::complex<double>>, "gemm supports float, double and their complex types");
+    return BLB200_Z;
+  }
+}
+}  // namespace detail
+}  // namespace batchlas
+
+// ---- Device / Event / Queue (global namespace, as in the reference) ------------------------------
+enum class DeviceType { CPU, GPU, ACCELERATOR, HOST };
+
+struct Device {
+  static std::vector<Device> get_devices(DeviceType type) {
+    std::vector<Device> out;
+    if (type != DeviceType::GPU) return out;  // this build drives CUDA GPUs only
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) n = 0;
+    for (int i = 0; i < n; ++i) out.emplace_back((size_t)i, DeviceType::GPU);
+    return out;
+  }
+  Device() = default;
+  Device(size_t idx, DeviceType type) : idx(idx), type(type) {}
+  Device(std::string name) {
+    std::transform(name.begin(), name.end(), name.begin(), ::tolower);
+    if (name != "gpu") throw std::runtime_error(name == "cpu" || name == "accelerator" ? "No " + name + " device available"
+                                                                                        : "Invalid device type: " + name);
+    auto devs = get_devices(DeviceType::GPU);
+    if (devs.empty()) throw std::runtime_error("No gpu device available");
+    *this = devs.at(0);
+  }
+  Device(const char* name) : Device(std::string(name)) {}
+  static Device default_device() {
+    auto devs = get_devices(DeviceType::GPU);
+    if (devs.empty()) throw std::runtime_error("No gpu device available");
+    return devs.at(0);
+  }
+  std::string get_name() const {
+    cudaDeviceProp prop;
+    batchlas::detail::cuda_check(cudaGetDeviceProperties(&prop, (int)idx), "cudaGetDeviceProperties");
+    return prop.name;
+  }
+  size_t idx = 0;
+  DeviceType type = DeviceType::GPU;
+};
+
+struct Event {
+  Event() = default;
+  explicit Event(std::shared_ptr<CUevent_st> ev) : ev_(std::move(ev)) {}
+  void wait() const {
+    if (ev_) batchlas::detail::cuda_check(cudaEventSynchronize(ev_.get()), "Event::wait");
+  }
+  cudaEvent_t native() const { return ev_.get(); }
+
+ private:
+  std::shared_ptr<CUevent_st> ev_;
+};
+
+struct Queue {
+  Queue() : Queue(Device::default_device()) {}
+  Queue(Device device, bool in_order = true) : Queue(device, batchlas::Backend::AUTO, in_order) {}
+  Queue(Device device, batchlas::Backend backend, bool in_order = true) : device_(device), in_order_(in_order) {
+    if (device.type != DeviceType::GPU) throw std::runtime_error("Queue: only GPU devices are available in this build");
+    set_backend(backend);
+    make_current();
+    batchlas::detail::cuda_check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
+    batchlas::detail::status_check(blb200_arena_create((int)device.idx, stream_, &arena_));
+  }
+  // A further queue on the same device (the reference shares the SYCL context; CUDA's primary
+  // context is shared by construction).
+  Queue(const Queue& base, bool in_order) : Queue(base.device_, base.backend_, in_order) {}
+  Queue(const Queue&) = delete;
+  Queue& operator=(const Queue&) = delete;
+  Queue(Queue&& o) noexcept { steal(o); }
+  Queue& operator=(Queue&& o) noexcept {
+    if (this != &o) {
+      destroy();
+      steal(o);
+    }
+    return *this;
+  }
+  ~Queue() { destroy(); }
+
+  void make_current() const { batchlas::detail::cuda_check(cudaSetDevice((int)device_.idx), "cudaSetDevice"); }
+  cudaStream_t native_stream() const { return stream_; }
+
+  void wait() const {
+    make_current();
+    batchlas::detail::cuda_check(cudaStreamSynchronize(stream_), "Queue::wait");
+  }
+  void wait_and_throw() const { wait(); }
+  Event get_event() const { return record(); }
+  // The launcher enqueues on this queue's own stream, so "after external work" is simply "now".
+  Event create_event_after_external_work() { return record(); }
+  void enqueue(Event& ev) {
+    if (ev.native()) batchlas::detail::cuda_check(cudaStreamWaitEvent(stream_, ev.native(), 0), "cudaStreamWaitEvent");
+  }
+
+  [[nodiscard]] inline batchlas::WorkspaceLease workspace(size_t bytes);
+  size_t workspace_capacity() const { return blb200_arena_capacity(arena_); }
+  [[nodiscard]] bool trim_workspace() {
+    int rc = blb200_arena_trim(arena_);
+    if (rc < 0) batchlas::detail::status_check(rc);
+    return rc == 1;
+  }
+
+  Device device() const { return device_; }
+  bool in_order() const { return in_order_; }
+  batchlas::Backend backend() const { return batchlas::Backend::CUDA; }  // AUTO resolves to the only arm
+  batchlas::Backend requested_backend() const { return backend_; }
+  void set_backend(batchlas::Backend b) {
+    if (!backend_available(b)) throw std::runtime_error("Queue::set_backend: backend not compiled into this build");
+    backend_ = b;
+  }
+  static bool backend_available(batchlas::Backend b) {
+    return b == batchlas::Backend::AUTO || b == batchlas::Backend::CUDA;
+  }
+  blb200_arena* arena() const { return arena_; }
+
+ private:
+  Event record() const {
+    make_current();
+    cudaEvent_t ev = nullptr;
+    batchlas::detail::cuda_check(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreate");
+    std::shared_ptr<CUevent_st> sp(ev, [](cudaEvent_t e) { cudaEventDestroy(e); });
+    batchlas::detail::cuda_check(cudaEventRecord(ev, stream_), "cudaEventRecord");
+    return Event(sp);
+  }
+  void steal(Queue& o) {
+    device_ = o.device_;
+    in_order_ = o.in_order_;
+    backend_ = o.backend_;
+    stream_ = o.stream_;
+    arena_ = o.arena_;
+    o.stream_ = nullptr;
+    o.arena_ = nullptr;
+  }
+  void destroy() noexcept {
+    if (!stream_ && !arena_) return;
+    cudaSetDevice((int)device_.idx);
+    if (stream_) cudaStreamSynchronize(stream_);  // enqueued kernels may still read arena blocks
+    if (arena_) blb200_arena_destroy(arena_);
+    if (stream_) cudaStreamDestroy(stream_);
+    stream_ = nullptr;
+    arena_ = nullptr;
+  }
+  Device device_;
+  bool in_order_ = true;
+  batchlas::Backend backend_ = batchlas::Backend::AUTO;
+  cudaStream_t stream_ = nullptr;
+  blb200_arena* arena_ = nullptr;
+};
+
+namespace batchlas {
+
+// Scoped borrow of device scratch from a Queue's arena; move-only, releases on destruction.
+class WorkspaceLease {
+ public:
+  WorkspaceLease() = default;
+  WorkspaceLease(const WorkspaceLease&) = delete;
+  WorkspaceLease& operator=(const WorkspaceLease&) = delete;
+  WorkspaceLease(WorkspaceLease&& o) noexcept : arena_(o.arena_), lease_(o.lease_) { o.arena_ = nullptr; o.lease_ = {}; }
+  WorkspaceLease& operator=(WorkspaceLease&& o) noexcept {
+    if (this != &o) {
+      release();  // necessarily out of order: `o` was acquired before this one is returned
+      arena_ = o.arena_;
+      lease_ = o.lease_;
+      o.arena_ = nullptr;
+      o.lease_ = {};
+    }
+    return *this;
+  }
+  ~WorkspaceLease() { release(); }
+  std::byte* data() const { return static_cast<std::byte*>(lease_.ptr); }
+  std::size_t size() const { return lease_.bytes; }
+  void release() noexcept {
+    if (arena_ && lease_.seq) blb200_arena_release(arena_, &lease_);
+    arena_ = nullptr;
+    lease_ = {};
+  }
+
+ private:
+  friend struct ::Queue;
+  WorkspaceLease(blb200_arena* a, const blb200_lease& l) : arena_(a), lease_(l) {}
+  blb200_arena* arena_ = nullptr;
+  blb200_lease lease_{};
+};
+
+struct SliceEnd {};
+struct Slice {  // default selects everything
+  int64_t start = std::numeric_limits<int64_t>::min();
+  int64_t end = std::numeric_limits<int64_t>::max();
+  Slice() = default;
+  Slice(int64_t s, SliceEnd) : start(s) {}
+  Slice(int64_t s, int64_t e) : start(s), end(e) {}
+  Slice(int64_t s) : start(s) {}
+};
+
+namespace detail {
+inline std::pair<int64_t, int64_t> normalize_slice(Slice s, int64_t extent) {
+  int64_t b = s.start == std::numeric_limits<int64_t>::min() ? 0 : (s.start < 0 ? s.start + extent : s.start);
+  int64_t e = s.end == std::numeric_limits<int64_t>::max() ? extent : (s.end < 0 ? s.end + extent : s.end);
+  b = std::clamp<int64_t>(b, 0, extent);
+  e = std::clamp<int64_t>(e, 0, extent);
+  return {b, e - b};
+}
+}  // namespace detail
+
+// Non-owning column-major view: element (i, j) of item b is data[b*stride + j*ld + i].
+template <typename T, MatrixFormat MType = MatrixFormat::Dense>
+class MatrixView {
+  static_assert(MType == MatrixFormat::Dense, "only dense views are on this path");
+
+ public:
+  MatrixView() = default;
+  MatrixView(T* data, int rows, int cols, int ld = 0, int64_t stride = 0, int batch_size = 1)
+      : data_(data), rows_(rows), cols_(cols), ld_(ld > 0 ? ld : rows),
+        stride_(stride > 0 ? stride : (int64_t)(ld > 0 ? ld : rows) * cols), batch_size_(batch_size) {}
+  T* data_ptr() const { return data_; }
+  int rows() const { return rows_; }
+  int cols() const { return cols_; }
+  int ld() const { return ld_; }
+  int64_t stride() const { return stride_; }
+  int batch_size() const { return batch_size_; }
+  T& at(int row, int col, int batch = 0) const { return data_[(int64_t)batch * stride_ + (int64_t)col * ld_ + row]; }
+  T& operator()(int row, int col, int batch = 0) const { return at(row, col, batch); }
+  MatrixView batch_item(int b) const {
+    if (b < 0 || b >= batch_size_) throw std::out_of_range("Batch index out of range");
+    return MatrixView(data_ + (int64_t)b * stride_, rows_, cols_, ld_);
+  }
+  MatrixView operator[](int b) const { return batch_item(b); }
+  MatrixView operator()(Slice rows, Slice cols) const {
+    auto [r0, rl] = detail::normalize_slice(rows, rows_);
+    auto [c0, cl] = detail::normalize_slice(cols, cols_);
+    if (rl <= 0 || cl <= 0)
+      throw std::invalid_argument("Invalid slice dimensions: " + std::to_string(rl) + "x" + std::to_string(cl));
+    return MatrixView(data_ + c0 * ld_ + r0, (int)rl, (int)cl, ld_, stride_, batch_size_);
+  }
+  MatrixView operator()(Slice rows) const { return (*this)(rows, {}); }
+
+ private:
+  T* data_ = nullptr;
+  int rows_ = 0, cols_ = 0, ld_ = 0;
+  int64_t stride_ = 0;
+  int batch_size_ = 1;
+};
+
+// Owning batch of column-major matrices in managed (host-visible) memory.
+template <typename T, MatrixFormat MType = MatrixFormat::Dense>
+class Matrix {
+  static_assert(MType == MatrixFormat::Dense, "only dense matrices are on this path");
+
+ public:
+  Matrix() = default;
+  Matrix(int rows, int cols, int batch_size = 1, int ld = 0, int64_t stride = 0)
+      : rows_(rows), cols_(cols), batch_size_(batch_size), ld_(ld > 0 ? ld : rows),
+        stride_(stride > 0 ? stride : (int64_t)(ld > 0 ? ld : rows) * cols) {
+    const size_t n = std::max<size_t>(1, (size_t)stride_ * (size_t)batch_size_);
+    void* p = nullptr;
+    detail::cuda_check(cudaMallocManaged(&p, n * sizeof(T)), "Matrix: cudaMallocManaged");
+    data_.reset(static_cast<T*>(p), [](T* q) { cudaFree(q); });
+    count_ = n;
+  }
+  Matrix(const Matrix&) = delete;
+  Matrix& operator=(const Matrix&) = delete;
+  Matrix(Matrix&&) noexcept = default;
+  Matrix& operator=(Matrix&&) noexcept = default;
+
+  static Matrix Zeros(int rows, int cols, int batch_size = 1) {
+    Matrix m(rows, cols, batch_size);
+    m.fill(T(0));
+    return m;
+  }
+  static Matrix Identity(int n, int batch_size = 1) {
+    Matrix m = Zeros(n, n, batch_size);
+    for (int b = 0; b < batch_size; ++b)
+      for (int i = 0; i < n; ++i) m(i, i, b) = T(1);
+    return m;
+  }
+  // uniform[-1, 1]; the reference draws from a oneDPL minstd stream (src/matrix.cc:938-990) that
+  // cannot be reproduced without oneDPL, so only the distribution is kept.
+  static Matrix Random(int rows, int cols, bool hermitian = false, int batch_size = 1, unsigned seed = 42) {
+    Matrix m(rows, cols, batch_size);
+    std::mt19937_64 gen(seed);
+    std::uniform_real_distribution<double> dist(-1.0, 1.0);
+    for (int b = 0; b < batch_size; ++b)
+      for (int j = 0; j < cols; ++j)
+        for (int i = 0; i < rows; ++i) {
+          if constexpr (std::is_floating_point_v<T>) m(i, j, b) = (T)dist(gen);
+          else m(i, j, b) = T((float_t<T>)dist(gen), (float_t<T>)dist(gen));
+        }
+    if (hermitian && rows == cols)
+      for (int b = 0; b < batch_size; ++b)
+        for (int j = 0; j < cols; ++j)
+          for (int i = 0; i <= j; ++i) {
+            if constexpr (std::is_floating_point_v<T>) m(j, i, b) = m(i, j, b);
+            else {
+              if (i == j) m(i, i, b) = T(m(i, i, b).real(), 0);
+              m(j, i, b) = std::conj(m(i, j, b));
+            }
+          }
+    return m;
+  }
+
+  void fill(T v) { std::fill(data_.get(), data_.get() + count_, v); }
+  Matrix clone() const {
+    Matrix m(rows_, cols_, batch_size_, ld_, stride_);
+    std::copy(data_.get(), data_.get() + count_, m.data_.get());
+    return m;
+  }
+  MatrixView<T, MType> view() const { return MatrixView<T, MType>(data_.get(), rows_, cols_, ld_, stride_, batch_size_); }
+  operator MatrixView<T, MType>() const { return view(); }
+  T& operator()(int i, int j, int b = 0) const { return data_.get()[(int64_t)b * stride_ + (int64_t)j * ld_ + i]; }
+  T* data_ptr() const { return data_.get(); }
+  int rows() const { return rows_; }
+  int cols() const { return cols_; }
+  int ld() const { return ld_; }
+  int64_t stride() const { return stride_; }
+  int batch_size() const { return batch_size_; }
+
+ private:
+  std::shared_ptr<T> data_;
+  size_t count_ = 0;
+  int rows_ = 0, cols_ = 0, batch_size_ = 1, ld_ = 0;
+  int64_t stride_ = 0;
+};
+
+template <typename T, MatrixFormat M>
+inline std::pair<int, int> get_effective_dims(const MatrixView<T, M>& mat, Transpose trans) {
+  return trans == Transpose::NoTrans ? std::make_pair(mat.rows(), mat.cols()) : std::make_pair(mat.cols(), mat.rows());
+}
+
+template <typename T>
+struct GemmOptions {
+  T alpha = T(1);
+  T beta = T(0);
+  Transpose transA = Transpose::NoTrans;
+  Transpose transB = Transpose::NoTrans;
+  ComputePrecision precision = ComputePrecision::Default;
+};
+
+template <typename F>
+inline auto with_backend(Queue& ctx, F&& f) {
+  switch (ctx.backend()) {
+    case Backend::CUDA: return f(std::integral_constant<Backend, Backend::CUDA>{});
+    default: break;
+  }
+  throw std::runtime_error("BatchLAS: this Queue's backend has no implementation in this build. "
+                           "Check Queue::backend_available() before pinning a backend.");
+}
+
+// The seam: gemm<Backend::CUDA, T> (replaces BatchLAS src/backends/cublas.cc:1574-1585).
+template <Backend Back, typename T>
+Event gemm(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
+           const MatrixView<T, MatrixFormat::Dense>& C, T alpha, T beta, Transpose transA, Transpose transB,
+           ComputePrecision precision = ComputePrecision::Default) {
+  static_assert(Back == Backend::CUDA, "only the CUDA backend exists in this build");
+  constexpr bool is_f32 = std::is_same_v<float_t<T>, float>;
+  // Reduced-precision requests change results; only the storage precision is accepted.
+  if (!(precision == ComputePrecision::Default || (is_f32 && precision == ComputePrecision::F32) ||
+        (!is_f32 && precision == ComputePrecision::F64)))
+    throw std::runtime_error("GEMM: reduced compute precision is not available on this path");
+  auto [m, k] = get_effective_dims(A, transA);
+  auto [kb, n] = get_effective_dims(B, transB);
+  if (A.batch_size() != B.batch_size() || A.batch_size() != C.batch_size() || k != kb || C.rows() != m ||
+      C.cols() != n || m < 0 || n < 0 || k < 0)
+    throw std::runtime_error("GEMM: incompatible matrix dimensions");
+  blb200_gemm_desc d{};
+  d.a = A.data_ptr();
+  d.b = B.data_ptr();
+  d.c = C.data_ptr();
+  d.m = m; d.n = n; d.k = k; d.batch = A.batch_size();
+  d.lda = A.ld(); d.ldb = B.ld(); d.ldc = C.ld();
+  d.stride_a = A.stride(); d.stride_b = B.stride(); d.stride_c = C.stride();
+  if constexpr (std::is_floating_point_v<T>) {
+    d.alpha[0] = alpha; d.beta[0] = beta;
+  } else {
+    d.alpha[0] = alpha.real(); d.alpha[1] = alpha.imag();
+    d.beta[0] = beta.real(); d.beta[1] = beta.imag();
+  }
+  d.dtype = detail::dtype_code<T>();
+  d.op_a = (int)transA;
+  d.op_b = (int)transB;
+  ctx.make_current();
+  detail::status_check(blb200_gemm_strided_batched(&d, ctx.native_stream()));
+  return ctx.create_event_after_external_work();
+}
+
+template <Backend Back, typename T>
+inline Event gemm(Queue& ctx, const Matrix<T>& A, const Matrix<T>& B, const Matrix<T>& C, T alpha, T beta,
+                  Transpose transA, Transpose transB, ComputePrecision precision = ComputePrecision::Default) {
+  return gemm<Back, T>(ctx, A.view(), B.view(), C.view(), alpha, beta, transA, transB, precision);
+}
+
+// Backend-deducing positional overloads.
+template <typename T>
+inline Event gemm(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
+                  const MatrixView<T, MatrixFormat::Dense>& C, T alpha, T beta, Transpose transA, Transpose transB,
+                  ComputePrecision precision = ComputePrecision::Default) {
+  return with_backend(ctx, [&](auto Bk) { return gemm<Bk.value, T>(ctx, A, B, C, alpha, beta, transA, transB, precision); });
+}
+template <typename T>
+inline Event gemm(Queue& ctx, const Matrix<T>& A, const Matrix<T>& B, const Matrix<T>& C, T alpha, T beta,
+                  Transpose transA, Transpose transB, ComputePrecision precision = ComputePrecision::Default) {
+  return gemm<T>(ctx, A.view(), B.view(), C.view(), alpha, beta, transA, transB, precision);
+}
+
+// Option-struct spellings; T comes from the matrix arguments so `{.alpha = 2.0f}` binds.
+template <Backend Back, typename T>
+inline Event gemm(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
+                  const MatrixView<T, MatrixFormat::Dense>& C, const GemmOptions<std::type_identity_t<T>>& o) {
+  return gemm<Back, T>(ctx, A, B, C, o.alpha, o.beta, o.transA, o.transB, o.precision);
+}
+template <typename T>
+inline Event gemm(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
+                  const MatrixView<T, MatrixFormat::Dense>& C, const GemmOptions<std::type_identity_t<T>>& o = {}) {
+  return with_backend(ctx, [&](auto Bk) { return gemm<Bk.value, T>(ctx, A, B, C, o); });
+}
+template <typename T>
+inline Event gemm(Queue& ctx, const Matrix<T>& A, const Matrix<T>& B, const Matrix<T>& C,
+                  const GemmOptions<std::type_identity_t<T>>& o = {}) {
+  return gemm<T>(ctx, A.view(), B.view(), C.view(), o);
+}
+
+}  // namespace batchlas
+
+inline batchlas::WorkspaceLease Queue::workspace(size_t bytes) {
+  make_current();
+  blb200_lease l{};
+  batchlas::detail::status_check(blb200_arena_acquire(arena_, bytes, &l));
+  return batchlas::WorkspaceLease(arena_, l);
+}

@@ -1,0 +1,246 @@
+// C++ parity tests through the mirrored BatchLAS API (include/batchlas_b200.hh): the test bodies
+// follow the reference's own (BatchLAS tests/gemm_tests.cc, backend_dispatch_tests.cc,
+// options_api_tests.cc, mempool_tests.cc) with a naive host triple loop as the second
+// implementation, since there is no vendor backend to compare against here.
+// Build: g++ -std=c++20 -I include -I $CUDA/include tests/cpp/gemm_api_tests.cc -L batchlas_b200
+//        -lbatchlas_b200 -L $CUDA/lib64 -lcudart.   `--compile-only-check` exits before touching a GPU.
+#include <batchlas_b200.hh>
+
+#include <cmath>
+#include <complex>
+#include <cstdio>
+#include <cstring>
+#include <functional>
+#include <iostream>
+
+using namespace batchlas;
+
+static int g_failed = 0, g_run = 0;
+#define CHECK(cond)                                                                   \
+  do {                                                                                \
+    if (!(cond)) {                                                                    \
+      std::printf("  CHECK failed %s:%d: %s\n", __FILE__, __LINE__, #cond);           \
+      ++g_failed;                                                                     \
+      return;                                                                         \
+    }                                                                                 \
+  } while (0)
+
+template <typename T>
+constexpr double tolerance() {  // BatchLAS tests/test_utils.hh:230-240
+  using R = batchlas::float_t<T>;
+  double t = std::is_same_v<R, float> ? 1e-5 : 1e-10;
+  return std::is_same_v<T, R> ? t : 2 * t;
+}
+
+template <typename T>
+T op_elem(const Matrix<T>& M, Transpose t, int r, int c, int b) {
+  if (t == Transpose::NoTrans) return M(r, c, b);
+  T v = M(c, r, b);
+  if constexpr (!std::is_floating_point_v<T>) return t == Transpose::ConjTrans ? std::conj(v) : v;
+  else return v;
+}
+
+// C_ref = alpha*op(A)*op(B) + beta*C0, accumulated in the widest type available.
+template <typename T>
+double max_abs_diff(const Matrix<T>& A, const Matrix<T>& B, const Matrix<T>& C0, const Matrix<T>& C, T alpha, T beta,
+                    Transpose ta, Transpose tb, int m, int n, int k, int batch) {
+  using W = std::conditional_t<std::is_floating_point_v<T>, long double, std::complex<long double>>;
+  double worst = 0;
+  for (int b = 0; b < batch; ++b)
+    for (int j = 0; j < n; ++j)
+      for (int i = 0; i < m; ++i) {
+        W s = 0;
+        for (int l = 0; l < k; ++l) s += W(op_elem(A, ta, i, l, b)) * W(op_elem(B, tb, l, j, b));
+        W ref = W(alpha) * s;
+        if (beta != T(0)) ref += W(beta) * W(C0(i, j, b));
+        worst = std::max(worst, (double)std::abs(W(C(i, j, b)) - ref));
+      }
+  return worst;
+}
+
+template <typename T>
+void GemmWithIdentityMatrix(Queue& ctx) {  // gemm_tests.cc:355-374
+  const int rows = 10, cols = 10, ld = 10;
+  auto A = Matrix<T>::Random(rows, cols);
+  auto B = Matrix<T>::Identity(cols);
+  auto C = Matrix<T>::Zeros(rows, cols);
+  MatrixView<T, MatrixFormat::Dense> A_view(A.data_ptr(), rows, cols, ld);
+  MatrixView<T, MatrixFormat::Dense> B_view(B.data_ptr(), cols, cols, ld);
+  MatrixView<T, MatrixFormat::Dense> C_view(C.data_ptr(), rows, cols, ld);
+  gemm(ctx, A_view, B_view, C_view, {.alpha = T(1.0), .beta = T(0.0)});
+  ctx.wait();
+  for (int j = 0; j < cols; ++j)
+    for (int i = 0; i < rows; ++i) CHECK(std::abs(C(i, j) - A(i, j)) <= tolerance<T>());
+}
+
+template <typename T>
+void BatchedGemm(Queue& ctx) {  // gemm_tests.cc:377-396
+  const int n = 10, batch = 3;
+  auto A = Matrix<T>::Random(n, n, false, batch);
+  auto B = Matrix<T>::Identity(n, batch);
+  auto C = Matrix<T>::Zeros(n, n, batch);
+  gemm(ctx, A.view(), B.view(), C.view(), {.alpha = T(1.0), .beta = T(0.0)});
+  ctx.wait();
+  for (int b = 0; b < batch; ++b)
+    for (int j = 0; j < n; ++j)
+      for (int i = 0; i < n; ++i) CHECK(std::abs(C(i, j, b) - A(i, j, b)) <= tolerance<T>());
+}
+
+template <typename T>
+void GeneralCase(Queue& ctx, int m, int n, int k, int batch, Transpose ta, Transpose tb, T alpha, T beta, double tol_mult) {
+  auto A = ta == Transpose::NoTrans ? Matrix<T>::Random(m, k, false, batch) : Matrix<T>::Random(k, m, false, batch);
+  auto B = tb == Transpose::NoTrans ? Matrix<T>::Random(k, n, false, batch, 43) : Matrix<T>::Random(n, k, false, batch, 43);
+  auto C = Matrix<T>::Random(m, n, false, batch, 44);
+  auto C0 = C.clone();
+  gemm(ctx, A.view(), B.view(), C.view(), {.alpha = alpha, .beta = beta, .transA = ta, .transB = tb});
+  ctx.wait();
+  double worst = max_abs_diff(A, B, C0, C, alpha, beta, ta, tb, m, n, k, batch);
+  CHECK(worst <= tolerance<T>() * tol_mult);
+}
+
+template <typename T>
+void ReferenceShapes(Queue& ctx) {
+  GeneralCase<T>(ctx, 32, 32, 32, 4, Transpose::NoTrans, Transpose::NoTrans, T(1), T(0), 50);     // :674-739
+  GeneralCase<T>(ctx, 128, 128, 128, 2, Transpose::NoTrans, Transpose::NoTrans, T(1), T(1), 100);
+  GeneralCase<T>(ctx, 24, 20, 16, 3, Transpose::Trans, Transpose::Trans, T(1), T(0), 50);         // :1276-1351
+  GeneralCase<T>(ctx, 96, 80, 64, 1, Transpose::Trans, Transpose::Trans, T(1), T(0), 100);
+  GeneralCase<T>(ctx, 18, 14, 12, 2, Transpose::ConjTrans, Transpose::NoTrans, T(1), T(0), 50);   // :2035-2071
+  GeneralCase<T>(ctx, 200, 130, 70, 3, Transpose::NoTrans, Transpose::NoTrans, T(2), T(-1), 100); // :1995-2033
+}
+
+template <typename T>
+void DeducedBackendMatchesExplicit(Queue& ctx) {  // backend_dispatch_tests.cc:96-142
+  const int n = 16, batch = 2;
+  auto A = Matrix<T>::Random(n, n, false, batch);
+  auto B = Matrix<T>::Random(n, n, false, batch, 7);
+  auto C1 = Matrix<T>::Zeros(n, n, batch);
+  auto C2 = Matrix<T>::Zeros(n, n, batch);
+  gemm(ctx, A.view(), B.view(), C1.view(), T(1), T(0), Transpose::NoTrans, Transpose::NoTrans);
+  gemm<Backend::CUDA>(ctx, A.view(), B.view(), C2.view(), T(1), T(0), Transpose::NoTrans, Transpose::NoTrans);
+  ctx.wait();
+  for (int b = 0; b < batch; ++b)
+    for (int j = 0; j < n; ++j)
+      for (int i = 0; i < n; ++i) CHECK(C1(i, j, b) == C2(i, j, b));
+  // owning-Matrix overloads (:176-194) and defaulted ComputePrecision (:198-219)
+  auto C3 = Matrix<T>::Zeros(n, n, batch);
+  gemm(ctx, A, B, C3, T(1), T(0), Transpose::NoTrans, Transpose::NoTrans);
+  ctx.wait();
+  CHECK(C3(3, 5, 1) == C1(3, 5, 1));
+}
+
+void OptionDefaultsAndErrors(Queue& ctx) {  // options_api_tests.cc:148-183
+  GemmOptions<float> o;
+  CHECK(o.alpha == 1.0f && o.beta == 0.0f && o.transA == Transpose::NoTrans && o.transB == Transpose::NoTrans &&
+        o.precision == ComputePrecision::Default);
+  auto A = Matrix<float>::Random(8, 8), B = Matrix<float>::Random(8, 8), C = Matrix<float>::Zeros(8, 8);
+  auto C2 = Matrix<float>::Zeros(8, 8);
+  gemm(ctx, A, B, C);  // all defaults
+  gemm(ctx, A.view(), B.view(), C2.view(), {.alpha = 1.0f});
+  ctx.wait();
+  CHECK(C(2, 3) == C2(2, 3));
+  auto Bad = Matrix<float>::Random(7, 8);
+  bool threw = false;
+  try {
+    gemm(ctx, A.view(), Bad.view(), C.view(), {});
+  } catch (const std::runtime_error& e) {
+    threw = std::string(e.what()) == "GEMM: incompatible matrix dimensions";  // cublas.cc:119-121
+  }
+  CHECK(threw);
+  threw = false;
+  try {
+    gemm(ctx, A.view(), B.view(), C.view(), {.precision = ComputePrecision::TF32});
+  } catch (const std::runtime_error&) {
+    threw = true;
+  }
+  CHECK(threw);
+  threw = false;
+  try {
+    ctx.set_backend(Backend::NETLIB);
+  } catch (const std::runtime_error&) {
+    threw = true;
+  }
+  CHECK(threw && ctx.backend() == Backend::CUDA && Queue::backend_available(Backend::CUDA) &&
+        !Queue::backend_available(Backend::ROCM));
+}
+
+void SlicedViews(Queue& ctx) {  // slices offset the base pointer: matrix.hh:855-869
+  auto A = Matrix<double>::Random(40, 40, false, 2), B = Matrix<double>::Random(40, 40, false, 2, 5);
+  auto C = Matrix<double>::Zeros(40, 40, 2);
+  auto As = A.view()({3, 35}, {1, 20}), Bs = B.view()({0, 19}, {7, 30}), Cs = C.view()({5, 37}, {2, 25});
+  CHECK(As.rows() == 32 && As.cols() == 19 && Bs.rows() == 19 && Bs.cols() == 23 && Cs.ld() == 40);
+  gemm(ctx, As, Bs, Cs, {.alpha = 1.0});
+  ctx.wait();
+  double worst = 0;
+  for (int b = 0; b < 2; ++b)
+    for (int j = 0; j < 23; ++j)
+      for (int i = 0; i < 32; ++i) {
+        long double s = 0;
+        for (int l = 0; l < 19; ++l) s += (long double)A(3 + i, 1 + l, b) * B(l, 7 + j, b);
+        worst = std::max(worst, (double)std::abs(s - C(5 + i, 2 + j, b)));
+      }
+  CHECK(worst < 1e-12);
+  CHECK(C(0, 0, 0) == 0.0 && C(39, 39, 1) == 0.0 && C(4, 2, 0) == 0.0 && C(37, 2, 0) == 0.0);  // outside the slice
+}
+
+void WorkspaceLeases(Queue& ctx) {  // mempool_tests.cc:829-1078
+  {
+    auto a = ctx.workspace(1000);
+    CHECK(a.data() != nullptr && a.size() == 1000 && (reinterpret_cast<uintptr_t>(a.data()) % 256) == 0);
+  }
+  size_t cap = ctx.workspace_capacity();
+  std::byte* first = nullptr;
+  for (int i = 0; i < 20; ++i) {
+    auto a = ctx.workspace(1000);
+    if (!first) first = a.data();
+    CHECK(a.data() == first);
+  }
+  CHECK(ctx.workspace_capacity() == cap);  // repeated calls do not grow the arena
+  {
+    auto outer = ctx.workspace(4096);
+    auto inner = ctx.workspace(8 << 20);
+    CHECK(inner.data() + inner.size() <= outer.data() || inner.data() >= outer.data() + outer.size());
+    CHECK(!ctx.trim_workspace());  // refuses while leased
+    outer.release();               // early, out of order: only marked
+    auto third = ctx.workspace(4096);
+    CHECK(third.data() != first);
+  }
+  auto ws = ctx.workspace(100);
+  ws = ctx.workspace(200);  // reassignment defers reclaim, never aliases
+  CHECK(ws.size() == 200);
+  ws.release();
+  CHECK(ctx.trim_workspace() && ctx.workspace_capacity() == 0);
+}
+
+int main(int argc, char** argv) {
+  if (argc > 1 && std::strcmp(argv[1], "--compile-only-check") == 0) {
+    std::puts("compiled: overload set resolves");
+    return 0;
+  }
+  Queue ctx(Device::default_device());
+  std::printf("device: %s\n", ctx.device().get_name().c_str());
+  auto run = [&](const char* name, std::function<void()> f) {
+    int before = g_failed;
+    ++g_run;
+    try {
+      f();
+    } catch (const std::exception& e) {
+      std::printf("  exception: %s\n", e.what());
+      ++g_failed;
+    }
+    std::printf("[%s] %s\n", g_failed == before ? " OK " : "FAIL", name);
+  };
+#define FOR_TYPES(fn)                                                       \
+  run(#fn "<float>", [&] { fn<float>(ctx); });                              \
+  run(#fn "<double>", [&] { fn<double>(ctx); });                            \
+  run(#fn "<complex<float>>", [&] { fn<std::complex<float>>(ctx); });       \
+  run(#fn "<complex<double>>", [&] { fn<std::complex<double>>(ctx); });
+  FOR_TYPES(GemmWithIdentityMatrix)
+  FOR_TYPES(BatchedGemm)
+  FOR_TYPES(ReferenceShapes)
+  FOR_TYPES(DeducedBackendMatchesExplicit)
+  run("OptionDefaultsAndErrors", [&] { OptionDefaultsAndErrors(ctx); });
+  run("SlicedViews", [&] { SlicedViews(ctx); });
+  run("WorkspaceLeases", [&] { WorkspaceLeases(ctx); });
+  std::printf("%d test groups, %d failed\n", g_run, g_failed);
+  return g_failed ? 1 : 0;
+}

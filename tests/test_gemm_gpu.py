@@ -120,6 +120,24 @@ def test_unaligned_views_take_a_safe_path(bl, dt):
         assert_parity(p, A, B, C0, C, what=f"offset view via {kern}")
 
 
+@pytest.mark.parametrize("size", [32, 64])
+@pytest.mark.parametrize("oa", ["N", "T"])
+@pytest.mark.parametrize("ob", ["N", "T"])
+def test_small_kernel_rings_over_many_items(bl, size, oa, ob):
+    """Batch sizes around the SM count and far beyond it walk every ring slot through many rounds;
+    a sample of items is checked against the oracle and every item against the generic kernel."""
+    rng = np.random.default_rng(size)
+    for batch, beta in [(1, 0.0), (7, -0.5), (147, 0.0), (149, 1.0), (1000, -0.5), (5003, 0.0)]:
+        p = oracle.make_problem("s", oa, ob, size, size, size, batch, alpha=1.5, beta=beta)
+        A, B, C0 = make_inputs(p)
+        C, kern = run_device(bl, p, A, B, C0)
+        assert kern == f"small{size}"
+        items = sorted(set([0, batch - 1] + [int(x) for x in rng.integers(0, batch, 12)]))
+        assert_parity(p, A, B, C0, C, items, what=f"{kern} {oa}{ob} b{batch}")
+        Cg, _ = run_device(bl, p, A, B, C0, kernel="generic")
+        assert np.allclose(C, Cg, rtol=2e-5, atol=2e-5), f"{kern} {oa}{ob} b{batch} vs generic"
+
+
 def test_forced_kernel_that_cannot_run_reports_unsupported(bl):
     p = oracle.make_problem("d", "N", "N", 20, 20, 20, 1)
     A, B, C0 = make_inputs(p)
