@@ -53,8 +53,6 @@ int env_int(const char* name, int dflt) {
 // =================================================================================================
 // small32
 // =================================================================================================
-constexpr int kConsumerWarps32 = 8;
-constexpr int kThreads32 = 32 * (1 + kConsumerWarps32);
 constexpr int kMatBytes32 = 32 * 32 * 4;
 
 // acc[r][c] += sum_k opA(4ti+r, k) * opB(k, 8tj+c) for one 32x32x32 item held in shared memory.
@@ -121,9 +119,9 @@ __device__ __forceinline__ void mma32(const float4* __restrict__ As4, const floa
 }
 
 // Shared memory: `stages` x {A, B[, C]} of 4 KiB each, then full[stages], empty[stages] barriers.
-// `stages` is a multiple of kConsumerWarps32 and at most 32 (one producer lane per stage).
-template <bool A_KMAJOR, bool B_KMAJOR, bool HAS_C>
-__global__ void __launch_bounds__(kThreads32, 1)
+// `stages` is a multiple of the consumer warp count CW and at most 32 (one producer lane per stage).
+template <int CW, bool A_KMAJOR, bool B_KMAJOR, bool HAS_C>
+__global__ void __launch_bounds__(32 * (1 + CW), 1)
     gemm_small32_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
                         long long sa, long long sb, long long sc, int batch, float alpha, float beta,
                         int stages) {
@@ -163,9 +161,9 @@ __global__ void __launch_bounds__(kThreads32, 1)
 
   const int cw = warp - 1;
   const int ti = lane & 7, tj = lane >> 3;
-  int s = cw;          // stage of this warp's current item: (cw + 8*i) % stages
+  int s = cw;          // stage of this warp's current item: (cw + CW*i) % stages
   uint32_t round = 0;  // how many times this warp has been through stage `s` before
-  for (int j = cw; j < my_items; j += kConsumerWarps32) {
+  for (int j = cw; j < my_items; j += CW) {
     if (!mbar_wait(&full_bar[s], round & 1u, kWaitFull)) return;
     const unsigned char* st = smem + (size_t)s * kStageBytes;
     const float4* As4 = reinterpret_cast<const float4*>(st);
@@ -204,7 +202,7 @@ __global__ void __launch_bounds__(kThreads32, 1)
       }
       Cg4[(8 * tj + c) * 8 + ti] = o;
     }
-    s += kConsumerWarps32;
+    s += CW;
     if (s >= stages) {
       s -= stages;
       ++round;
@@ -212,18 +210,18 @@ __global__ void __launch_bounds__(kThreads32, 1)
   }
 }
 
-template <bool AK, bool BK, bool HC>
+template <int CW, bool AK, bool BK, bool HC>
 int launch32(const GemmParams& p, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
   constexpr int kStageBytes = (HC ? 3 : 2) * kMatBytes32;
   const size_t budget = dev.smem_optin > 8192 ? dev.smem_optin - 4096 : 0;
   static const int want = env_int("BLB200_SMALL32_STAGES", 16);  // tuning knob; rounded to a legal value
-  int stages = (int)(budget / ((size_t)kStageBytes * kConsumerWarps32)) * kConsumerWarps32;
-  if (stages > 32) stages = 32;
-  if (want >= kConsumerWarps32 && want < stages) stages = want / kConsumerWarps32 * kConsumerWarps32;
-  if (stages < kConsumerWarps32) return BLB200_E_UNSUPPORTED;
+  int stages = (int)(budget / ((size_t)kStageBytes * CW)) * CW;
+  if (stages > 32) stages = 32 / CW * CW;
+  if (want >= CW && want < stages) stages = want / CW * CW;
+  if (stages < CW) return BLB200_E_UNSUPPORTED;
   const size_t smem = (size_t)stages * kStageBytes + (size_t)stages * 2 * sizeof(uint64_t);
-  auto kern = gemm_small32_kernel<AK, BK, HC>;
+  auto kern = gemm_small32_kernel<CW, AK, BK, HC>;
   static thread_local int configured_for = -1;  // per (instantiation, thread): device last configured
   int cur = 0;
   cudaGetDevice(&cur);
@@ -234,7 +232,7 @@ int launch32(const GemmParams& p, cudaStream_t stream) {
     configured_for = cur;
   }
   const int grid = p.batch < dev.sm_count ? p.batch : dev.sm_count;
-  kern<<<grid, kThreads32, smem, stream>>>((const float*)p.a, (const float*)p.b, (float*)p.c, p.sa, p.sb,
+  kern<<<grid, 32 * (1 + CW), smem, stream>>>((const float*)p.a, (const float*)p.b, (float*)p.c, p.sa, p.sb,
                                            p.sc, p.batch, (float)p.alpha[0], (float)p.beta[0], stages);
   return (int)cudaGetLastError();
 }
@@ -490,10 +488,13 @@ int launch_small32(const GemmParams& p, int dtype, cudaStream_t stream) {
   const bool ak = p.op_a != BLB200_N;  // op T stores A as k x m: k runs fastest
   const bool bk = p.op_b == BLB200_N;  // op N stores B as k x n: k runs fastest
   const bool hc = (float)p.beta[0] != 0.f;
+  static const int cw = env_int("BLB200_SMALL32_WARPS", 16);  // tuning knob: 8, 12 or 16 consumer warps
   int rc;
-#define BLB_CASE(a, b)                                                              \
-  if (ak == a && bk == b) {                                                         \
-    rc = hc ? launch32<a, b, true>(p, stream) : launch32<a, b, false>(p, stream);   \
+#define BLB_CASE(a, b)                                                                            \
+  if (ak == a && bk == b) {                                                                       \
+    if (cw == 16) rc = hc ? launch32<16, a, b, true>(p, stream) : launch32<16, a, b, false>(p, stream); \
+    else if (cw == 12) rc = hc ? launch32<12, a, b, true>(p, stream) : launch32<12, a, b, false>(p, stream); \
+    else rc = hc ? launch32<8, a, b, true>(p, stream) : launch32<8, a, b, false>(p, stream);      \
   } else
   BLB_CASE(false, false) BLB_CASE(false, true) BLB_CASE(true, false) BLB_CASE(true, true) { rc = BLB200_E_INTERNAL; }
 #undef BLB_CASE

@@ -24,6 +24,58 @@ __global__ void __launch_bounds__(256) fma_rate_kernel(R* sink, int iters, R a, 
   if (total == (R)123456789) sink[0] = total;  // practically never true; keeps the chain live
 }
 
+// FP64 tensor-core rate: mma.sync m8n8k4 (256 FMAs per warp instruction), 8 independent accumulator
+// pairs per thread.
+__global__ void __launch_bounds__(256) dmma_rate_kernel(double* sink, int iters, double a, double b) {
+  double c[8][2];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) c[i][0] = c[i][1] = (double)(threadIdx.x + i);
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int rep = 0; rep < 4; ++rep)
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+                     : "+d"(c[i][0]), "+d"(c[i][1])
+                     : "d"(a), "d"(b));
+  }
+  double total = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) total += c[i][0] + c[i][1];
+  if (total == 123456789.0) sink[0] = total;
+}
+
+int measure_dmma(double* tflops) {
+  const DeviceInfo& dev = device_info();
+  double* sink = nullptr;
+  cudaError_t e = cudaMalloc(&sink, sizeof(double));
+  if (e != cudaSuccess) return (int)e;
+  const int iters = 2048, blocks = dev.sm_count * 8, threads = 256;
+  cudaEvent_t t0, t1;
+  cudaEventCreate(&t0);
+  cudaEventCreate(&t1);
+  dmma_rate_kernel<<<blocks, threads>>>(sink, 16, 0.999, 0.001);
+  float best = 1e30f;
+  for (int rep = 0; rep < 5; ++rep) {
+    cudaEventRecord(t0);
+    dmma_rate_kernel<<<blocks, threads>>>(sink, iters, 0.999, 0.001);
+    cudaEventRecord(t1);
+    e = cudaEventSynchronize(t1);
+    if (e != cudaSuccess) break;
+    float ms = 0;
+    cudaEventElapsedTime(&ms, t0, t1);
+    if (ms < best) best = ms;
+  }
+  cudaEventDestroy(t0);
+  cudaEventDestroy(t1);
+  cudaFree(sink);
+  if (e != cudaSuccess) return (int)e;
+  // per warp instruction: 8*8*4 FMAs = 512 flops; 32 instructions per iteration per warp
+  const double flops = 512.0 * 32.0 * iters * (double)blocks * (threads / 32);
+  *tflops = flops / (best * 1e-3) / 1e12;
+  return BLB200_OK;
+}
+
 template <typename R>
 int measure(double* tflops, double* ms_out) {
   const DeviceInfo& dev = device_info();
@@ -60,10 +112,12 @@ int measure(double* tflops, double* ms_out) {
 }  // namespace blb200
 
 // Measures the FMA issue rate of the current device for float (dtype S) or double (dtype D) in
-// TFLOP/s (2 flops per FMA).  Synchronous; allocates a few bytes; a diagnostic, not a data path.
+// TFLOP/s (2 flops per FMA); dtype Z selects the FP64 tensor-core (DMMA m8n8k4) rate instead.
+// Synchronous; allocates a few bytes; a diagnostic, not a data path.
 extern "C" int blb200_measure_pipe_peak(int32_t dtype, double* tflops) {
   if (!tflops) return BLB200_E_NULL;
   if (dtype == BLB200_S) return blb200::measure<float>(tflops, nullptr);
   if (dtype == BLB200_D) return blb200::measure<double>(tflops, nullptr);
+  if (dtype == BLB200_Z) return blb200::measure_dmma(tflops);
   return BLB200_E_DTYPE;
 }

@@ -151,8 +151,9 @@ def device_status() -> int:
 
 
 def measure_pipe_peak(dtype: str = "s") -> float:
-    """Measured FFMA ("s") or DFMA ("d") issue rate of the current device, TFLOP/s."""
+    """Measured FFMA ("s") or DFMA ("d") issue rate of the current device, TFLOP/s; "dmma" gives the
+    FP64 tensor-core (mma.sync m8n8k4) rate."""
     import ctypes
     out = ctypes.c_double(0.0)
-    check(load().blb200_measure_pipe_peak({"s": _lib.S, "d": _lib.D}[dtype], ctypes.byref(out)))
+    check(load().blb200_measure_pipe_peak({"s": _lib.S, "d": _lib.D, "dmma": _lib.Z}[dtype], ctypes.byref(out)))
     return out.value

@@ -109,7 +109,8 @@ int blb200_device_status(int* out);
 
 /* Diagnostic: measured FMA issue rate of the current device in TFLOP/s (2 flops per FMA) for
  * dtype BLB200_S (FFMA) or BLB200_D (DFMA) — the pipe peak that compute-bound shapes are judged
- * against, next to the nominal SMs x lanes x 2 x clock figure.  Synchronous. */
+ * against, next to the nominal SMs x lanes x 2 x clock figure.  dtype BLB200_Z selects the FP64
+ * tensor-core (mma.sync m8n8k4) rate instead.  Synchronous. */
 int blb200_measure_pipe_peak(int32_t dtype, double* tflops);
 
 /* ---- per-queue workspace arena -------------------------------------------------------
