@@ -111,10 +111,12 @@ int launch_generic(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_small32(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_small64(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_tiled(const GemmParams& p, int dtype, cudaStream_t stream);
+int launch_dmma(const GemmParams& p, int dtype, cudaStream_t stream);
 
 bool small32_supported(const GemmParams& p, int dtype);
 bool small64_supported(const GemmParams& p, int dtype);
 bool tiled_supported(const GemmParams& p, int dtype);
+bool dmma_supported(const GemmParams& p, int dtype);
 
 // Device properties cached per device.
 struct DeviceInfo {

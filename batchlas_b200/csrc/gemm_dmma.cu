@@ -1,0 +1,343 @@
+// FP64 tensor-core tiles for double and complex<double>: mma.sync m8n8k4 (DMMA) fed from the same
+// multi-stage ring of 16-byte asynchronous copies as the FFMA/DFMA tiled kernel.
+//
+// Why DMMA: on B200 the DMMA issue rate measured 37.2 TFLOP/s against 33.6 for DFMA, and a DMMA
+// fragment load moves one double per lane for 8 FMAs per lane, where the register-blocked DFMA
+// tile needs 12 doubles for 32 FMAs — the DFMA kernel is bound by shared-memory-to-register
+// bandwidth (about 78 % of it busy for 61 % of the FP64 pipe), the DMMA kernel is not.  DMMA
+// multiplies and accumulates in full binary64, so results stay within the same bound.
+//
+// Layout.  Operands stay in their stored orientation; rows of a stage are pitched 32 bytes past
+// their natural length so that the 16 lanes of a half-warp request (4 fragment rows x 4 k) fall
+// into 16 different 8-byte bank pairs:
+//   M-major A (op N):   stage rows are k, BM doubles each;    fragment (m = g, k = t) at [k][m]
+//   K-major A (op T/C): stage rows are m, BK doubles each;    fragment at [m][k]
+//   (g = lane >> 2, t = lane & 3; B likewise with n in place of m.)
+// A warp owns a 32 x 32 block of C as 4 x 4 DMMA tiles (16 accumulator pairs); a CTA of 8 warps
+// owns 128 x 64.  Complex operands keep (re, im) interleaved, one 16-byte fragment load per lane,
+// and each complex tile product is four real DMMAs; conjugation flips the sign of the imaginary
+// fragment in registers.
+//
+// Preconditions are those of the tiled kernel (16-byte aligned bases, ld and stride multiples of
+// 16 bytes); edges are zero-filled on load and predicated on store.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace blb200 {
+namespace {
+
+__device__ __forceinline__ void dmma(double& c0, double& c1, double a, double b) {
+  asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+               : "+d"(c0), "+d"(c1)
+               : "d"(a), "d"(b));
+}
+
+// Bytes added to every stage row.  A request must spread its fragment rows over all banks: 4 rows
+// of 32 bytes (double, half-warp of 64-bit loads; complex M-major, quarter-warp of 4 k-rows x 2
+// elements) want a 32-byte shift per row, 2 rows of 64 bytes (complex K-major) a 64-byte shift.
+__host__ __device__ constexpr int pad_for(int es, bool kmajor) { return (es == 16 && kmajor) ? 64 : 32; }
+
+// Asynchronous copy of one operand tile into a pitched stage.  ES = element bytes (8 or 16).
+template <int ES, int BMN, int BK, int THREADS, bool KMAJOR>
+__device__ __forceinline__ void load_tile_pitched(unsigned char* smem, const unsigned char* __restrict__ base,
+                                                  long long ld, int MN0, int MN, int k0, int K, int tid) {
+  constexpr int V = 16 / ES;  // elements per 16-byte chunk
+  if (!KMAJOR) {
+    constexpr int CH_PER_ROW = BMN / V, CHUNKS = BK * CH_PER_ROW, PITCH = BMN * ES + pad_for(ES, false);
+#pragma unroll
+    for (int c = tid; c < CHUNKS; c += THREADS) {
+      const int kk = c / CH_PER_ROW, mc = c % CH_PER_ROW;
+      const int gk = k0 + kk, gm = MN0 + mc * V;
+      int valid = (gk < K) ? (MN - gm) : 0;
+      valid = valid < 0 ? 0 : (valid > V ? V : valid);
+      const unsigned char* src = valid ? base + ((long long)gk * ld + gm) * ES : base;
+      cp_async16(smem + (size_t)kk * PITCH + (size_t)mc * 16, src, valid * ES);
+    }
+  } else {
+    constexpr int CH_PER_ROW = BK / V, CHUNKS = BMN * CH_PER_ROW, PITCH = BK * ES + pad_for(ES, true);
+#pragma unroll
+    for (int c = tid; c < CHUNKS; c += THREADS) {
+      const int r = c / CH_PER_ROW, kc = c % CH_PER_ROW;
+      const int gmn = MN0 + r, gk = k0 + kc * V;
+      int valid = (gmn < MN) ? (K - gk) : 0;
+      valid = valid < 0 ? 0 : (valid > V ? V : valid);
+      const unsigned char* src = valid ? base + ((long long)gmn * ld + gk) * ES : base;
+      cp_async16(smem + (size_t)r * PITCH + (size_t)kc * 16, src, valid * ES);
+    }
+  }
+}
+
+template <int ES, int BMN, int BK, bool KMAJOR>
+__host__ __device__ constexpr int pitched_stage_bytes() {
+  return KMAJOR ? BMN * (BK * ES + pad_for(ES, true)) : BK * (BMN * ES + pad_for(ES, false));
+}
+
+// ---- real double -------------------------------------------------------------------------------
+template <int OPA, int OPB>
+__global__ void __launch_bounds__(256, 2) gemm_dmma_d_kernel(GemmParams p, int tiles_m, int tiles_n) {
+  constexpr int BM = 128, BN = 64, BK = 16, STAGES = 3, THREADS = 256;
+  constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
+  constexpr int A_STAGE = pitched_stage_bytes<8, BM, BK, AK>(), B_STAGE = pitched_stage_bytes<8, BN, BK, BKM>();
+  constexpr int A_PITCH = AK ? BK * 8 + pad_for(8, true) : BM * 8 + pad_for(8, false);
+  constexpr int B_PITCH = BKM ? BK * 8 + pad_for(8, true) : BN * 8 + pad_for(8, false);
+
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* As = smem;
+  unsigned char* Bs = smem + (size_t)STAGES * A_STAGE;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int wm = warp & 3, wn = warp >> 2;  // 4 x 2 warps, 32 x 32 each
+
+  const long long tiles_per_item = (long long)tiles_m * tiles_n;
+  const long long tile = blockIdx.x;
+  const long long item = tile / tiles_per_item;
+  const int rem = (int)(tile - item * tiles_per_item);
+  const int m0 = (rem % tiles_m) * BM, n0 = (rem / tiles_m) * BN;
+  const unsigned char* A = (const unsigned char*)p.a + item * p.sa * 8;
+  const unsigned char* B = (const unsigned char*)p.b + item * p.sb * 8;
+  double* C = (double*)p.c + item * p.sc;
+
+  double acc[4][4][2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+
+  const int KT = (p.k + BK - 1) / BK;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < KT) {
+      load_tile_pitched<8, BM, BK, THREADS, AK>(As + (size_t)s * A_STAGE, A, p.lda, m0, p.m, s * BK, p.k, tid);
+      load_tile_pitched<8, BN, BK, THREADS, BKM>(Bs + (size_t)s * B_STAGE, B, p.ldb, n0, p.n, s * BK, p.k, tid);
+    }
+    cp_async_commit();
+  }
+
+  // byte offsets of this lane's fragment element inside a stage, for k-step 0
+  const int a_off = AK ? (wm * 32 + g) * A_PITCH + t * 8 : t * A_PITCH + (wm * 32 + g) * 8;
+  const int b_off = BKM ? (wn * 32 + g) * B_PITCH + t * 8 : t * B_PITCH + (wn * 32 + g) * 8;
+  constexpr int A_MB = AK ? 8 * A_PITCH : 64;       // next 8 rows of m
+  constexpr int B_NB = BKM ? 8 * B_PITCH : 64;      // next 8 columns of n
+  constexpr int A_K4 = AK ? 32 : 4 * A_PITCH;       // next 4 k
+  constexpr int B_K4 = BKM ? 32 : 4 * B_PITCH;
+
+  for (int kt = 0; kt < KT; ++kt) {
+    cp_async_wait<STAGES - 2>();
+    __syncthreads();
+    {
+      const int nxt = kt + STAGES - 1;
+      if (nxt < KT) {
+        const int s = nxt % STAGES;
+        load_tile_pitched<8, BM, BK, THREADS, AK>(As + (size_t)s * A_STAGE, A, p.lda, m0, p.m, nxt * BK, p.k, tid);
+        load_tile_pitched<8, BN, BK, THREADS, BKM>(Bs + (size_t)s * B_STAGE, B, p.ldb, n0, p.n, nxt * BK, p.k, tid);
+      }
+      cp_async_commit();
+    }
+    const unsigned char* as = As + (size_t)(kt % STAGES) * A_STAGE + a_off;
+    const unsigned char* bs = Bs + (size_t)(kt % STAGES) * B_STAGE + b_off;
+#pragma unroll
+    for (int k4 = 0; k4 < BK / 4; ++k4) {
+      double af[4], bf[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) af[i] = *reinterpret_cast<const double*>(as + k4 * A_K4 + i * A_MB);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bf[j] = *reinterpret_cast<const double*>(bs + k4 * B_K4 + j * B_NB);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dmma(acc[i][j][0], acc[i][j][1], af[i], bf[j]);
+    }
+  }
+  cp_async_wait<0>();
+
+  const double alpha = p.alpha[0], beta = p.beta[0];
+  const bool beta_zero = beta == 0.0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int col = n0 + wn * 32 + j * 8 + 2 * t + e;
+      if (col >= p.n) continue;
+      double* ccol = C + (long long)col * p.ldc;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = m0 + wm * 32 + i * 8 + g;
+        if (row >= p.m) continue;
+        double out = alpha * acc[i][j][e];
+        if (!beta_zero) out = fma(beta, ccol[row], out);
+        ccol[row] = out;
+      }
+    }
+}
+
+// ---- complex double ------------------------------------------------------------------------------
+// CTA 64 x 64, 8 warps as 2 (m) x 4 (n), warp tile 32 x 16: 4 x 2 DMMA tiles, re and im planes.
+template <int OPA, int OPB>
+__global__ void __launch_bounds__(256, 2) gemm_dmma_z_kernel(GemmParams p, int tiles_m, int tiles_n) {
+  constexpr int BM = 64, BN = 64, BK = 8, STAGES = 3, THREADS = 256;
+  constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
+  constexpr bool CONJ_A = (OPA == BLB200_H), CONJ_B = (OPB == BLB200_H);
+  constexpr int A_STAGE = pitched_stage_bytes<16, BM, BK, AK>(), B_STAGE = pitched_stage_bytes<16, BN, BK, BKM>();
+  constexpr int A_PITCH = AK ? BK * 16 + pad_for(16, true) : BM * 16 + pad_for(16, false);
+  constexpr int B_PITCH = BKM ? BK * 16 + pad_for(16, true) : BN * 16 + pad_for(16, false);
+
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* As = smem;
+  unsigned char* Bs = smem + (size_t)STAGES * A_STAGE;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int wm = warp & 1, wn = warp >> 1;  // 2 x 4 warps, 32 x 16 each
+
+  const long long tiles_per_item = (long long)tiles_m * tiles_n;
+  const long long tile = blockIdx.x;
+  const long long item = tile / tiles_per_item;
+  const int rem = (int)(tile - item * tiles_per_item);
+  const int m0 = (rem % tiles_m) * BM, n0 = (rem / tiles_m) * BN;
+  const unsigned char* A = (const unsigned char*)p.a + item * p.sa * 16;
+  const unsigned char* B = (const unsigned char*)p.b + item * p.sb * 16;
+  double2* C = (double2*)p.c + item * p.sc;
+
+  double accr[4][2][2], acci[4][2][2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) accr[i][j][0] = accr[i][j][1] = acci[i][j][0] = acci[i][j][1] = 0.0;
+
+  const int KT = (p.k + BK - 1) / BK;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < KT) {
+      load_tile_pitched<16, BM, BK, THREADS, AK>(As + (size_t)s * A_STAGE, A, p.lda, m0, p.m, s * BK, p.k, tid);
+      load_tile_pitched<16, BN, BK, THREADS, BKM>(Bs + (size_t)s * B_STAGE, B, p.ldb, n0, p.n, s * BK, p.k, tid);
+    }
+    cp_async_commit();
+  }
+
+  const int a_off = AK ? (wm * 32 + g) * A_PITCH + t * 16 : t * A_PITCH + (wm * 32 + g) * 16;
+  const int b_off = BKM ? (wn * 16 + g) * B_PITCH + t * 16 : t * B_PITCH + (wn * 16 + g) * 16;
+  constexpr int A_MB = AK ? 8 * A_PITCH : 128;
+  constexpr int B_NB = BKM ? 8 * B_PITCH : 128;
+  constexpr int A_K4 = AK ? 64 : 4 * A_PITCH;
+  constexpr int B_K4 = BKM ? 64 : 4 * B_PITCH;
+
+  for (int kt = 0; kt < KT; ++kt) {
+    cp_async_wait<STAGES - 2>();
+    __syncthreads();
+    {
+      const int nxt = kt + STAGES - 1;
+      if (nxt < KT) {
+        const int s = nxt % STAGES;
+        load_tile_pitched<16, BM, BK, THREADS, AK>(As + (size_t)s * A_STAGE, A, p.lda, m0, p.m, nxt * BK, p.k, tid);
+        load_tile_pitched<16, BN, BK, THREADS, BKM>(Bs + (size_t)s * B_STAGE, B, p.ldb, n0, p.n, nxt * BK, p.k, tid);
+      }
+      cp_async_commit();
+    }
+    const unsigned char* as = As + (size_t)(kt % STAGES) * A_STAGE + a_off;
+    const unsigned char* bs = Bs + (size_t)(kt % STAGES) * B_STAGE + b_off;
+#pragma unroll
+    for (int k4 = 0; k4 < BK / 4; ++k4) {
+      double2 af[4], bf[2];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        af[i] = *reinterpret_cast<const double2*>(as + k4 * A_K4 + i * A_MB);
+        if (CONJ_A) af[i].y = -af[i].y;
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        bf[j] = *reinterpret_cast<const double2*>(bs + k4 * B_K4 + j * B_NB);
+        if (CONJ_B) bf[j].y = -bf[j].y;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const double nai = -af[i].y;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          dmma(accr[i][j][0], accr[i][j][1], af[i].x, bf[j].x);
+          dmma(accr[i][j][0], accr[i][j][1], nai, bf[j].y);
+          dmma(acci[i][j][0], acci[i][j][1], af[i].x, bf[j].y);
+          dmma(acci[i][j][0], acci[i][j][1], af[i].y, bf[j].x);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+  const double2 alpha = make_double2(p.alpha[0], p.alpha[1]), beta = make_double2(p.beta[0], p.beta[1]);
+  const bool beta_zero = beta.x == 0.0 && beta.y == 0.0;
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int col = n0 + wn * 16 + j * 8 + 2 * t + e;
+      if (col >= p.n) continue;
+      double2* ccol = C + (long long)col * p.ldc;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = m0 + wm * 32 + i * 8 + g;
+        if (row >= p.m) continue;
+        const double2 v = make_double2(accr[i][j][e], acci[i][j][e]);
+        ccol[row] = epilogue<double2>(alpha, v, beta, beta_zero, ccol + row);
+      }
+    }
+}
+
+template <typename Kern>
+int launch_kernel(Kern kern, size_t smem, const GemmParams& p, int BM, int BN, cudaStream_t stream, int* configured_for) {
+  const int tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BN - 1) / BN;
+  const long long total = (long long)tiles_m * tiles_n * p.batch;
+  if (total > 0x7fffffffLL) return BLB200_E_UNSUPPORTED;
+  int cur = 0;
+  cudaGetDevice(&cur);
+  if (*configured_for != cur) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    *configured_for = cur;
+  }
+  kern<<<(unsigned)total, 256, smem, stream>>>(p, tiles_m, tiles_n);
+  return (int)cudaGetLastError();
+}
+
+template <int OPA, int OPB>
+int launch_d(const GemmParams& p, cudaStream_t stream) {
+  constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
+  constexpr size_t smem = 3 * (size_t)(pitched_stage_bytes<8, 128, 16, AK>() + pitched_stage_bytes<8, 64, 16, BKM>());
+  static thread_local int configured_for = -1;
+  return launch_kernel(gemm_dmma_d_kernel<OPA, OPB>, smem, p, 128, 64, stream, &configured_for);
+}
+
+template <int OPA, int OPB>
+int launch_z(const GemmParams& p, cudaStream_t stream) {
+  constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
+  constexpr size_t smem = 3 * (size_t)(pitched_stage_bytes<16, 64, 8, AK>() + pitched_stage_bytes<16, 64, 8, BKM>());
+  static thread_local int configured_for = -1;
+  return launch_kernel(gemm_dmma_z_kernel<OPA, OPB>, smem, p, 64, 64, stream, &configured_for);
+}
+
+}  // namespace
+
+bool dmma_supported(const GemmParams& p, int dtype) {
+  return (dtype == BLB200_D || dtype == BLB200_Z) && tiled_supported(p, dtype);
+}
+
+int launch_dmma(const GemmParams& p, int dtype, cudaStream_t stream) {
+  if (!dmma_supported(p, dtype)) return BLB200_E_UNSUPPORTED;
+  const int oa = p.op_a, ob = p.op_b;
+  int rc = BLB200_E_INTERNAL;
+  if (dtype == BLB200_D) {
+#define BLB_OP(A_, B_) \
+  if (oa == A_ && ob == B_) rc = launch_d<A_, B_>(p, stream);
+    BLB_OP(0, 0) BLB_OP(0, 1) BLB_OP(1, 0) BLB_OP(1, 1)
+#undef BLB_OP
+  } else {
+#define BLB_OP(A_, B_) \
+  if (oa == A_ && ob == B_) rc = launch_z<A_, B_>(p, stream);
+    BLB_OP(0, 0) BLB_OP(0, 1) BLB_OP(0, 2) BLB_OP(1, 0) BLB_OP(1, 1) BLB_OP(1, 2) BLB_OP(2, 0) BLB_OP(2, 1) BLB_OP(2, 2)
+#undef BLB_OP
+  }
+  if (rc == BLB200_OK) note_launch("dmma");
+  return rc;
+}
+
+}  // namespace blb200

@@ -47,10 +47,10 @@ enum {
 enum {
   BLB200_K_AUTO = 0,
   BLB200_K_GENERIC = 1, /* any dtype/op/ld/alignment; predicated scalar loads              */
-  BLB200_K_SMALL32 = 2, /* whole 32x32x32 matrices per warp, bulk-copy pipeline (S and D)   */
-  BLB200_K_SMALL64 = 3, /* whole 64x64x64 float matrices per warp pair, bulk-copy pipeline  */
-  BLB200_K_TILED = 4,   /* register-blocked smem tiles fed by 16-byte async copies          */
-  BLB200_K_TILED_TMA = 5 /* register-blocked smem tiles fed by tensor-map TMA               */
+  BLB200_K_SMALL32 = 2, /* whole 32x32x32 float matrices per warp, TMA bulk-copy ring           */
+  BLB200_K_SMALL64 = 3, /* whole 64x64x64 float matrices per warp pair, TMA ring (tiled+bulk)   */
+  BLB200_K_TILED = 4,   /* register-blocked FFMA/DFMA smem tiles fed by 16-byte async copies    */
+  BLB200_K_DMMA = 5     /* FP64 tensor-core (mma.sync m8n8k4) tiles, double and complex<double> */
 };
 
 /*

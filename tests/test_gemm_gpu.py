@@ -120,6 +120,26 @@ def test_unaligned_views_take_a_safe_path(bl, dt):
         assert_parity(p, A, B, C0, C, what=f"offset view via {kern}")
 
 
+@pytest.mark.parametrize("kernel", ["tiled", "dmma"])
+@pytest.mark.parametrize("dt", ["d", "z"])
+def test_both_fp64_tile_kernels_on_ragged_and_aligned_shapes(bl, kernel, dt):
+    """The register-blocked DFMA tiles and the tensor-core DMMA tiles are interchangeable: both must
+    meet the bound on every op pair, including ragged edges in m, n and k (the reference's ragged
+    case is 200 x 130 x 70, alpha = 2, beta = -1: tests/gemm_tests.cc:1995-2033)."""
+    code = oracle.DTYPES[dt]
+    ops = ["N", "T"] if dt == "d" else ["N", "T", "C"]
+    for oa in ops:
+        for ob in ops:
+            for (m, n, k, batch, alpha, beta) in [(200, 130, 70, 3, 2.0, -1.0), (128, 64, 96, 2, 1.0, 0.0),
+                                                 (66, 34, 6, 2, 1.0, 1.0), (256, 256, 40, 1, 0.5, 0.0)]:
+                p = oracle.make_problem(dt, oa, ob, m, n, k, batch, alpha=scalar_for(code, alpha),
+                                        beta=scalar_for(code, beta))
+                A, B, C0 = make_inputs(p)
+                C, kern = run_device(bl, p, A, B, C0, kernel=kernel)
+                assert kern == kernel
+                assert_parity(p, A, B, C0, C, what=f"{kernel} {dt} {oa}{ob} {m}x{n}x{k}")
+
+
 @pytest.mark.parametrize("size", [32, 64])
 @pytest.mark.parametrize("oa", ["N", "T"])
 @pytest.mark.parametrize("ob", ["N", "T"])
