@@ -248,38 +248,77 @@ constexpr int kHalfBytes64 = 32 * 64 * 4;             // one operand, half of K:
 constexpr int kSlotBytes64 = 2 * kHalfBytes64;        // A half + B half
 constexpr int kMatElems64 = 64 * 64;
 
-// One half-K (32 k) of the product for this lane's 8 x 8 block.
+// Packed FP32 FMA (Blackwell FFMA2): d.lo += a.lo*b.lo, d.hi += a.hi*b.hi, each an IEEE fused
+// multiply-add.  One instruction issues two FMAs, which matters because the 8 x 8 register block is
+// issue-bound with scalar FFMA (64 FMAs + 16 fragment floats + addressing per k per lane).
+__device__ __forceinline__ void ffma2(uint64_t& d, uint64_t a, uint64_t b) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
+}
+__device__ __forceinline__ uint64_t dup2(float f) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(f));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+// How the 64 accumulators of a lane are paired for FFMA2.  Pairs must be adjacent in the operand
+// that shared memory delivers as float4 along the output dimension:
+//   kRowPairs  A M-major: a float4 holds 4 consecutive rows  -> acc pairs (row 2p, 2p+1), B value duplicated
+//   kColPairs  A K-major, B N-major: a float4 holds 4 consecutive columns -> pairs (col 2p, 2p+1), A duplicated
+//   kScalar    both K-major: no operand is contiguous along an output dimension; plain FFMA
+enum PackMode { kScalar = 0, kRowPairs = 1, kColPairs = 2 };
+template <bool A_KMAJOR, bool B_KMAJOR>
+__host__ __device__ constexpr PackMode pack_mode() {
+  return !A_KMAJOR ? kRowPairs : (!B_KMAJOR ? kColPairs : kScalar);
+}
+
+// One half-K (32 k) of the product for this lane's 8 x 8 block.  `acc` is float[8][8] in scalar
+// mode; in the packed modes the same 64 registers are addressed as uint64_t[32].
 template <bool A_KMAJOR, bool B_KMAJOR>
 __device__ __forceinline__ void mma64_half(const unsigned char* __restrict__ As, const unsigned char* __restrict__ Bs,
-                                           int ti, int tj, int hw, float (&acc)[8][8]) {
+                                           int ti, int tj, int hw, float (&acc)[8][8], uint64_t (&accp)[32]) {
+  constexpr PackMode PM = pack_mode<A_KMAJOR, B_KMAJOR>();
   const float4* As4 = reinterpret_cast<const float4*>(As);
   const float4* Bs4 = reinterpret_cast<const float4*>(Bs);
-#pragma unroll 2
-  for (int kc = 0; kc < 8; ++kc) {
-    float af[8][4], bf[8][4];  // [row or col][kk]
-    if (A_KMAJOR) {            // swizzled rows of 128 bytes: row i = ti + 8r, i & 7 == ti
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const float4 v = As4[(ti + 8 * r) * 8 + (kc ^ ti)];
-        af[r][0] = v.x; af[r][1] = v.y; af[r][2] = v.z; af[r][3] = v.w;
-      }
-    } else {                   // k-rows of 256 bytes: rows 4ti..4ti+3 and 32+4ti..32+4ti+3
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        const float4 lo = As4[(4 * kc + kk) * 16 + ti];
-        const float4 hi = As4[(4 * kc + kk) * 16 + 8 + ti];
-        af[0][kk] = lo.x; af[1][kk] = lo.y; af[2][kk] = lo.z; af[3][kk] = lo.w;
-        af[4][kk] = hi.x; af[5][kk] = hi.y; af[6][kk] = hi.z; af[7][kk] = hi.w;
-      }
-    }
-    if (B_KMAJOR) {            // swizzled: column j = 32hw + tj + 4c, j & 7 == (tj + 4c) & 7
+  const ulonglong2* As2 = reinterpret_cast<const ulonglong2*>(As);
+  const ulonglong2* Bs2 = reinterpret_cast<const ulonglong2*>(Bs);
+  if constexpr (PM == kRowPairs && B_KMAJOR) {
+    // B fragments for a whole 4-k chunk come from 8 swizzled loads; they are fetched one chunk
+    // ahead (two register buffers) so that their latency hides behind the previous chunk's FMAs.
+    float bf[2][8][4];  // [buffer][col][kk]; column j = 32hw + tj + 4c
+    auto load_b = [&](int kc, float (&dst)[8][4]) {
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         const int j = 32 * hw + tj + 4 * c;
         const float4 v = Bs4[j * 8 + (kc ^ (j & 7))];
-        bf[c][0] = v.x; bf[c][1] = v.y; bf[c][2] = v.z; bf[c][3] = v.w;
+        dst[c][0] = v.x; dst[c][1] = v.y; dst[c][2] = v.z; dst[c][3] = v.w;
       }
-    } else {                   // k-rows of 256 bytes: columns 32hw + 8tj + c
+    };
+    load_b(0, bf[0]);
+#pragma unroll
+    for (int kc = 0; kc < 8; ++kc) {
+      if (kc + 1 < 8) load_b(kc + 1, bf[(kc + 1) & 1]);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const ulonglong2 lo = As2[(4 * kc + kk) * 16 + ti];
+        const ulonglong2 hi = As2[(4 * kc + kk) * 16 + 8 + ti];
+        const uint64_t a2[4] = {lo.x, lo.y, hi.x, hi.y};
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint64_t bd = dup2(bf[kc & 1][c][kk]);
+#pragma unroll
+          for (int rp = 0; rp < 4; ++rp) ffma2(accp[rp * 8 + c], a2[rp], bd);
+        }
+      }
+    }
+    return;
+  }
+#pragma unroll 2
+  for (int kc = 0; kc < 8; ++kc) {
+    if constexpr (PM == kRowPairs) {
+      float bf[8][4];  // [col][kk], k-rows of 256 bytes: columns 32hw + 8tj + c
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
         const float4 v0 = Bs4[(4 * kc + kk) * 16 + 8 * hw + 2 * tj];
@@ -287,13 +326,58 @@ __device__ __forceinline__ void mma64_half(const unsigned char* __restrict__ As,
         bf[0][kk] = v0.x; bf[1][kk] = v0.y; bf[2][kk] = v0.z; bf[3][kk] = v0.w;
         bf[4][kk] = v1.x; bf[5][kk] = v1.y; bf[6][kk] = v1.z; bf[7][kk] = v1.w;
       }
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        // rows 4ti..4ti+3 and 32+4ti..32+4ti+3 as four row pairs
+        const ulonglong2 lo = As2[(4 * kc + kk) * 16 + ti];
+        const ulonglong2 hi = As2[(4 * kc + kk) * 16 + 8 + ti];
+        const uint64_t a2[4] = {lo.x, lo.y, hi.x, hi.y};
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint64_t bd = dup2(bf[c][kk]);
+#pragma unroll
+          for (int rp = 0; rp < 4; ++rp) ffma2(accp[rp * 8 + c], a2[rp], bd);
+        }
+      }
+    } else if constexpr (PM == kColPairs) {
+      float af[8][4];  // [row][kk], swizzled rows ti + 8r
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float4 v = As4[(ti + 8 * r) * 8 + (kc ^ ti)];
+        af[r][0] = v.x; af[r][1] = v.y; af[r][2] = v.z; af[r][3] = v.w;
+      }
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const ulonglong2 v0 = Bs2[(4 * kc + kk) * 16 + 8 * hw + 2 * tj];
+        const ulonglong2 v1 = Bs2[(4 * kc + kk) * 16 + 8 * hw + 2 * tj + 1];
+        const uint64_t b2[4] = {v0.x, v0.y, v1.x, v1.y};  // column pairs (8tj+0,1) (2,3) (4,5) (6,7)
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          const uint64_t ad = dup2(af[r][kk]);
+#pragma unroll
+          for (int cp = 0; cp < 4; ++cp) ffma2(accp[r * 4 + cp], ad, b2[cp]);
+        }
+      }
+    } else {
+      float af[8][4], bf[8][4];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float4 v = As4[(ti + 8 * r) * 8 + (kc ^ ti)];
+        af[r][0] = v.x; af[r][1] = v.y; af[r][2] = v.z; af[r][3] = v.w;
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const int j = 32 * hw + tj + 4 * c;
+        const float4 v = Bs4[j * 8 + (kc ^ (j & 7))];
+        bf[c][0] = v.x; bf[c][1] = v.y; bf[c][2] = v.z; bf[c][3] = v.w;
+      }
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+#pragma unroll
+          for (int c = 0; c < 8; ++c) acc[r][c] = fmaf(af[r][kk], bf[c][kk], acc[r][c]);
     }
-#pragma unroll
-    for (int kk = 0; kk < 4; ++kk)
-#pragma unroll
-      for (int r = 0; r < 8; ++r)
-#pragma unroll
-        for (int c = 0; c < 8; ++c) acc[r][c] = fmaf(af[r][kk], bf[c][kk], acc[r][c]);
   }
 }
 
@@ -357,23 +441,39 @@ __global__ void __launch_bounds__(kThreads64, 1)
   int slot_i = 0;      // q % 3
   uint32_t round = 0;  // q / 3
   for (int j = pair; j < my_items; j += kPairs64) {
+    constexpr PackMode PM = pack_mode<A_KMAJOR, B_KMAJOR>();
     float acc[8][8];
+    uint64_t accp[32];
 #pragma unroll
     for (int r = 0; r < 8; ++r)
 #pragma unroll
       for (int c = 0; c < 8; ++c) acc[r][c] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) accp[i] = 0ull;
 #pragma unroll 1
     for (int half = 0; half < 2; ++half) {
       const int s = pair * kSlotsPerPair64 + slot_i;
       if (!mbar_wait(&full_bar[s], round & 1u, kWaitFull)) return;
       const unsigned char* st = smem + (size_t)s * kSlotBytes64;
-      mma64_half<A_KMAJOR, B_KMAJOR>(st, st + kHalfBytes64, ti, tj, hw, acc);
+      mma64_half<A_KMAJOR, B_KMAJOR>(st, st + kHalfBytes64, ti, tj, hw, acc, accp);
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[s]);
       if (++slot_i == kSlotsPerPair64) {
         slot_i = 0;
         ++round;
       }
+    }
+
+    if constexpr (PM == kRowPairs) {
+#pragma unroll
+      for (int rp = 0; rp < 4; ++rp)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) unpack2(accp[rp * 8 + c], acc[2 * rp][c], acc[2 * rp + 1][c]);
+    } else if constexpr (PM == kColPairs) {
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+#pragma unroll
+        for (int cp = 0; cp < 4; ++cp) unpack2(accp[r * 4 + cp], acc[r][2 * cp], acc[r][2 * cp + 1]);
     }
 
     const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;

@@ -45,6 +45,58 @@ __global__ void __launch_bounds__(256) dmma_rate_kernel(double* sink, int iters,
   if (total == 123456789.0) sink[0] = total;
 }
 
+// Packed FP32 FMA rate (fma.rn.f32x2: two FMAs per lane per instruction).
+__global__ void __launch_bounds__(256) ffma2_rate_kernel(unsigned long long* sink, int iters, float a, float b) {
+  unsigned long long acc[16], av, bv;
+  asm("mov.b64 %0, {%1, %1};" : "=l"(av) : "f"(a));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(bv) : "f"(b));
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float f = (float)(threadIdx.x + i);
+    asm("mov.b64 %0, {%1, %1};" : "=l"(acc[i]) : "f"(f));
+  }
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int rep = 0; rep < 4; ++rep)
+#pragma unroll
+      for (int i = 0; i < 16; ++i) asm volatile("fma.rn.f32x2 %0, %0, %1, %2;" : "+l"(acc[i]) : "l"(av), "l"(bv));
+  }
+  unsigned long long total = 0;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) total ^= acc[i];
+  if (total == 0x123456789abcdefull) sink[0] = total;
+}
+
+int measure_ffma2(double* tflops) {
+  const DeviceInfo& dev = device_info();
+  unsigned long long* sink = nullptr;
+  cudaError_t e = cudaMalloc(&sink, sizeof(unsigned long long));
+  if (e != cudaSuccess) return (int)e;
+  const int iters = 4096, blocks = dev.sm_count * 8, threads = 256;
+  cudaEvent_t t0, t1;
+  cudaEventCreate(&t0);
+  cudaEventCreate(&t1);
+  ffma2_rate_kernel<<<blocks, threads>>>(sink, 16, 0.999f, 0.001f);
+  float best = 1e30f;
+  for (int rep = 0; rep < 5; ++rep) {
+    cudaEventRecord(t0);
+    ffma2_rate_kernel<<<blocks, threads>>>(sink, iters, 0.999f, 0.001f);
+    cudaEventRecord(t1);
+    e = cudaEventSynchronize(t1);
+    if (e != cudaSuccess) break;
+    float ms = 0;
+    cudaEventElapsedTime(&ms, t0, t1);
+    if (ms < best) best = ms;
+  }
+  cudaEventDestroy(t0);
+  cudaEventDestroy(t1);
+  cudaFree(sink);
+  if (e != cudaSuccess) return (int)e;
+  const double flops = 2.0 * 2.0 * 64.0 * iters * (double)blocks * threads;
+  *tflops = flops / (best * 1e-3) / 1e12;
+  return BLB200_OK;
+}
+
 int measure_dmma(double* tflops) {
   const DeviceInfo& dev = device_info();
   double* sink = nullptr;
@@ -112,12 +164,14 @@ int measure(double* tflops, double* ms_out) {
 }  // namespace blb200
 
 // Measures the FMA issue rate of the current device for float (dtype S) or double (dtype D) in
-// TFLOP/s (2 flops per FMA); dtype Z selects the FP64 tensor-core (DMMA m8n8k4) rate instead.
+// TFLOP/s (2 flops per FMA); dtype Z selects the FP64 tensor-core (DMMA m8n8k4) rate and dtype C
+// the packed FP32 (fma.rn.f32x2) rate instead.
 // Synchronous; allocates a few bytes; a diagnostic, not a data path.
 extern "C" int blb200_measure_pipe_peak(int32_t dtype, double* tflops) {
   if (!tflops) return BLB200_E_NULL;
   if (dtype == BLB200_S) return blb200::measure<float>(tflops, nullptr);
   if (dtype == BLB200_D) return blb200::measure<double>(tflops, nullptr);
   if (dtype == BLB200_Z) return blb200::measure_dmma(tflops);
+  if (dtype == BLB200_C) return blb200::measure_ffma2(tflops);
   return BLB200_E_DTYPE;
 }
