@@ -43,6 +43,8 @@ class Lease(ctypes.Structure):
 SIGNATURES = {
     "blb200_gemm_validate": (ctypes.c_int, [ctypes.POINTER(GemmDesc)]),
     "blb200_gemm_strided_batched": (ctypes.c_int, [ctypes.POINTER(GemmDesc), ctypes.c_void_p]),
+    "blb200_gemm_heterogeneous": (ctypes.c_int, [ctypes.POINTER(GemmDesc), ctypes.c_void_p, ctypes.c_void_p,
+                                                 ctypes.c_void_p, ctypes.c_void_p]),
     "blb200_gemm_strided_batched_host": (ctypes.c_int, [ctypes.POINTER(GemmDesc), ctypes.c_int, ctypes.c_int32]),
     "blb200_last_kernel_name": (ctypes.c_char_p, []),
     "blb200_launch_count": (ctypes.c_uint64, []),

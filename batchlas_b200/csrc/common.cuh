@@ -20,6 +20,14 @@ struct GemmParams {
   int op_a, op_b;
 };
 
+// Optional per-item dims of a heterogeneous batch (null pointer = every item uses the capacity).
+struct HeteroDims {
+  const int* m;
+  const int* n;
+  const int* k;
+  int cap_m, cap_n, cap_k;
+};
+
 // ---- scalar traits ---------------------------------------------------------------------------
 // Real types are float/double; complex types are float2/double2 with (x,y) = (re,im), which is
 // the memory layout of std::complex<T>.
@@ -108,6 +116,7 @@ void note_launch(const char* kernel_name);
 // Each returns BLB200_OK / a cudaError_t, or BLB200_E_UNSUPPORTED when the kernel's preconditions
 // do not hold for `p` (the dispatcher then falls through to the next candidate).
 int launch_generic(const GemmParams& p, int dtype, cudaStream_t stream);
+int launch_generic_hetero(const GemmParams& p, const HeteroDims& het, int dtype, cudaStream_t stream);
 int launch_small32(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_small64(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_tiled(const GemmParams& p, int dtype, cudaStream_t stream);

@@ -105,9 +105,25 @@ int dispatch(const blb200_gemm_desc* d, cudaStream_t stream) {
   return launch_generic(p, d->dtype, stream);
 }
 
+int dispatch_hetero(const blb200_gemm_desc* d, const int32_t* m_items, const int32_t* n_items,
+                    const int32_t* k_items, cudaStream_t stream) {
+  if (!m_items && !n_items && !k_items) return dispatch(d, stream);
+  int rc = validate(d);
+  if (rc != BLB200_OK) return rc;
+  if (d->m == 0 || d->n == 0 || d->batch == 0) return BLB200_OK;
+  const GemmParams p = to_params(d);
+  HeteroDims het{m_items, n_items, k_items, d->m, d->n, d->k};
+  return launch_generic_hetero(p, het, d->dtype, stream);
+}
+
 }  // namespace blb200
 
 extern "C" {
+
+int blb200_gemm_heterogeneous(const blb200_gemm_desc* desc, const int32_t* m_items, const int32_t* n_items,
+                              const int32_t* k_items, void* cuda_stream) {
+  return blb200::dispatch_hetero(desc, m_items, n_items, k_items, (cudaStream_t)cuda_stream);
+}
 
 int blb200_gemm_validate(const blb200_gemm_desc* desc) { return blb200::validate(desc); }
 

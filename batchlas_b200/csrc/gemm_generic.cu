@@ -13,8 +13,12 @@ namespace {
 
 // 16 x 16 threads; each owns a TM x TN block of C whose rows/cols are strided by 16 so that a
 // half-warp touches 16 consecutive rows of one column (coalesced C traffic, conflict-free A reads).
+// `het` carries optional per-item dims (device-readable int arrays of length batch, or null): the
+// heterogeneous batch of BatchLAS (MatrixView active_rows_/active_cols_, include/blas/matrix.hh:62-63;
+// the reference's CUDA route launches once per item, src/backends/cublas.cc:59-104).  p.m/p.n/p.k
+// are then the capacities the tile grid is laid over; tiles outside an item's dims do nothing.
 template <typename T, int TM, int TN, int BK>
-__global__ void __launch_bounds__(256) gemm_generic_kernel(GemmParams p, long long tiles_m,
+__global__ void __launch_bounds__(256) gemm_generic_kernel(GemmParams p, HeteroDims het, long long tiles_m,
                                                            long long tiles_n) {
   constexpr int BM = 16 * TM, BN = 16 * TN;
   __shared__ T As[BK][BM + 1];
@@ -35,6 +39,10 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(GemmParams p, long lo
     const long long rem = tile - item * tiles_per_item;
     const int m0 = (int)(rem % tiles_m) * BM;
     const int n0 = (int)(rem / tiles_m) * BN;
+    if (het.m) p.m = min(het.m[item], het.cap_m);
+    if (het.n) p.n = min(het.n[item], het.cap_n);
+    if (het.k) p.k = min(het.k[item], het.cap_k);
+    if (m0 >= p.m || n0 >= p.n) continue;  // uniform across the CTA
     const T* A = (const T*)p.a + item * p.sa;
     const T* B = (const T*)p.b + item * p.sb;
     T* C = (T*)p.c + item * p.sc;
@@ -108,41 +116,46 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(GemmParams p, long lo
 }
 
 template <typename T, int TM, int TN, int BK>
-int launch_one(const GemmParams& p, cudaStream_t stream) {
+int launch_one(const GemmParams& p, const HeteroDims& het, cudaStream_t stream) {
   constexpr int BM = 16 * TM, BN = 16 * TN;
   const long long tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BN - 1) / BN;
   const long long total = tiles_m * tiles_n * (long long)p.batch;
   if (total == 0) return BLB200_OK;
   const long long cap = (long long)device_info().sm_count * 64;  // grid-stride beyond this
   const unsigned grid = (unsigned)(total < cap ? total : cap);
-  gemm_generic_kernel<T, TM, TN, BK><<<grid, 256, 0, stream>>>(p, tiles_m, tiles_n);
+  gemm_generic_kernel<T, TM, TN, BK><<<grid, 256, 0, stream>>>(p, het, tiles_m, tiles_n);
   return (int)cudaGetLastError();
 }
 
 template <typename T>
-int launch_typed(const GemmParams& p, cudaStream_t stream) {
+int launch_typed(const GemmParams& p, const HeteroDims& het, cudaStream_t stream) {
   // Small outputs take 16x16 tiles (one element per thread) so that CTAs are not mostly idle;
   // larger ones take 4x4 (real) or 2x2 (complex) register blocks.
   const bool tiny = p.m <= 16 || p.n <= 16;
-  if (tiny) return launch_one<T, 1, 1, 16>(p, stream);
+  if (tiny) return launch_one<T, 1, 1, 16>(p, het, stream);
   if (sizeof(T) <= 8 && !Scalar<T>::is_complex && p.m > 32 && p.n > 32)
-    return launch_one<T, 4, 4, 16>(p, stream);
-  return launch_one<T, 2, 2, 16>(p, stream);
+    return launch_one<T, 4, 4, 16>(p, het, stream);
+  return launch_one<T, 2, 2, 16>(p, het, stream);
 }
 
 }  // namespace
 
-int launch_generic(const GemmParams& p, int dtype, cudaStream_t stream) {
+int launch_generic_hetero(const GemmParams& p, const HeteroDims& het, int dtype, cudaStream_t stream) {
   int rc;
   switch (dtype) {
-    case BLB200_S: rc = launch_typed<float>(p, stream); break;
-    case BLB200_D: rc = launch_typed<double>(p, stream); break;
-    case BLB200_C: rc = launch_typed<float2>(p, stream); break;
-    case BLB200_Z: rc = launch_typed<double2>(p, stream); break;
+    case BLB200_S: rc = launch_typed<float>(p, het, stream); break;
+    case BLB200_D: rc = launch_typed<double>(p, het, stream); break;
+    case BLB200_C: rc = launch_typed<float2>(p, het, stream); break;
+    case BLB200_Z: rc = launch_typed<double2>(p, het, stream); break;
     default: return BLB200_E_DTYPE;
   }
-  if (rc == BLB200_OK) note_launch("generic");
+  if (rc == BLB200_OK) note_launch((het.m || het.n || het.k) ? "generic_hetero" : "generic");
   return rc;
+}
+
+int launch_generic(const GemmParams& p, int dtype, cudaStream_t stream) {
+  HeteroDims none{};
+  return launch_generic_hetero(p, none, dtype, stream);
 }
 
 }  // namespace blb200

@@ -301,7 +301,19 @@ def run_ours(args, rank, local_rank, world):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        # NCCL announces its version on stdout when the first communicator comes up; stdout must
+        # carry exactly one JSON line, so that chatter is sent to stderr.
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=device)
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
 
     def barrier():
         if world > 1:
@@ -472,7 +484,7 @@ def run_ours(args, rank, local_rank, world):
                            "global_batch": batch * world, "sharding": f"contiguous batch ranges x{world}, no collective",
                            "l2": "inputs (12.3 GB per GPU) exceed the 126 MB L2; no flush needed",
                            "seed": 42},
-                "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+                "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches) * world, "clocks": clocks,
                 "parity_worst_error_ratio": worst}
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline("C2")

@@ -292,6 +292,17 @@ class MatrixView {
   T* data_ptr() const { return data_; }
   int rows() const { return rows_; }
   int cols() const { return cols_; }
+  // Per-item active dimensions of a heterogeneous batch (device-readable int[batch], or null).
+  int rows(int b) const { return active_rows_ ? active_rows_[b] : rows_; }
+  int cols(int b) const { return active_cols_ ? active_cols_[b] : cols_; }
+  bool is_heterogeneous() const { return active_rows_ || active_cols_; }
+  const int* active_rows() const { return active_rows_; }
+  const int* active_cols() const { return active_cols_; }
+  MatrixView& set_active_dims(const int* active_rows, const int* active_cols) {
+    active_rows_ = active_rows;
+    active_cols_ = active_cols;
+    return *this;
+  }
   int ld() const { return ld_; }
   int64_t stride() const { return stride_; }
   int batch_size() const { return batch_size_; }
@@ -299,7 +310,7 @@ class MatrixView {
   T& operator()(int row, int col, int batch = 0) const { return at(row, col, batch); }
   MatrixView batch_item(int b) const {
     if (b < 0 || b >= batch_size_) throw std::out_of_range("Batch index out of range");
-    return MatrixView(data_ + (int64_t)b * stride_, rows_, cols_, ld_);
+    return MatrixView(data_ + (int64_t)b * stride_, rows(b), cols(b), ld_);
   }
   MatrixView operator[](int b) const { return batch_item(b); }
   MatrixView operator()(Slice rows, Slice cols) const {
@@ -316,6 +327,8 @@ class MatrixView {
   int rows_ = 0, cols_ = 0, ld_ = 0;
   int64_t stride_ = 0;
   int batch_size_ = 1;
+  const int* active_rows_ = nullptr;
+  const int* active_cols_ = nullptr;
 };
 
 // Owning batch of column-major matrices in managed (host-visible) memory.
@@ -381,7 +394,33 @@ class Matrix {
     std::copy(data_.get(), data_.get() + count_, m.data_.get());
     return m;
   }
-  MatrixView<T, MType> view() const { return MatrixView<T, MType>(data_.get(), rows_, cols_, ld_, stride_, batch_size_); }
+  MatrixView<T, MType> view() const {
+    MatrixView<T, MType> v(data_.get(), rows_, cols_, ld_, stride_, batch_size_);
+    if (active_) v.set_active_dims(active_.get(), active_.get() + batch_size_);
+    return v;
+  }
+  // Per-item active dims (each <= the allocated rows/cols), kept in managed memory so that both the
+  // host checks and the kernel can read them.  Empty vectors clear them.
+  Matrix& set_active_dims(const std::vector<int>& active_rows, const std::vector<int>& active_cols) {
+    if (active_rows.empty() && active_cols.empty()) {
+      active_.reset();
+      return *this;
+    }
+    if ((int)active_rows.size() != batch_size_ || (int)active_cols.size() != batch_size_)
+      throw std::invalid_argument("active dims must have one entry per batch item");
+    for (int b = 0; b < batch_size_; ++b)
+      if (active_rows[b] < 0 || active_rows[b] > rows_ || active_cols[b] < 0 || active_cols[b] > cols_)
+        throw std::invalid_argument("active dims exceed the matrix capacity");
+    void* p = nullptr;
+    detail::cuda_check(cudaMallocManaged(&p, sizeof(int) * 2 * (size_t)batch_size_), "Matrix: cudaMallocManaged");
+    active_.reset(static_cast<int*>(p), [](int* q) { cudaFree(q); });
+    std::copy(active_rows.begin(), active_rows.end(), active_.get());
+    std::copy(active_cols.begin(), active_cols.end(), active_.get() + batch_size_);
+    return *this;
+  }
+  bool is_heterogeneous() const { return (bool)active_; }
+  int rows(int b) const { return active_ ? active_.get()[b] : rows_; }
+  int cols(int b) const { return active_ ? active_.get()[batch_size_ + b] : cols_; }
   operator MatrixView<T, MType>() const { return view(); }
   T& operator()(int i, int j, int b = 0) const { return data_.get()[(int64_t)b * stride_ + (int64_t)j * ld_ + i]; }
   T* data_ptr() const { return data_.get(); }
@@ -393,6 +432,7 @@ class Matrix {
 
  private:
   std::shared_ptr<T> data_;
+  std::shared_ptr<int> active_;
   size_t count_ = 0;
   int rows_ = 0, cols_ = 0, batch_size_ = 1, ld_ = 0;
   int64_t stride_ = 0;
@@ -438,6 +478,18 @@ Event gemm(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const Matrix
   if (A.batch_size() != B.batch_size() || A.batch_size() != C.batch_size() || k != kb || C.rows() != m ||
       C.cols() != n || m < 0 || n < 0 || k < 0)
     throw std::runtime_error("GEMM: incompatible matrix dimensions");
+  const bool hetero = A.is_heterogeneous() || B.is_heterogeneous() || C.is_heterogeneous();
+  if (hetero) {
+    // per-item check on the host, as gemm_batch_dimensions_compatible does (gemm_variant.hh:29-41);
+    // the arrays are managed memory, so the queue is drained first
+    ctx.wait();
+    for (int b = 0; b < A.batch_size(); ++b) {
+      const int mi = transA == Transpose::NoTrans ? A.rows(b) : A.cols(b), ki = transA == Transpose::NoTrans ? A.cols(b) : A.rows(b);
+      const int kj = transB == Transpose::NoTrans ? B.rows(b) : B.cols(b), ni = transB == Transpose::NoTrans ? B.cols(b) : B.rows(b);
+      if (ki != kj || C.rows(b) != mi || C.cols(b) != ni || mi < 0 || ni < 0 || ki < 0)
+        throw std::runtime_error("GEMM: incompatible matrix dimensions");
+    }
+  }
   blb200_gemm_desc d{};
   d.a = A.data_ptr();
   d.b = B.data_ptr();
@@ -455,8 +507,33 @@ Event gemm(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const Matrix
   d.op_a = (int)transA;
   d.op_b = (int)transB;
   ctx.make_current();
-  detail::status_check(blb200_gemm_strided_batched(&d, ctx.native_stream()));
+  if (hetero) {
+    const int* mi = C.active_rows() ? C.active_rows() : (transA == Transpose::NoTrans ? A.active_rows() : A.active_cols());
+    const int* ni = C.active_cols() ? C.active_cols() : (transB == Transpose::NoTrans ? B.active_cols() : B.active_rows());
+    const int* ki = (transA == Transpose::NoTrans ? A.active_cols() : A.active_rows());
+    if (!ki) ki = (transB == Transpose::NoTrans ? B.active_rows() : B.active_cols());
+    detail::status_check(blb200_gemm_heterogeneous(&d, mi, ni, ki, ctx.native_stream()));
+  } else {
+    detail::status_check(blb200_gemm_strided_batched(&d, ctx.native_stream()));
+  }
   return ctx.create_event_after_external_work();
+}
+
+// gemm on views with per-item active dimensions; same call as gemm (the reference keeps both names,
+// include/blas/functions/gemm.hh:48-78).
+template <Backend Back, typename T>
+inline Event gemm_heterogeneous(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A,
+                                const MatrixView<T, MatrixFormat::Dense>& B, const MatrixView<T, MatrixFormat::Dense>& C,
+                                T alpha, T beta, Transpose transA, Transpose transB,
+                                ComputePrecision precision = ComputePrecision::Default) {
+  return gemm<Back, T>(ctx, A, B, C, alpha, beta, transA, transB, precision);
+}
+template <typename T>
+inline Event gemm_heterogeneous(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A,
+                                const MatrixView<T, MatrixFormat::Dense>& B, const MatrixView<T, MatrixFormat::Dense>& C,
+                                T alpha, T beta, Transpose transA, Transpose transB,
+                                ComputePrecision precision = ComputePrecision::Default) {
+  return gemm_heterogeneous<Backend::CUDA, T>(ctx, A, B, C, alpha, beta, transA, transB, precision);
 }
 
 template <Backend Back, typename T>

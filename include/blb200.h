@@ -85,6 +85,18 @@ int blb200_gemm_validate(const blb200_gemm_desc* desc);
  * gemm_vendor_impl's cublasGemmStridedBatchedEx (BatchLAS src/backends/cublas.cc:126-147). */
 int blb200_gemm_strided_batched(const blb200_gemm_desc* desc, void* cuda_stream);
 
+/* Heterogeneous batch: item b computes an m_items[b] x n_items[b] x k_items[b] product inside the
+ * capacity (desc->m, n, k) that ld/stride were laid out for; one launch for the whole batch.
+ * The arrays are DEVICE-readable int32[batch] (device or managed memory); a NULL array means every
+ * item uses the capacity; values above the capacity are clamped to it.  Per item the BLAS rules
+ * hold: m or n == 0 -> untouched, k == 0 -> C scaled by beta.  This is gemm on views with per-item
+ * active dimensions (BatchLAS include/blas/matrix.hh:62-63,117-124; gemm_heterogeneous,
+ * include/blas/functions/gemm.hh:48-78), which the reference's CUDA route runs as one launch per
+ * item (src/backends/cublas.cc:59-104).  The caller checks that the per-item shapes of A, B and C
+ * agree (the reference does so on the host, src/backends/gemm_variant.hh:29-41). */
+int blb200_gemm_heterogeneous(const blb200_gemm_desc* desc, const int32_t* m_items, const int32_t* n_items,
+                              const int32_t* k_items, void* cuda_stream);
+
 /* Same operation with a/b/c HOST pointers (pinned for full speed; pageable works, slower).
  * The batch is cut into chunks; chunk i+1's host->device copies and chunk i-1's device->host
  * copy overlap chunk i's kernel on three streams of `device`.  Device staging comes from the

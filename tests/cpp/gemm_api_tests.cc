@@ -128,6 +128,51 @@ void DeducedBackendMatchesExplicit(Queue& ctx) {  // backend_dispatch_tests.cc:9
   CHECK(C3(3, 5, 1) == C1(3, 5, 1));
 }
 
+template <typename T>
+void HeterogeneousBatchedGemm(Queue& ctx) {  // gemm_tests.cc:398-586
+  const int batch = 4, max_m = 40, max_n = 37, max_k = 33;
+  const std::vector<int> ms = {40, 2, 0, 17}, ns = {37, 2, 4, 33}, ks = {33, 3, 3, 0};
+  for (auto [ta, tb] : {std::pair{Transpose::NoTrans, Transpose::NoTrans}, std::pair{Transpose::Trans, Transpose::NoTrans},
+                        std::pair{Transpose::NoTrans, Transpose::ConjTrans}}) {
+    const bool an = ta == Transpose::NoTrans, bn = tb == Transpose::NoTrans;
+    auto A = an ? Matrix<T>::Random(max_m, max_k, false, batch) : Matrix<T>::Random(max_k, max_m, false, batch);
+    auto B = bn ? Matrix<T>::Random(max_k, max_n, false, batch, 9) : Matrix<T>::Random(max_n, max_k, false, batch, 9);
+    auto C = Matrix<T>::Random(max_m, max_n, false, batch, 11);
+    auto C0 = C.clone();
+    A.set_active_dims(an ? ms : ks, an ? ks : ms);
+    B.set_active_dims(bn ? ks : ns, bn ? ns : ks);
+    C.set_active_dims(ms, ns);
+    const T alpha = T(2), beta = T(0.5);
+    gemm_heterogeneous(ctx, A.view(), B.view(), C.view(), alpha, beta, ta, tb);
+    ctx.wait();
+    // inside the active window: the per-item product (k == 0 -> C scaled by beta)
+    using W = std::conditional_t<std::is_floating_point_v<T>, long double, std::complex<long double>>;
+    for (int b = 0; b < batch; ++b)
+      for (int j = 0; j < max_n; ++j)
+        for (int i = 0; i < max_m; ++i) {
+          if (i < ms[b] && j < ns[b]) {
+            W s = 0;
+            for (int l = 0; l < ks[b]; ++l) s += W(op_elem(A, ta, i, l, b)) * W(op_elem(B, tb, l, j, b));
+            W ref = W(alpha) * s + W(beta) * W(C0(i, j, b));
+            CHECK(std::abs(W(C(i, j, b)) - ref) <= tolerance<T>() * 100);
+          } else {
+            CHECK(C(i, j, b) == C0(i, j, b));  // outside the active window nothing is written
+          }
+        }
+  }
+  // mismatched per-item shapes are rejected like mismatched capacities
+  auto A = Matrix<T>::Random(8, 8, false, 2), B = Matrix<T>::Random(8, 8, false, 2), C = Matrix<T>::Zeros(8, 8, 2);
+  A.set_active_dims({8, 4}, {8, 5});
+  B.set_active_dims({8, 6}, {8, 8});
+  bool threw = false;
+  try {
+    gemm(ctx, A.view(), B.view(), C.view(), {});
+  } catch (const std::runtime_error&) {
+    threw = true;
+  }
+  CHECK(threw);
+}
+
 void OptionDefaultsAndErrors(Queue& ctx) {  // options_api_tests.cc:148-183
   GemmOptions<float> o;
   CHECK(o.alpha == 1.0f && o.beta == 0.0f && o.transA == Transpose::NoTrans && o.transB == Transpose::NoTrans &&
@@ -238,6 +283,7 @@ int main(int argc, char** argv) {
   FOR_TYPES(BatchedGemm)
   FOR_TYPES(ReferenceShapes)
   FOR_TYPES(DeducedBackendMatchesExplicit)
+  FOR_TYPES(HeterogeneousBatchedGemm)
   run("OptionDefaultsAndErrors", [&] { OptionDefaultsAndErrors(ctx); });
   run("SlicedViews", [&] { SlicedViews(ctx); });
   run("WorkspaceLeases", [&] { WorkspaceLeases(ctx); });

@@ -158,6 +158,48 @@ def test_small_kernel_rings_over_many_items(bl, size, oa, ob):
         assert np.allclose(C, Cg, rtol=2e-5, atol=2e-5), f"{kern} {oa}{ob} b{batch} vs generic"
 
 
+@pytest.mark.parametrize("dt", DTYPE_NAMES)
+def test_heterogeneous_batch_in_one_launch(bl, dt):
+    """Per-item active dims inside a common capacity (BatchLAS tests/gemm_tests.cc:398-586: includes an
+    item with m == 0 and one with k == 0, which scales C by beta).  Every item is checked against the
+    oracle as a batch-1 problem; everything outside the active windows must be untouched."""
+    code = oracle.DTYPES[dt]
+    cap_m, cap_n, cap_k = 70, 45, 50
+    ms = [70, 2, 0, 33, 17, 64]
+    ns = [45, 2, 4, 45, 0, 31]
+    ks = [50, 3, 3, 0, 9, 50]
+    batch = len(ms)
+    for oa, ob in [("N", "N"), ("T", "N"), ("N", "C"), ("C", "T")]:
+        p = oracle.make_problem(dt, oa, ob, cap_m, cap_n, cap_k, batch, alpha=scalar_for(code, 1.5),
+                                beta=scalar_for(code, -0.5))
+        A, B, C0 = make_inputs(p)
+        dA, dB, dC = (torch.from_numpy(x).cuda() for x in (A, B, C0))
+        dm, dn, dk = (torch.tensor(v, dtype=torch.int32, device="cuda") for v in (ms, ns, ks))
+        desc = bl.make_desc(dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), p.dtype, p.op_a, p.op_b, cap_m, cap_n, cap_k,
+                            batch, p.lda, p.ldb, p.ldc, p.stride_a, p.stride_b, p.stride_c, p.alpha, p.beta)
+        bl._lib.check(bl._lib.load().blb200_gemm_heterogeneous(desc, dm.data_ptr(), dn.data_ptr(), dk.data_ptr(),
+                                                               torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert bl.last_kernel_name() == "generic_hetero"
+        C = dC.cpu().numpy()
+        expect_untouched = np.ones(C.size, bool)
+        es = A.itemsize
+        for b in range(batch):
+            pi = oracle.make_problem(dt, oa, ob, ms[b], ns[b], ks[b], 1, lda=p.lda, ldb=p.ldb, ldc=p.ldc,
+                                     alpha=p.alpha, beta=p.beta)
+            sl = lambda x, st: x[b * st:]
+            bad, worst = oracle.check(pi, sl(A, p.stride_a), sl(B, p.stride_b), sl(C0, p.stride_c), sl(C, p.stride_c))
+            assert bad == 0, (dt, oa, ob, b, worst)
+            for j in range(ns[b]):
+                expect_untouched[b * p.stride_c + j * p.ldc: b * p.stride_c + j * p.ldc + ms[b]] = False
+        assert np.array_equal(C.view(np.uint8).reshape(C.size, -1)[expect_untouched],
+                              C0.view(np.uint8).reshape(C0.size, -1)[expect_untouched])
+    # null arrays fall back to the homogeneous dispatcher
+    bl._lib.check(bl._lib.load().blb200_gemm_heterogeneous(desc, None, None, None, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert bl.last_kernel_name() != "generic_hetero"
+
+
 def test_forced_kernel_that_cannot_run_reports_unsupported(bl):
     p = oracle.make_problem("d", "N", "N", 20, 20, 20, 1)
     A, B, C0 = make_inputs(p)
