@@ -18,7 +18,30 @@ struct GemmParams {
   long long sa, sb, sc;
   double alpha[2], beta[2];
   int op_a, op_b;
+  // Split-K (splits > 1): the launch walks batch * splits virtual items; virtual item v is split
+  // v % splits of item v / splits, covers k in [s*kchunk, min(k, (s+1)*kchunk)), reads A and B at
+  // element offsets s*split_a / s*split_b past the item, and writes its own partial at c + v*sc.
+  int splits, kchunk;
+  long long split_a, split_b;
 };
+
+// Resolves a virtual item into (real item, operand offsets in elements, K extent of this split).
+struct SplitView {
+  long long item, a_off, b_off;
+  int k;
+};
+__host__ __device__ inline SplitView resolve_split(const GemmParams& p, long long vitem) {
+  SplitView v{vitem, 0, 0, p.k};
+  if (p.splits > 1) {
+    const int s = (int)(vitem % p.splits);
+    v.item = vitem / p.splits;
+    v.a_off = (long long)s * p.split_a;
+    v.b_off = (long long)s * p.split_b;
+    const int left = p.k - s * p.kchunk;
+    v.k = left < 0 ? 0 : (left < p.kchunk ? left : p.kchunk);
+  }
+  return v;
+}
 
 // Optional per-item dims of a heterogeneous batch (null pointer = every item uses the capacity).
 struct HeteroDims {
@@ -121,6 +144,8 @@ int launch_small32(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_small64(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_tiled(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_dmma(const GemmParams& p, int dtype, cudaStream_t stream);
+int launch_splitk_reduce(const GemmParams& orig, int dtype, const void* partials, int splits, long long part_ld,
+                         long long part_stride, cudaStream_t stream);
 
 bool small32_supported(const GemmParams& p, int dtype);
 bool small64_supported(const GemmParams& p, int dtype);

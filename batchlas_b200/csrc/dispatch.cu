@@ -78,12 +78,17 @@ static GemmParams to_params(const blb200_gemm_desc* d) {
   p.beta[1] = cplx ? d->beta[1] : 0.0;
   p.op_a = d->op_a;
   p.op_b = d->op_b;
+  p.splits = 1;
+  p.kchunk = d->k;
+  p.split_a = p.split_b = 0;
   if (!cplx) {  // conjugation is the identity on real data
     if (p.op_a == BLB200_H) p.op_a = BLB200_T;
     if (p.op_b == BLB200_H) p.op_b = BLB200_T;
   }
   return p;
 }
+
+GemmParams to_params_public(const blb200_gemm_desc* d) { return to_params(d); }
 
 int dispatch(const blb200_gemm_desc* d, cudaStream_t stream) {
   int rc = validate(d);

@@ -91,12 +91,15 @@ __global__ void __launch_bounds__(256, 2) gemm_dmma_d_kernel(GemmParams p, int t
 
   const long long tiles_per_item = (long long)tiles_m * tiles_n;
   const long long tile = blockIdx.x;
-  const long long item = tile / tiles_per_item;
-  const int rem = (int)(tile - item * tiles_per_item);
+  const long long vitem = tile / tiles_per_item;
+  const int rem = (int)(tile - vitem * tiles_per_item);
+  const SplitView sv = resolve_split(p, vitem);
+  const long long item = sv.item;
+  p.k = sv.k;
   const int m0 = (rem % tiles_m) * BM, n0 = (rem / tiles_m) * BN;
-  const unsigned char* A = (const unsigned char*)p.a + item * p.sa * 8;
-  const unsigned char* B = (const unsigned char*)p.b + item * p.sb * 8;
-  double* C = (double*)p.c + item * p.sc;
+  const unsigned char* A = (const unsigned char*)p.a + (item * p.sa + sv.a_off) * 8;
+  const unsigned char* B = (const unsigned char*)p.b + (item * p.sb + sv.b_off) * 8;
+  double* C = (double*)p.c + vitem * p.sc;
 
   double acc[4][4][2];
 #pragma unroll
@@ -192,12 +195,15 @@ __global__ void __launch_bounds__(256, 2) gemm_dmma_z_kernel(GemmParams p, int t
 
   const long long tiles_per_item = (long long)tiles_m * tiles_n;
   const long long tile = blockIdx.x;
-  const long long item = tile / tiles_per_item;
-  const int rem = (int)(tile - item * tiles_per_item);
+  const long long vitem = tile / tiles_per_item;
+  const int rem = (int)(tile - vitem * tiles_per_item);
+  const SplitView sv = resolve_split(p, vitem);
+  const long long item = sv.item;
+  p.k = sv.k;
   const int m0 = (rem % tiles_m) * BM, n0 = (rem / tiles_m) * BN;
-  const unsigned char* A = (const unsigned char*)p.a + item * p.sa * 16;
-  const unsigned char* B = (const unsigned char*)p.b + item * p.sb * 16;
-  double2* C = (double2*)p.c + item * p.sc;
+  const unsigned char* A = (const unsigned char*)p.a + (item * p.sa + sv.a_off) * 16;
+  const unsigned char* B = (const unsigned char*)p.b + (item * p.sb + sv.b_off) * 16;
+  double2* C = (double2*)p.c + vitem * p.sc;
 
   double accr[4][2][2], acci[4][2][2];
 #pragma unroll

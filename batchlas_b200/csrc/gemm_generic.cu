@@ -34,18 +34,23 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(GemmParams p, HeteroD
   const bool conj_a = Scalar<T>::is_complex && p.op_a == BLB200_H;
   const bool conj_b = Scalar<T>::is_complex && p.op_b == BLB200_H;
 
+  const int k_full = p.k;
   for (long long tile = blockIdx.x; tile < total; tile += gridDim.x) {
-    const long long item = tile / tiles_per_item;
-    const long long rem = tile - item * tiles_per_item;
+    p.k = k_full;
+    const long long vitem = tile / tiles_per_item;
+    const long long rem = tile - vitem * tiles_per_item;
+    const SplitView sv = resolve_split(p, vitem);
+    const long long item = sv.item;
+    if (p.splits > 1) p.k = sv.k;
     const int m0 = (int)(rem % tiles_m) * BM;
     const int n0 = (int)(rem / tiles_m) * BN;
     if (het.m) p.m = min(het.m[item], het.cap_m);
     if (het.n) p.n = min(het.n[item], het.cap_n);
     if (het.k) p.k = min(het.k[item], het.cap_k);
     if (m0 >= p.m || n0 >= p.n) continue;  // uniform across the CTA
-    const T* A = (const T*)p.a + item * p.sa;
-    const T* B = (const T*)p.b + item * p.sb;
-    T* C = (T*)p.c + item * p.sc;
+    const T* A = (const T*)p.a + item * p.sa + sv.a_off;
+    const T* B = (const T*)p.b + item * p.sb + sv.b_off;
+    T* C = (T*)p.c + vitem * p.sc;
 
     T acc[TM][TN];
 #pragma unroll

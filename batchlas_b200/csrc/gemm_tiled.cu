@@ -140,12 +140,15 @@ __global__ void __launch_bounds__(Cfg::THREADS, MIN_BLOCKS)
 
   const long long tiles_per_item = (long long)tiles_m * tiles_n;
   const long long tile = blockIdx.x;
-  const long long item = tile / tiles_per_item;
-  const int rem = (int)(tile - item * tiles_per_item);
+  const long long vitem = tile / tiles_per_item;
+  const int rem = (int)(tile - vitem * tiles_per_item);
+  const SplitView sv = resolve_split(p, vitem);
+  const long long item = sv.item;
+  p.k = sv.k;
   const int m0 = (rem % tiles_m) * BM, n0 = (rem / tiles_m) * BN;
-  const T* A = (const T*)p.a + item * p.sa;
-  const T* B = (const T*)p.b + item * p.sb;
-  T* C = (T*)p.c + item * p.sc;
+  const T* A = (const T*)p.a + item * p.sa + sv.a_off;
+  const T* B = (const T*)p.b + item * p.sb + sv.b_off;
+  T* C = (T*)p.c + vitem * p.sc;
 
   T acc[TM][TN];
 #pragma unroll

@@ -62,6 +62,10 @@ def configs():
                    pad=0, dist_ab=("normal", 1.0), dist_c=("uniform", 1.0)),
         "C5": dict(dtype="d", ops=[("N", "N")], m=1024, n=1024, k=1024, batch=512, alpha=1.0, beta=1.0, pad=0,
                    dist_ab=("normal", 1.0 / 32.0), dist_c=("uniform", 1.0)),
+        # not a BASELINE configuration: a Gram-matrix shaped product (few output tiles, long k) for
+        # the split-K path, only reachable through --case SK [--splitk]
+        "SK": dict(dtype="d", ops=[("T", "N")], m=64, n=64, k=262144, batch=2, alpha=1.0, beta=0.0, pad=0,
+                   dist_ab=("normal", 1.0 / 512.0), dist_c=("uniform", 1.0)),
     }
 
 
@@ -513,10 +517,20 @@ def run_case(args):
     out = {"case": name, "batch": batch, "ops": {}}
     for o in ops:
         d = desc_for(bl, c, o, tens, mt, batch, kernel=args.kernel)
+        launch = lambda: bl.gemm_strided_batched(d)
+        if args.splitk:
+            import ctypes
+            from batchlas_b200 import _lib
+            need = ctypes.c_size_t(0)
+            splits = _lib.load().blb200_gemm_splitk_plan(d, 0, ctypes.byref(need))
+            ws = torch.empty(max(need.value, 16), dtype=torch.uint8, device="cuda")
+            stream = torch.cuda.current_stream().cuda_stream
+            launch = lambda: _lib.check(_lib.load().blb200_gemm_splitk(d, splits, ws.data_ptr(), need.value, stream))
+            out["splits"] = splits
         for _ in range(args.warmup):
-            bl.gemm_strided_batched(d)
+            launch()
         torch.cuda.synchronize()
-        ms = time_launches(torch, lambda: bl.gemm_strided_batched(d), args.steps)
+        ms = time_launches(torch, launch, args.steps)
         w = verify_sample(bl, torch, c, o, tens, mt, batch, 0, n_check=2)
         out["ops"][o[0] + o[1]] = {"ms": ms, "kernel": bl.last_kernel_name(), "worst_error_ratio": w,
                                    "gflops": flops_per_item(c) * batch / (ms * 1e-3) / 1e9,
@@ -536,6 +550,7 @@ def main():
     ap.add_argument("--case", default="", help="profiling mode: CONFIG[:OP], e.g. C2:NT or C3:TN (1 GPU)")
     ap.add_argument("--batch", type=int, default=0, help="batch override for --case")
     ap.add_argument("--kernel", default="auto", help="forced kernel for --case")
+    ap.add_argument("--splitk", action="store_true", help="--case through blb200_gemm_splitk with planned scratch")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -514,7 +514,16 @@ Event gemm(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const Matrix
     if (!ki) ki = (transB == Transpose::NoTrans ? B.active_rows() : B.active_cols());
     detail::status_check(blb200_gemm_heterogeneous(&d, mi, ni, ki, ctx.native_stream()));
   } else {
-    detail::status_check(blb200_gemm_strided_batched(&d, ctx.native_stream()));
+    // Few output tiles and a long k: split k across the GPU, scratch leased from the queue's arena
+    // for the duration of the call (the stream is in order, so the bytes may be re-lent afterwards).
+    size_t ws_bytes = 0;
+    const int splits = blb200_gemm_splitk_plan(&d, 0, &ws_bytes);
+    if (splits > 1) {
+      WorkspaceLease ws = ctx.workspace(ws_bytes);
+      detail::status_check(blb200_gemm_splitk(&d, splits, ws.data(), ws.size(), ctx.native_stream()));
+    } else {
+      detail::status_check(blb200_gemm_strided_batched(&d, ctx.native_stream()));
+    }
   }
   return ctx.create_event_after_external_work();
 }

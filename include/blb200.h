@@ -97,6 +97,21 @@ int blb200_gemm_strided_batched(const blb200_gemm_desc* desc, void* cuda_stream)
 int blb200_gemm_heterogeneous(const blb200_gemm_desc* desc, const int32_t* m_items, const int32_t* n_items,
                               const int32_t* k_items, void* cuda_stream);
 
+/* ---- split-K ---------------------------------------------------------------------------------
+ * For problems with fewer output tiles than SMs and a long k (small m x n, small batch): k is cut
+ * into `splits` chunks computed side by side into scratch partials, then summed with alpha/beta.
+ * Counterpart of the reference's experimental split-K + reduce (BatchLAS
+ * src/sycl/gemm/split_k.hh:52-162), for every dtype / op pair / shape.
+ *
+ * blb200_gemm_splitk_plan: returns the number of splits that would be used (`splits` = 0 lets the
+ * library choose; 1 = splitting does not help) and writes the scratch bytes needed.
+ * blb200_gemm_splitk: runs with caller-provided DEVICE scratch (16-byte aligned, at least the
+ * planned bytes; typically a lease from the queue's workspace arena).  Allocates nothing; falls
+ * back to the ordinary launch when the plan says 1. */
+int32_t blb200_gemm_splitk_plan(const blb200_gemm_desc* desc, int32_t splits, size_t* workspace_bytes);
+int blb200_gemm_splitk(const blb200_gemm_desc* desc, int32_t splits, void* workspace, size_t workspace_bytes,
+                       void* cuda_stream);
+
 /* Same operation with a/b/c HOST pointers (pinned for full speed; pageable works, slower).
  * The batch is cut into chunks; chunk i+1's host->device copies and chunk i-1's device->host
  * copy overlap chunk i's kernel on three streams of `device`.  Device staging comes from the

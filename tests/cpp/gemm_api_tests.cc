@@ -173,6 +173,19 @@ void HeterogeneousBatchedGemm(Queue& ctx) {  // gemm_tests.cc:398-586
   CHECK(threw);
 }
 
+template <typename T>
+void LongKUsesSplitKFromTheArena(Queue& ctx) {
+  // one small output, very long k: gemm() leases split-K scratch from the queue and gives it back
+  const size_t before = ctx.workspace_capacity();
+  GeneralCase<T>(ctx, 48, 40, 6000, 1, Transpose::Trans, Transpose::NoTrans, T(2), T(-1), 2000);
+  CHECK(std::string(blb200_last_kernel_name()) == "splitk");
+  CHECK(ctx.workspace_capacity() > before);
+  const size_t cap = ctx.workspace_capacity();
+  GeneralCase<T>(ctx, 48, 40, 6000, 1, Transpose::NoTrans, Transpose::NoTrans, T(1), T(0), 2000);
+  CHECK(ctx.workspace_capacity() == cap);  // repeated calls do not grow the arena
+  CHECK(ctx.trim_workspace());             // nothing is left leased
+}
+
 void OptionDefaultsAndErrors(Queue& ctx) {  // options_api_tests.cc:148-183
   GemmOptions<float> o;
   CHECK(o.alpha == 1.0f && o.beta == 0.0f && o.transA == Transpose::NoTrans && o.transB == Transpose::NoTrans &&
@@ -284,6 +297,7 @@ int main(int argc, char** argv) {
   FOR_TYPES(ReferenceShapes)
   FOR_TYPES(DeducedBackendMatchesExplicit)
   FOR_TYPES(HeterogeneousBatchedGemm)
+  FOR_TYPES(LongKUsesSplitKFromTheArena)
   run("OptionDefaultsAndErrors", [&] { OptionDefaultsAndErrors(ctx); });
   run("SlicedViews", [&] { SlicedViews(ctx); });
   run("WorkspaceLeases", [&] { WorkspaceLeases(ctx); });

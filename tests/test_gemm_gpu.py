@@ -200,6 +200,54 @@ def test_heterogeneous_batch_in_one_launch(bl, dt):
     assert bl.last_kernel_name() != "generic_hetero"
 
 
+def run_splitk(bl, p, A, B, C0, splits):
+    L = bl._lib.load()
+    dA, dB, dC = (torch.from_numpy(x).cuda() for x in (A, B, C0))
+    desc = bl.make_desc(dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), p.dtype, p.op_a, p.op_b, p.m, p.n, p.k, p.batch,
+                        p.lda, p.ldb, p.ldc, p.stride_a, p.stride_b, p.stride_c, p.alpha, p.beta)
+    need = ctypes.c_size_t(0)
+    used = L.blb200_gemm_splitk_plan(desc, splits, ctypes.byref(need))
+    ws = torch.empty(max(need.value, 16), dtype=torch.uint8, device="cuda")
+    bl._lib.check(L.blb200_gemm_splitk(desc, splits, ws.data_ptr(), need.value, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    return dC.cpu().numpy(), used, need.value, bl.last_kernel_name()
+
+
+@pytest.mark.parametrize("dt", DTYPE_NAMES)
+def test_split_k_matches_the_oracle(bl, dt):
+    """Long-k, few-tile problems computed as side-by-side k chunks into scratch partials plus a
+    reduce pass (the reference's experimental split-K, src/sycl/gemm/split_k.hh:52-162)."""
+    code = oracle.DTYPES[dt]
+    ops = ["N", "T"] if dt in "sd" else ["N", "C"]
+    for oa in ops:
+        for ob in ops:
+            for (m, n, k, batch, splits, beta) in [(64, 48, 1000, 2, 4, 0.5), (33, 17, 515, 1, 7, 0.0),
+                                                   (128, 64, 2048, 1, 0, 1.0), (20, 10, 300, 3, 3, -1.0)]:
+                p = oracle.make_problem(dt, oa, ob, m, n, k, batch, ldc=m + 3, alpha=scalar_for(code, 1.25),
+                                        beta=scalar_for(code, beta))
+                A, B, C0 = make_inputs(p)
+                C, used, need, kern = run_splitk(bl, p, A, B, C0, splits)
+                assert used >= 2 and need > 0 and kern == "splitk", (m, n, k, used, kern)
+                assert_parity(p, A, B, C0, C, what=f"splitk {dt} {oa}{ob} {m}x{n}x{k} s={used}")
+
+
+def test_split_k_plan_declines_when_the_gpu_is_already_full(bl):
+    L = bl._lib.load()
+    need = ctypes.c_size_t(7)
+    d = bl.make_desc(16, 16, 16, 1, 0, 0, 256, 256, 256, 2048, 256, 256, 256, 65536, 65536, 65536)
+    assert L.blb200_gemm_splitk_plan(d, 0, ctypes.byref(need)) == 1 and need.value == 0
+    d = bl.make_desc(16, 16, 16, 1, 0, 0, 64, 64, 100000, 1, 64, 100000, 64, 0, 0, 0)
+    s = L.blb200_gemm_splitk_plan(d, 0, ctypes.byref(need))
+    assert 2 <= s <= 64 and need.value == s * 64 * 64 * 8
+    # too little scratch is refused, not overrun
+    p = oracle.make_problem("d", "N", "N", 64, 64, 4096, 1)
+    A, B, C0 = make_inputs(p)
+    dA, dB, dC = (torch.from_numpy(x).cuda() for x in (A, B, C0))
+    desc = bl.make_desc(dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 1, 0, 0, 64, 64, 4096, 1, 64, 4096, 64, 0, 0, 0)
+    ws = torch.empty(1024, dtype=torch.uint8, device="cuda")
+    assert L.blb200_gemm_splitk(desc, 8, ws.data_ptr(), 1024, None) == bl._lib.E_TOO_LARGE
+
+
 def test_forced_kernel_that_cannot_run_reports_unsupported(bl):
     p = oracle.make_problem("d", "N", "N", 20, 20, 20, 1)
     A, B, C0 = make_inputs(p)
