@@ -8,6 +8,8 @@
 // from the calling queue's workspace arena instead of a fresh allocation.
 //
 // A second entry point keeps the scratch in a fixed device array for callers that cannot allocate.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace blb200 {
@@ -133,9 +135,54 @@ int launch_splitk_reduce(const GemmParams& orig, int dtype, const void* partials
   }
 }
 
+// ---- fixed scratch for callers that must not allocate ----------------------------------------------
+// The partials of blb200_gemm_splitk_static live in this array.  It is part of the library image:
+// every GPU that loads the library sets the bytes aside until the process exits.
+constexpr size_t kStaticScratchBytes = (size_t)8 << 20;
+static __device__ __align__(256) unsigned char g_splitk_static_scratch[kStaticScratchBytes];
+
+// Device address of the array on the current device.  In host code the array's name is only a
+// handle for the runtime, not something a kernel can dereference, so the address is asked for
+// once per device (with that device current) and remembered.
+static int static_scratch_address(void** out) {
+  static std::mutex mu;
+  static void* cached[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return BLB200_E_NO_DEVICE;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_splitk_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (!ptr) return BLB200_E_INTERNAL;
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return BLB200_OK;
+}
+
 }  // namespace blb200
 
 extern "C" {
+
+size_t blb200_gemm_splitk_static_capacity(void) { return blb200::kStaticScratchBytes; }
+
+int blb200_gemm_splitk_static(const blb200_gemm_desc* desc, int32_t splits, void* cuda_stream) {
+  int rc = blb200_gemm_validate(desc);
+  if (rc != BLB200_OK) return rc;
+  if (desc->m == 0 || desc->n == 0 || desc->batch == 0) return BLB200_OK;
+  const blb200::SplitPlan pl = blb200::plan_split(*desc, splits);
+  if (pl.splits < 2) return blb200::dispatch(desc, (cudaStream_t)cuda_stream);  // needs no scratch at all
+  if (pl.bytes > blb200::kStaticScratchBytes) return BLB200_E_TOO_LARGE;
+  void* scratch = nullptr;
+  rc = blb200::static_scratch_address(&scratch);
+  if (rc != BLB200_OK) return rc;
+  // Every element of every partial window is written by the tile kernel before the reduce pass
+  // reads it, so nothing left over from an earlier call has to be cleared first.
+  return blb200::run_splitk(desc, pl, scratch, (cudaStream_t)cuda_stream);
+}
 
 int32_t blb200_gemm_splitk_plan(const blb200_gemm_desc* desc, int32_t splits, size_t* workspace_bytes) {
   if (workspace_bytes) *workspace_bytes = 0;

@@ -112,6 +112,31 @@ int32_t blb200_gemm_splitk_plan(const blb200_gemm_desc* desc, int32_t splits, si
 int blb200_gemm_splitk(const blb200_gemm_desc* desc, int32_t splits, void* workspace, size_t workspace_bytes,
                        void* cuda_stream);
 
+/* Split-K for callers that are not allowed to allocate device memory.  (No counterpart in the
+ * reference: it always takes its split-K partials from a freshly allocated Matrix.)
+ *
+ * Who needs it: a host program that has handed the whole of HBM to its own pool, a plug-in whose
+ * embedding runtime owns the allocator, or a latency-critical loop in which a call into the CUDA
+ * allocator (which may synchronise the device or fail late) is forbidden.  Such callers cannot
+ * produce the scratch that blb200_gemm_splitk asks for, and cannot let the library call
+ * cudaMalloc for them either.
+ *
+ * This variant therefore keeps the partials in one fixed array inside the library image,
+ * blb200_gemm_splitk_static_capacity() bytes (8 MiB) on every GPU that loads the library, held
+ * until the process exits.  It calls no cudaMalloc, cudaFree or other allocating routine.  A/B/C
+ * are passed exactly as for blb200_gemm_splitk.
+ *   - A plan that needs more scratch than the capacity is refused with BLB200_E_TOO_LARGE
+ *     ("problem exceeds the fixed capacity of this entry point"); ask blb200_gemm_splitk_plan for
+ *     the bytes beforehand, or pass a smaller `splits`.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current).  Make that first call during start-up, before any stream capture begins.
+ *   - All calls share the one array, and it keeps whatever the previous call left in it.  The
+ *     kernels overwrite every partial element they later read, so no clearing is needed; but two
+ *     calls that can overlap on the GPU (different streams, different host threads) race on the
+ *     array.  Keep calls to this entry point ordered on one stream per device. */
+size_t blb200_gemm_splitk_static_capacity(void);
+int blb200_gemm_splitk_static(const blb200_gemm_desc* desc, int32_t splits, void* cuda_stream);
+
 /* Same operation with a/b/c HOST pointers (pinned for full speed; pageable works, slower).
  * The batch is cut into chunks; chunk i+1's host->device copies and chunk i-1's device->host
  * copy overlap chunk i's kernel on three streams of `device`.  Device staging comes from the
