@@ -240,10 +240,7 @@ int launch32(const GemmParams& p, cudaStream_t stream) {
 // =================================================================================================
 // small64
 // =================================================================================================
-constexpr int kPairs64 = 4;
-constexpr int kSlotsPerPair64 = 3;
-constexpr int kSlots64 = kPairs64 * kSlotsPerPair64;  // 12 half-K slots
-constexpr int kThreads64 = 32 * (1 + 2 * kPairs64);
+constexpr int kSlots64 = 12;  // half-K slots; PAIRS warp pairs own kSlots64 / PAIRS of them each
 constexpr int kHalfBytes64 = 32 * 64 * 4;             // one operand, half of K: 8 KiB
 constexpr int kSlotBytes64 = 2 * kHalfBytes64;        // A half + B half
 constexpr int kMatElems64 = 64 * 64;
@@ -392,11 +389,13 @@ __device__ __forceinline__ void tma_load_3d(void* dst_smem, const CUtensorMap* m
 
 // Pair p's q-th half-item lives in slot p*3 + q % 3 (round q / 3); half-item q is half q & 1 of
 // the pair's (q >> 1)-th item.  Producer lane l < 12 owns slot l.
-template <bool A_KMAJOR, bool B_KMAJOR, bool HAS_C>
-__global__ void __launch_bounds__(kThreads64, 1)
+template <int PAIRS, bool A_KMAJOR, bool B_KMAJOR, bool HAS_C>
+__global__ void __launch_bounds__(32 * (1 + 2 * PAIRS), 1)
     gemm_small64_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
                         long long sa, long long sb, long long sc, int batch, float alpha, float beta,
                         const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b) {
+  constexpr int kPairs64 = PAIRS, kSlotsPerPair64 = kSlots64 / PAIRS;
+  static_assert(kSlots64 % PAIRS == 0 && kSlotsPerPair64 >= 2, "every pair owns the same number (>= 2) of slots");
   extern __shared__ unsigned char smem_raw[];
   // the 128-byte swizzle is a function of the shared-memory address: slots must be 1024-byte aligned
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -540,7 +539,7 @@ int make_kmajor_map64(CUtensorMap* map, const float* base, long long stride_elem
   return r == CUDA_SUCCESS ? BLB200_OK : BLB200_E_INTERNAL;
 }
 
-template <bool AK, bool BK, bool HC>
+template <int PAIRS, bool AK, bool BK, bool HC>
 int launch64(const GemmParams& p, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
   const size_t smem = (size_t)kSlots64 * kSlotBytes64 + (size_t)kSlots64 * 2 * sizeof(uint64_t) + 1024;
@@ -556,7 +555,7 @@ int launch64(const GemmParams& p, cudaStream_t stream) {
     int rc = make_kmajor_map64(&map_b, (const float*)p.b, p.batch > 1 ? p.sb : kMatElems64, p.batch);
     if (rc != BLB200_OK) return rc;
   }
-  auto kern = gemm_small64_kernel<AK, BK, HC>;
+  auto kern = gemm_small64_kernel<PAIRS, AK, BK, HC>;
   static thread_local int configured_for = -1;
   int cur = 0;
   cudaGetDevice(&cur);
@@ -566,7 +565,7 @@ int launch64(const GemmParams& p, cudaStream_t stream) {
     configured_for = cur;
   }
   const int grid = p.batch < dev.sm_count ? p.batch : dev.sm_count;
-  kern<<<grid, kThreads64, smem, stream>>>((const float*)p.a, (const float*)p.b, (float*)p.c, p.sa, p.sb, p.sc,
+  kern<<<grid, 32 * (1 + 2 * PAIRS), smem, stream>>>((const float*)p.a, (const float*)p.b, (float*)p.c, p.sa, p.sb, p.sc,
                                            p.batch, (float)p.alpha[0], (float)p.beta[0], map_a, map_b);
   return (int)cudaGetLastError();
 }
@@ -619,10 +618,12 @@ int launch_small64(const GemmParams& p, int dtype, cudaStream_t stream) {
   const bool ak = p.op_a != BLB200_N;
   const bool bk = p.op_b == BLB200_N;
   const bool hc = (float)p.beta[0] != 0.f;
+  static const int pairs = env_int("BLB200_SMALL64_PAIRS", 4);  // tuning knob: 4 or 6 warp pairs
   int rc;
-#define BLB_CASE(a, b)                                                              \
-  if (ak == a && bk == b) {                                                         \
-    rc = hc ? launch64<a, b, true>(p, stream) : launch64<a, b, false>(p, stream);   \
+#define BLB_CASE(a, b)                                                                               \
+  if (ak == a && bk == b) {                                                                          \
+    if (pairs == 6) rc = hc ? launch64<6, a, b, true>(p, stream) : launch64<6, a, b, false>(p, stream); \
+    else rc = hc ? launch64<4, a, b, true>(p, stream) : launch64<4, a, b, false>(p, stream);         \
   } else
   BLB_CASE(false, false) BLB_CASE(false, true) BLB_CASE(true, false) BLB_CASE(true, true) { rc = BLB200_E_INTERNAL; }
 #undef BLB_CASE
