@@ -144,6 +144,7 @@ int launch_small32(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_small64(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_tiled(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_dmma(const GemmParams& p, int dtype, cudaStream_t stream);
+int launch_sgemm128(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_splitk_reduce(const GemmParams& orig, int dtype, const void* partials, int splits, long long part_ld,
                          long long part_stride, cudaStream_t stream);
 
@@ -151,6 +152,7 @@ bool small32_supported(const GemmParams& p, int dtype);
 bool small64_supported(const GemmParams& p, int dtype);
 bool tiled_supported(const GemmParams& p, int dtype);
 bool dmma_supported(const GemmParams& p, int dtype);
+bool sgemm128_supported(const GemmParams& p, int dtype);
 
 // Device properties cached per device.
 struct DeviceInfo {

@@ -47,7 +47,7 @@ static int validate(const blb200_gemm_desc* d) {
   if (d->ldb < (b_rows > 1 ? b_rows : 1)) return BLB200_E_SHAPE;
   if (d->ldc < (d->m > 1 ? d->m : 1)) return BLB200_E_SHAPE;
   if (d->stride_a < 0 || d->stride_b < 0 || d->stride_c < 0) return BLB200_E_SHAPE;
-  if (d->kernel_hint < BLB200_K_AUTO || d->kernel_hint > BLB200_K_DMMA) return BLB200_E_UNSUPPORTED;
+  if (d->kernel_hint < BLB200_K_AUTO || d->kernel_hint > BLB200_K_SGEMM128) return BLB200_E_UNSUPPORTED;
   const bool has_work = d->m > 0 && d->n > 0 && d->batch > 0;
   if (has_work) {
     if (!d->c) return BLB200_E_NULL;
@@ -101,11 +101,13 @@ int dispatch(const blb200_gemm_desc* d, cudaStream_t stream) {
     case BLB200_K_SMALL64: return launch_small64(p, d->dtype, stream);
     case BLB200_K_TILED: return launch_tiled(p, d->dtype, stream);
     case BLB200_K_DMMA: return launch_dmma(p, d->dtype, stream);
+    case BLB200_K_SGEMM128: return launch_sgemm128(p, d->dtype, stream);
     default: break;
   }
   if (small32_supported(p, d->dtype)) return launch_small32(p, d->dtype, stream);
   if (small64_supported(p, d->dtype)) return launch_small64(p, d->dtype, stream);
   if (dmma_supported(p, d->dtype)) return launch_dmma(p, d->dtype, stream);
+  if (sgemm128_supported(p, d->dtype)) return launch_sgemm128(p, d->dtype, stream);
   if (tiled_supported(p, d->dtype)) return launch_tiled(p, d->dtype, stream);
   return launch_generic(p, d->dtype, stream);
 }

@@ -114,6 +114,7 @@ int run_splitk(const blb200_gemm_desc* d, const SplitPlan& pl, void* scratch, cu
   p.split_b = (orig.op_b == BLB200_N) ? pl.kchunk : (long long)pl.kchunk * orig.ldb;
   int rc;
   if (dmma_supported(p, d->dtype)) rc = launch_dmma(p, d->dtype, stream);
+  else if (sgemm128_supported(p, d->dtype)) rc = launch_sgemm128(p, d->dtype, stream);
   else if (tiled_supported(p, d->dtype)) rc = launch_tiled(p, d->dtype, stream);
   else rc = launch_generic(p, d->dtype, stream);
   if (rc != BLB200_OK) return rc;

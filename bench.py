@@ -62,6 +62,16 @@ def configs():
                    pad=0, dist_ab=("normal", 1.0), dist_c=("uniform", 1.0)),
         "C5": dict(dtype="d", ops=[("N", "N")], m=1024, n=1024, k=1024, batch=512, alpha=1.0, beta=1.0, pad=0,
                    dist_ab=("normal", 1.0 / 32.0), dist_c=("uniform", 1.0)),
+        # the reference's own published SGEMM shapes (RTX 4090 numbers in experiments/sycl_vs_cuda/FINDINGS.md:
+        # 512^3 b512, 1024^3 b64, 256^3 b1024, beta = 1), reachable through --case S512 / S1024 / S256
+        "S512": dict(dtype="s", ops=[("N", "N")], m=512, n=512, k=512, batch=512, alpha=1.0, beta=1.0, pad=0,
+                     dist_ab=("uniform", 1.0), dist_c=("uniform", 1.0)),
+        "S1024": dict(dtype="s", ops=[("N", "N")], m=1024, n=1024, k=1024, batch=64, alpha=1.0, beta=1.0, pad=0,
+                      dist_ab=("uniform", 1.0), dist_c=("uniform", 1.0)),
+        "S256": dict(dtype="s", ops=[("N", "N")], m=256, n=256, k=256, batch=1024, alpha=1.0, beta=1.0, pad=0,
+                     dist_ab=("uniform", 1.0), dist_c=("uniform", 1.0)),
+        "S128": dict(dtype="s", ops=[("N", "N")], m=128, n=128, k=128, batch=4096, alpha=1.0, beta=1.0, pad=0,
+                     dist_ab=("uniform", 1.0), dist_c=("uniform", 1.0)),
         # not a BASELINE configuration: a Gram-matrix shaped product (few output tiles, long k) for
         # the split-K path, only reachable through --case SK [--splitk]
         "SK": dict(dtype="d", ops=[("T", "N")], m=64, n=64, k=262144, batch=2, alpha=1.0, beta=0.0, pad=0,

@@ -50,7 +50,8 @@ enum {
   BLB200_K_SMALL32 = 2, /* whole 32x32x32 float matrices per warp, TMA bulk-copy ring           */
   BLB200_K_SMALL64 = 3, /* whole 64x64x64 float matrices per warp pair, TMA ring (tiled+bulk)   */
   BLB200_K_TILED = 4,   /* register-blocked FFMA/DFMA smem tiles fed by 16-byte async copies    */
-  BLB200_K_DMMA = 5     /* FP64 tensor-core (mma.sync m8n8k4) tiles, double and complex<double> */
+  BLB200_K_DMMA = 5,    /* FP64 tensor-core (mma.sync m8n8k4) tiles, double and complex<double> */
+  BLB200_K_SGEMM128 = 6 /* float, A not transposed: 128x128x32 tiles, 8x8 blocks, packed FP32 FMA */
 };
 
 /*

@@ -55,6 +55,7 @@ def test_validate_follows_reference_shape_rules(lib):
     assert v(_desc(a=0, k=0)) == 0                 # k == 0 never touches A or B
     assert v(_desc(a=0, b=0, c=0, m=0)) == 0       # empty output is a no-op
     assert v(_desc(kernel_hint=99)) == _lib.E_UNSUPPORTED
+    assert v(_desc(kernel_hint=_lib.K_SGEMM128)) == 0
     assert lib.blb200_status_string(_lib.E_SHAPE).decode() == "GEMM: incompatible matrix dimensions"
 
 

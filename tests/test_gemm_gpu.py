@@ -140,6 +140,28 @@ def test_both_fp64_tile_kernels_on_ragged_and_aligned_shapes(bl, kernel, dt):
                 assert_parity(p, A, B, C0, C, what=f"{kernel} {dt} {oa}{ob} {m}x{n}x{k}")
 
 
+def test_large_float_tiles_with_packed_fma(bl):
+    """sgemm128 (A not transposed, B either way): aligned and ragged shapes, beta on and off; the
+    float shapes the reference tunes by hand (256^3 aligned, 200 x 130 x 70 ragged with alpha = 2,
+    beta = -1: tests/gemm_tests.cc:1964-2033)."""
+    for ob in ["N", "T"]:
+        for (m, n, k, batch, alpha, beta) in [(256, 256, 256, 2, 1.0, 0.0), (200, 130, 70, 3, 2.0, -1.0),
+                                             (128, 128, 128, 2, 1.0, 1.0), (64, 68, 33, 2, 1.5, 0.0),
+                                             (512, 256, 96, 1, 1.0, 0.5), (132, 260, 257, 1, -1.0, 1.0), (196, 132, 76, 2, 2.0, -1.0),
+                                             (100, 260, 44, 1, 1.0, 0.0)]:
+            p = oracle.make_problem("s", "N", ob, m, n, k, batch, alpha=alpha, beta=beta)
+            A, B, C0 = make_inputs(p)
+            C, kern = run_device(bl, p, A, B, C0)
+            aligned = p.lda % 4 == 0 and p.ldb % 4 == 0 and p.ldc % 4 == 0
+            assert kern == ("sgemm128" if aligned else "generic"), kern  # unaligned ld must decline the fast path
+            assert_parity(p, A, B, C0, C, what=f"{kern} N{ob} {m}x{n}x{k}")
+            Cn = C0.copy()
+            Cn[:] = np.nan if beta == 0.0 else Cn
+            if beta == 0.0:
+                C2, _ = run_device(bl, p, A, B, Cn)
+                assert not np.isnan(C2[: p.alloc_len("c")]).any()
+
+
 @pytest.mark.parametrize("size", [32, 64])
 @pytest.mark.parametrize("oa", ["N", "T"])
 @pytest.mark.parametrize("ob", ["N", "T"])
