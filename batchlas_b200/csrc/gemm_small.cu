@@ -414,8 +414,15 @@ __global__ void __launch_bounds__(32 * (1 + 2 * PAIRS), 1)
 
   const int my_items = (batch > (int)blockIdx.x) ? (batch - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
+  // Programmatic dependent launch: let the next kernel in the stream place its CTAs on SMs as this
+  // grid drains (its barrier set-up then overlaps our tail), and do not touch global memory until
+  // every earlier grid in the stream has finished.  Only the producer lanes need the second half:
+  // consumers see memory only through data those lanes fetched afterwards.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
   if (warp == 0) {
     if (lane < kSlots64) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       const int pair = lane / kSlotsPerPair64, i = lane % kSlotsPerPair64;
       // items of this pair: pair, pair + 4, ...
       const int pair_items = (my_items > pair) ? (my_items - 1 - pair) / kPairs64 + 1 : 0;
@@ -463,6 +470,14 @@ __global__ void __launch_bounds__(32 * (1 + 2 * PAIRS), 1)
       }
     }
 
+    if constexpr (PM != kScalar) {
+      // alpha is applied to the packed accumulators (32 packed multiplies, none when alpha == 1)
+      if (alpha != 1.f) {
+        const uint64_t al2 = dup2(alpha);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) asm("mul.rn.f32x2 %0, %0, %1;" : "+l"(accp[i]) : "l"(al2));
+      }
+    }
     if constexpr (PM == kRowPairs) {
 #pragma unroll
       for (int rp = 0; rp < 4; ++rp)
@@ -484,7 +499,7 @@ __global__ void __launch_bounds__(32 * (1 + 2 * PAIRS), 1)
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
           float* dst = Cg + col * 64 + ti + 8 * r;
-          float o = alpha * acc[r][c];
+          float o = (PM == kScalar) ? alpha * acc[r][c] : acc[r][c];
           if (HAS_C) o = fmaf(beta, *dst, o);
           *dst = o;
         }
@@ -492,8 +507,10 @@ __global__ void __launch_bounds__(32 * (1 + 2 * PAIRS), 1)
         float4* dst = reinterpret_cast<float4*>(Cg + col * 64);
 #pragma unroll
         for (int hgh = 0; hgh < 2; ++hgh) {
-          float4 o = make_float4(alpha * acc[4 * hgh][c], alpha * acc[4 * hgh + 1][c], alpha * acc[4 * hgh + 2][c],
-                                 alpha * acc[4 * hgh + 3][c]);
+          float4 o = make_float4(acc[4 * hgh][c], acc[4 * hgh + 1][c], acc[4 * hgh + 2][c], acc[4 * hgh + 3][c]);
+          if (PM == kScalar) {
+            o.x *= alpha; o.y *= alpha; o.z *= alpha; o.w *= alpha;
+          }
           if (HAS_C) {
             const float4 pr = dst[8 * hgh + ti];
             o.x = fmaf(beta, pr.x, o.x);
@@ -565,9 +582,20 @@ int launch64(const GemmParams& p, cudaStream_t stream) {
     configured_for = cur;
   }
   const int grid = p.batch < dev.sm_count ? p.batch : dev.sm_count;
-  kern<<<grid, 32 * (1 + 2 * PAIRS), smem, stream>>>((const float*)p.a, (const float*)p.b, (float*)p.c, p.sa, p.sb, p.sc,
-                                           p.batch, (float)p.alpha[0], (float)p.beta[0], map_a, map_b);
-  return (int)cudaGetLastError();
+  static const int use_pdl = env_int("BLB200_PDL", 1);  // 0 switches programmatic dependent launch off
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(32 * (1 + 2 * PAIRS));
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl ? 1 : 0;
+  return (int)cudaLaunchKernelEx(&cfg, kern, (const float*)p.a, (const float*)p.b, (float*)p.c, (long long)p.sa,
+                                 (long long)p.sb, (long long)p.sc, p.batch, (float)p.alpha[0], (float)p.beta[0], map_a,
+                                 map_b);
 }
 
 }  // namespace
