@@ -56,6 +56,7 @@ SIGNATURES = {
     "blb200_launch_count": (ctypes.c_uint64, []),
     "blb200_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "blb200_version": (ctypes.c_char_p, []),
+    "blb200_trace_flush": (ctypes.c_int, []),
     "blb200_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
     "blb200_arena_create": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p)]),
     "blb200_arena_destroy": (ctypes.c_int, [ctypes.c_void_p]),

@@ -2,7 +2,10 @@
 // The device-pointer launcher allocates nothing and never synchronises.
 #include <mutex>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
+#include <string>
+#include <vector>
 
 #include "common.cuh"
 
@@ -15,6 +18,78 @@ void note_launch(const char* kernel_name) {
   t_last_kernel = kernel_name;
   ++t_launches;
 }
+
+// ---- environment knobs (conventions of BatchLAS include/util/env.hh) -------------------------------
+// BATCHLAS_GEMM_B200_KERNEL=<generic|small32|small64|tiled|dmma|sgemm128>  forces a kernel for calls
+//   that leave kernel_hint at 0 (the role BATCHLAS_GEMM_SYCL_KERNEL plays for the reference's SYCL
+//   family, src/sycl/gemm_kernels.cc:270-329); a problem the forced kernel cannot run is dispatched
+//   normally.
+// BATCHLAS_KERNEL_TRACE=1 [BATCHLAS_KERNEL_TRACE_PATH=file]  brackets every launch with CUDA events
+//   and writes a Chrome trace at exit (the reference's kernel tracer, src/util/kernel-trace.hh:46-215).
+static int env_forced_kernel() {
+  static const int forced = [] {
+    const char* v = getenv("BATCHLAS_GEMM_B200_KERNEL");
+    if (!v || !*v) return (int)BLB200_K_AUTO;
+    const struct { const char* name; int id; } names[] = {
+        {"generic", BLB200_K_GENERIC}, {"small32", BLB200_K_SMALL32}, {"small64", BLB200_K_SMALL64},
+        {"tiled", BLB200_K_TILED},     {"dmma", BLB200_K_DMMA},       {"sgemm128", BLB200_K_SGEMM128}};
+    for (const auto& n : names)
+      if (strcmp(v, n.name) == 0) return n.id;
+    return (int)BLB200_K_AUTO;
+  }();
+  return forced;
+}
+
+namespace {
+struct TraceRecord {
+  std::string name;
+  cudaEvent_t start, stop;
+  int device;
+  long long m, n, k, batch;
+};
+struct Tracer {
+  bool enabled = false;
+  std::string path;
+  std::mutex mu;
+  std::vector<TraceRecord> records;
+  Tracer() {
+    const char* v = getenv("BATCHLAS_KERNEL_TRACE");
+    enabled = v && *v && strcmp(v, "0") != 0;
+    const char* pth = getenv("BATCHLAS_KERNEL_TRACE_PATH");
+    path = (pth && *pth) ? pth : "batchlas_b200_trace.json";
+  }
+  ~Tracer() { dump(); }
+  void dump() {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!enabled || records.empty()) return;
+    FILE* f = fopen(path.c_str(), "w");
+    if (!f) return;
+    fprintf(f, "{\"traceEvents\":[\n");
+    cudaEvent_t origin = records.front().start;
+    bool first = true;
+    for (auto& r : records) {
+      cudaSetDevice(r.device);
+      if (cudaEventSynchronize(r.stop) != cudaSuccess) continue;
+      float t0 = 0.f, dur = 0.f;
+      if (r.device == records.front().device) cudaEventElapsedTime(&t0, origin, r.start);
+      cudaEventElapsedTime(&dur, r.start, r.stop);
+      fprintf(f, "%s{\"name\":\"%s\",\"ph\":\"X\",\"pid\":%d,\"tid\":0,\"ts\":%.3f,\"dur\":%.3f,"
+                 "\"args\":{\"m\":%lld,\"n\":%lld,\"k\":%lld,\"batch\":%lld}}",
+              first ? "" : ",\n", r.name.c_str(), r.device, t0 * 1e3, dur * 1e3, r.m, r.n, r.k, r.batch);
+      first = false;
+      cudaEventDestroy(r.stop);
+      if (r.start != origin) cudaEventDestroy(r.start);
+    }
+    fprintf(f, "\n]}\n");
+    fclose(f);
+    records.clear();
+  }
+};
+Tracer& tracer() {
+  static Tracer t;
+  return t;
+}
+}  // namespace
 
 const DeviceInfo& device_info() {
   static DeviceInfo infos[64];
@@ -90,11 +165,44 @@ static GemmParams to_params(const blb200_gemm_desc* d) {
 
 GemmParams to_params_public(const blb200_gemm_desc* d) { return to_params(d); }
 
+static int dispatch_untraced(const blb200_gemm_desc* d, cudaStream_t stream);
+
 int dispatch(const blb200_gemm_desc* d, cudaStream_t stream) {
+  Tracer& tr = tracer();
+  if (!tr.enabled) return dispatch_untraced(d, stream);
+  TraceRecord rec{};
+  cudaGetDevice(&rec.device);
+  if (cudaEventCreate(&rec.start) != cudaSuccess || cudaEventCreate(&rec.stop) != cudaSuccess)
+    return dispatch_untraced(d, stream);
+  cudaEventRecord(rec.start, stream);
+  const int rc = dispatch_untraced(d, stream);
+  cudaEventRecord(rec.stop, stream);
+  if (d) {
+    rec.m = d->m; rec.n = d->n; rec.k = d->k; rec.batch = d->batch;
+  }
+  rec.name = std::string("gemm.") + t_last_kernel;
+  std::lock_guard<std::mutex> lock(tr.mu);
+  tr.records.push_back(rec);
+  return rc;
+}
+
+static int dispatch_untraced(const blb200_gemm_desc* d, cudaStream_t stream) {
   int rc = validate(d);
   if (rc != BLB200_OK) return rc;
   if (d->m == 0 || d->n == 0 || d->batch == 0) return BLB200_OK;
   const GemmParams p = to_params(d);
+  if (d->kernel_hint == BLB200_K_AUTO && env_forced_kernel() != BLB200_K_AUTO) {
+    const int dt = d->dtype;
+    switch (env_forced_kernel()) {
+      case BLB200_K_GENERIC: return launch_generic(p, dt, stream);
+      case BLB200_K_SMALL32: if (small32_supported(p, dt)) return launch_small32(p, dt, stream); break;
+      case BLB200_K_SMALL64: if (small64_supported(p, dt)) return launch_small64(p, dt, stream); break;
+      case BLB200_K_TILED: if (tiled_supported(p, dt)) return launch_tiled(p, dt, stream); break;
+      case BLB200_K_DMMA: if (dmma_supported(p, dt)) return launch_dmma(p, dt, stream); break;
+      case BLB200_K_SGEMM128: if (sgemm128_supported(p, dt)) return launch_sgemm128(p, dt, stream); break;
+      default: break;
+    }
+  }
   switch (d->kernel_hint) {
     case BLB200_K_GENERIC: return launch_generic(p, d->dtype, stream);
     case BLB200_K_SMALL32: return launch_small32(p, d->dtype, stream);
@@ -141,6 +249,11 @@ int blb200_gemm_strided_batched(const blb200_gemm_desc* desc, void* cuda_stream)
 const char* blb200_last_kernel_name(void) { return blb200::t_last_kernel; }
 uint64_t blb200_launch_count(void) { return blb200::t_launches; }
 const char* blb200_version(void) { return "0.1"; }
+
+int blb200_trace_flush(void) {
+  blb200::tracer().dump();
+  return BLB200_OK;
+}
 
 const char* blb200_status_string(int status) {
   switch (status) {

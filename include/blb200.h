@@ -156,6 +156,11 @@ uint64_t blb200_launch_count(void);
 const char* blb200_status_string(int status);
 /* Library version, "major.minor". */
 const char* blb200_version(void);
+/* With BATCHLAS_KERNEL_TRACE=1 in the environment every launch is bracketed by CUDA events and a
+ * Chrome trace (BATCHLAS_KERNEL_TRACE_PATH, default batchlas_b200_trace.json) is written at process
+ * exit; this writes it now (waits for the recorded launches) and clears the record.  Tracing
+ * mirrors BatchLAS src/util/kernel-trace.hh:46-215.  No-op when tracing is off. */
+int blb200_trace_flush(void);
 /* Synchronises the current device and reports whether any kernel of this library ever gave up
  * on one of its bounded waits: *out = 0 when none did, else a small code naming the wait. */
 int blb200_device_status(int* out);
