@@ -120,7 +120,10 @@ __device__ __forceinline__ void mma32(const float4* __restrict__ As4, const floa
 
 // Shared memory: `stages` x {A, B[, C]} of 4 KiB each, then full[stages], empty[stages] barriers.
 // `stages` is a multiple of the consumer warp count CW and at most 32 (one producer lane per stage).
-template <int CW, bool A_KMAJOR, bool B_KMAJOR, bool HAS_C>
+// TRANS_OUT: the lane's 4 x 8 block is a block of C^T (used for op pair TT, which is computed as
+// C^T = B_stored * A_stored with the operands swapped by the launcher, i.e. through the NN fragment
+// path); the epilogue then writes row 8tj..8tj+7 of column 4ti+r as two float4.
+template <int CW, bool A_KMAJOR, bool B_KMAJOR, bool HAS_C, bool TRANS_OUT = false>
 __global__ void __launch_bounds__(32 * (1 + CW), 1)
     gemm_small32_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
                         long long sa, long long sb, long long sc, int batch, float alpha, float beta,
@@ -180,13 +183,35 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
     float4 prior[8];
     if (HAS_C) {
 #pragma unroll
-      for (int c = 0; c < 8; ++c) prior[c] = Cs4[(8 * tj + c) * 8 + ti];
+      for (int c = 0; c < 8; ++c)
+        prior[c] = TRANS_OUT ? Cs4[(4 * ti + (c >> 1)) * 8 + 2 * tj + (c & 1)] : Cs4[(8 * tj + c) * 8 + ti];
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty_bar[s]);  // the slot may be refilled while we store
 
     const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
     float4* Cg4 = reinterpret_cast<float4*>(C + item * sc);
+    if (TRANS_OUT) {
+      // acc[r][c] = C(8tj + c, 4ti + r): column 4ti+r, rows 8tj..8tj+7 -> float4 index col*8 + 2tj + half
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          float4 o;
+          o.x = alpha * acc[r][4 * hf + 0];
+          o.y = alpha * acc[r][4 * hf + 1];
+          o.z = alpha * acc[r][4 * hf + 2];
+          o.w = alpha * acc[r][4 * hf + 3];
+          if (HAS_C) {
+            const float4 pr = prior[2 * r + hf];
+            o.x = fmaf(beta, pr.x, o.x);
+            o.y = fmaf(beta, pr.y, o.y);
+            o.z = fmaf(beta, pr.z, o.z);
+            o.w = fmaf(beta, pr.w, o.w);
+          }
+          Cg4[(4 * ti + r) * 8 + 2 * tj + hf] = o;
+        }
+    } else
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
       float4 o;
@@ -210,7 +235,7 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
   }
 }
 
-template <int CW, bool AK, bool BK, bool HC>
+template <int CW, bool AK, bool BK, bool HC, bool TRANS_OUT = false>
 int launch32(const GemmParams& p, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
   constexpr int kStageBytes = (HC ? 3 : 2) * kMatBytes32;
@@ -221,7 +246,7 @@ int launch32(const GemmParams& p, cudaStream_t stream) {
   if (want >= CW && want < stages) stages = want / CW * CW;
   if (stages < CW) return BLB200_E_UNSUPPORTED;
   const size_t smem = (size_t)stages * kStageBytes + (size_t)stages * 2 * sizeof(uint64_t);
-  auto kern = gemm_small32_kernel<CW, AK, BK, HC>;
+  auto kern = gemm_small32_kernel<CW, AK, BK, HC, TRANS_OUT>;
   static thread_local int configured_for = -1;  // per (instantiation, thread): device last configured
   int cur = 0;
   cudaGetDevice(&cur);
@@ -617,6 +642,18 @@ int launch_small32(const GemmParams& p, int dtype, cudaStream_t stream) {
   const bool hc = (float)p.beta[0] != 0.f;
   static const int cw = env_int("BLB200_SMALL32_WARPS", 16);  // tuning knob: 8, 12 or 16 consumer warps
   int rc;
+  if (ak && !bk) {
+    // TT: C^T = B_stored * A_stored.  B (n x k, column-major) plays the M-major left operand, A (k x m)
+    // the K-major right operand; the kernel writes its block transposed.
+    GemmParams q = p;
+    q.a = p.b; q.b = p.a;
+    q.sa = p.sb; q.sb = p.sa;
+    if (cw == 8) rc = hc ? launch32<8, false, true, true, true>(q, stream) : launch32<8, false, true, false, true>(q, stream);
+    else if (cw == 12) rc = hc ? launch32<12, false, true, true, true>(q, stream) : launch32<12, false, true, false, true>(q, stream);
+    else rc = hc ? launch32<16, false, true, true, true>(q, stream) : launch32<16, false, true, false, true>(q, stream);
+    if (rc == BLB200_OK) note_launch("small32");
+    return rc;
+  }
 #define BLB_CASE(a, b)                                                                            \
   if (ak == a && bk == b) {                                                                       \
     if (cw == 16) rc = hc ? launch32<16, a, b, true>(p, stream) : launch32<16, a, b, false>(p, stream); \
