@@ -112,7 +112,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.idx), "-lms", "100"], stdout=subprocess.PIPE,
+                                          "-i", str(self.idx), "-lms", "50"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -352,13 +352,16 @@ def run_ours(args, rank, local_rank, world):
         for d in descs:
             bl.gemm_strided_batched(d)
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    kernel_name = bl.last_kernel_name()
-    barrier()
+    # Clocks are sampled (nvidia-smi, 50 ms period) from the first warm-up step to the last timed
+    # step: K timed steps alone can be shorter than one sampling period.
     sampler = ClockSampler(local_rank)
     sampler.start()
-    time.sleep(0.3)
+    time.sleep(0.25)
+    t_load0 = time.time()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    kernel_name = bl.last_kernel_name()
     launches0 = bl.launch_count()
     barrier()
     t_wall0 = time.time()
@@ -373,7 +376,8 @@ def run_ours(args, rank, local_rank, world):
     ms_total = max_over_ranks(ev0.elapsed_time(ev1))
     time.sleep(0.2)
     sampler.stop()
-    clocks = sampler.summary(t_wall0, t_wall1)
+    clocks = sampler.summary(t_load0, t_wall1)
+    clocks["window"] = "warm-up + timed steps"
     ms_per_step = ms_total / args.steps
     flops_step = flops_per_item(c2) * batch * len(c2["ops"]) * world
     value = flops_step / (ms_per_step * 1e-3) / 1e9
@@ -551,7 +555,7 @@ def run_case(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the C1/C3/C4/C5 figures")
