@@ -270,6 +270,44 @@ def test_split_k_plan_declines_when_the_gpu_is_already_full(bl):
     assert L.blb200_gemm_splitk(desc, 8, ws.data_ptr(), 1024, None) == bl._lib.E_TOO_LARGE
 
 
+def test_back_to_back_dependent_launches_keep_stream_order(bl):
+    """The 64^3 kernel is launched with programmatic dependent launch: its CTAs may be placed while
+    the previous kernel of the stream is still draining.  A chain in which every call consumes the
+    previous call's output (and torch kernels write operands in between) must still see finished
+    data: X1 = A*B, X2 = X1*B + X1 (in place through beta), X3 = (2*X2)^T-free product X2*X1."""
+    batch = 700
+    p = oracle.make_problem("s", "N", "N", 64, 64, 64, batch)
+    A, B, _ = make_inputs(p, scale=0.125, tail=0)
+    A *= np.float32(0.125)
+    B *= np.float32(0.125)
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    X1 = torch.full_like(dA, float("nan"))
+    X2 = torch.empty_like(dA)
+    X3 = torch.full_like(dA, float("nan"))
+
+    def call(a, b, c, alpha, beta):
+        d = bl.make_desc(a.data_ptr(), b.data_ptr(), c.data_ptr(), 0, 0, 0, 64, 64, 64, batch, 64, 64, 64, 4096, 4096,
+                         4096, alpha, beta)
+        bl.gemm_strided_batched(d)
+        assert bl.last_kernel_name() == "small64"
+
+    for _ in range(3):  # repeated so that launches really queue up behind each other
+        call(dA, dB, X1, 1.0, 0.0)
+        X2.copy_(X1)                 # torch kernel between two of ours
+        call(X1, dB, X2, 1.0, 1.0)   # reads X1 written by the first call, accumulates into the copy
+        X2.mul_(2.0)                 # torch kernel writes an operand of the next call
+        call(X2, X1, X3, 1.0, 0.0)
+    torch.cuda.synchronize()
+
+    a = A.reshape(batch, 64, 64).transpose(0, 2, 1).astype(np.float64)  # math layout [b, row, col]
+    b = B.reshape(batch, 64, 64).transpose(0, 2, 1).astype(np.float64)
+    x1 = a @ b
+    x2 = 2.0 * (x1 @ b + x1)
+    x3 = x2 @ x1
+    got = X3.cpu().numpy().reshape(batch, 64, 64).transpose(0, 2, 1)
+    assert np.allclose(got, x3, rtol=2e-4, atol=1e-6), float(np.max(np.abs(got - x3)))
+
+
 def test_forced_kernel_that_cannot_run_reports_unsupported(bl):
     p = oracle.make_problem("d", "N", "N", 20, 20, 20, 1)
     A, B, C0 = make_inputs(p)
