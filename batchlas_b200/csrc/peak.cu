@@ -67,6 +67,70 @@ __global__ void __launch_bounds__(256) ffma2_rate_kernel(unsigned long long* sin
   if (total == 0x123456789abcdefull) sink[0] = total;
 }
 
+// The same instruction in the operand pattern of an 8 x 8 register block: 32 accumulator pairs,
+// 4 A pairs and 8 duplicated B values, every product a2[rp] * b2[c] (what the GEMM inner loops issue).
+__global__ void __launch_bounds__(256) ffma2_outer_kernel(unsigned long long* sink, int iters, float a, float b) {
+  unsigned long long acc[32], a2[4], b2[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float f = a + 0.001f * (float)(i + threadIdx.x % 3);
+    asm("mov.b64 %0, {%1, %1};" : "=l"(a2[i]) : "f"(f));
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float f = b + 0.001f * (float)i;
+    asm("mov.b64 %0, {%1, %1};" : "=l"(b2[i]) : "f"(f));
+  }
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const float f = (float)(threadIdx.x + i);
+    asm("mov.b64 %0, {%1, %1};" : "=l"(acc[i]) : "f"(f));
+  }
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int rep = 0; rep < 2; ++rep)
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+#pragma unroll
+        for (int rp = 0; rp < 4; ++rp)
+          asm volatile("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc[rp * 8 + c]) : "l"(a2[rp]), "l"(b2[c]));
+  }
+  unsigned long long total = 0;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) total ^= acc[i];
+  if (total == 0x123456789abcdefull) sink[0] = total;
+}
+
+int measure_ffma2_outer(double* tflops) {
+  const DeviceInfo& dev = device_info();
+  unsigned long long* sink = nullptr;
+  cudaError_t e = cudaMalloc(&sink, sizeof(unsigned long long));
+  if (e != cudaSuccess) return (int)e;
+  const int iters = 4096, blocks = dev.sm_count * 8, threads = 256;
+  cudaEvent_t t0, t1;
+  cudaEventCreate(&t0);
+  cudaEventCreate(&t1);
+  ffma2_outer_kernel<<<blocks, threads>>>(sink, 16, 0.999f, 0.001f);
+  float best = 1e30f;
+  for (int rep = 0; rep < 5; ++rep) {
+    cudaEventRecord(t0);
+    ffma2_outer_kernel<<<blocks, threads>>>(sink, iters, 0.999f, 0.001f);
+    cudaEventRecord(t1);
+    e = cudaEventSynchronize(t1);
+    if (e != cudaSuccess) break;
+    float ms = 0;
+    cudaEventElapsedTime(&ms, t0, t1);
+    if (ms < best) best = ms;
+  }
+  cudaEventDestroy(t0);
+  cudaEventDestroy(t1);
+  cudaFree(sink);
+  if (e != cudaSuccess) return (int)e;
+  const double flops = 2.0 * 2.0 * 64.0 * iters * (double)blocks * threads;
+  *tflops = flops / (best * 1e-3) / 1e12;
+  return BLB200_OK;
+}
+
 int measure_ffma2(double* tflops) {
   const DeviceInfo& dev = device_info();
   unsigned long long* sink = nullptr;
@@ -165,7 +229,8 @@ int measure(double* tflops, double* ms_out) {
 
 // Measures the FMA issue rate of the current device for float (dtype S) or double (dtype D) in
 // TFLOP/s (2 flops per FMA); dtype Z selects the FP64 tensor-core (DMMA m8n8k4) rate and dtype C
-// the packed FP32 (fma.rn.f32x2) rate instead.
+// the packed FP32 (fma.rn.f32x2) rate instead; 100 + BLB200_C measures fma.rn.f32x2 in the operand
+// pattern of an 8 x 8 register block (32 accumulators, 4 x 8 distinct operand pairs).
 // Synchronous; allocates a few bytes; a diagnostic, not a data path.
 extern "C" int blb200_measure_pipe_peak(int32_t dtype, double* tflops) {
   if (!tflops) return BLB200_E_NULL;
@@ -173,5 +238,6 @@ extern "C" int blb200_measure_pipe_peak(int32_t dtype, double* tflops) {
   if (dtype == BLB200_D) return blb200::measure<double>(tflops, nullptr);
   if (dtype == BLB200_Z) return blb200::measure_dmma(tflops);
   if (dtype == BLB200_C) return blb200::measure_ffma2(tflops);
+  if (dtype == 100 + BLB200_C) return blb200::measure_ffma2_outer(tflops);
   return BLB200_E_DTYPE;
 }

@@ -155,5 +155,5 @@ def measure_pipe_peak(dtype: str = "s") -> float:
     FP64 tensor-core (mma.sync m8n8k4) rate."""
     import ctypes
     out = ctypes.c_double(0.0)
-    check(load().blb200_measure_pipe_peak({"s": _lib.S, "d": _lib.D, "dmma": _lib.Z, "ffma2": _lib.C}[dtype], ctypes.byref(out)))
+    check(load().blb200_measure_pipe_peak({"s": _lib.S, "d": _lib.D, "dmma": _lib.Z, "ffma2": _lib.C, "ffma2_outer": 100 + _lib.C}[dtype], ctypes.byref(out)))
     return out.value
