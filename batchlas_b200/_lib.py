@@ -51,6 +51,13 @@ SIGNATURES = {
                                           ctypes.c_void_p]),
     "blb200_gemm_splitk_static_capacity": (ctypes.c_size_t, []),
     "blb200_gemm_splitk_static": (ctypes.c_int, [ctypes.POINTER(GemmDesc), ctypes.c_int32, ctypes.c_void_p]),
+    "blb200_level3_workspace_bytes": (ctypes.c_size_t, [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]),
+    "blb200_symm": (ctypes.c_int, [ctypes.POINTER(GemmDesc), ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                   ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "blb200_trmm": (ctypes.c_int, [ctypes.POINTER(GemmDesc), ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+                                   ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "blb200_syrk": (ctypes.c_int, [ctypes.POINTER(GemmDesc), ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
+                                   ctypes.c_size_t, ctypes.c_void_p]),
     "blb200_gemm_strided_batched_host": (ctypes.c_int, [ctypes.POINTER(GemmDesc), ctypes.c_int, ctypes.c_int32]),
     "blb200_last_kernel_name": (ctypes.c_char_p, []),
     "blb200_launch_count": (ctypes.c_uint64, []),

@@ -552,6 +552,49 @@ def run_case(args):
     print(json.dumps(out), flush=True)
 
 
+def run_level3(args):
+    """symm / hemm / trmm / syrk / herk (the calls BatchLAS builds on gemm) on square operands, each
+    beside the plain gemm of the same shape: the difference is the cost of expanding the triangle
+    (or of accumulating one).  One JSON line; times are CUDA events per call, after warm-up."""
+    import torch
+
+    import batchlas_b200 as bl
+    torch.cuda.set_device(0)
+    tdt = {"s": torch.float32, "d": torch.float64, "c": torch.complex64, "z": torch.complex128}
+    out = {"level3": []}
+    shapes = [("s", 128, 4096), ("d", 256, 512), ("z", 128, 1024), ("d", 1024, 32)]
+    for dt, n, batch in shapes:
+        if args.batch:
+            batch = args.batch
+        t = tdt[dt]
+        A, B, C = (bl.fill(torch.empty(batch, n, n, dtype=t, device="cuda"), 42, i) for i in range(3))
+        ws = torch.empty(bl.level3.workspace_bytes(t, n, batch), dtype=torch.uint8, device="cuda")
+        cplx = dt in "cz"
+        mul = 4 if cplx else 1  # real flops per complex fma pair, BLAS convention 8 per complex multiply-add
+        calls = {
+            "gemm": (lambda: bl.gemm(A, B, C, 1.0, 0.5), 2.0 * n * n * n),
+            "symm": (lambda: bl.symm(A, B, C, 1.0, 0.5, 0, 1, workspace=ws), 2.0 * n * n * n),
+            "trmm": (lambda: bl.trmm(A, B, C, 1.0, 0, 1, 0, 0, workspace=ws), 1.0 * n * n * n),
+            "syrk": (lambda: bl.syrk(A, C, 1.0, 0.5, 1, 0, workspace=ws), 1.0 * n * n * (n + 1)),
+        }
+        if cplx:
+            calls["hemm"] = (lambda: bl.hemm(A, B, C, 1.0, 0.5, 0, 1, workspace=ws), 2.0 * n * n * n)
+            calls["herk"] = (lambda: bl.herk(A, C, 1.0, 0.5, 1, 0, workspace=ws), 1.0 * n * n * (n + 1))
+        row = {"dtype": dt, "n": n, "batch": batch, "ops": {}}
+        for name, (fn, fl) in calls.items():
+            for _ in range(max(args.warmup, 3)):
+                fn()
+            torch.cuda.synchronize()
+            ms = time_launches(torch, fn, args.steps)
+            row["ops"][name] = {"ms": round(ms, 4), "blas_gflops": round(fl * mul * batch / (ms * 1e-3) / 1e9, 1),
+                                "kernel": bl.last_kernel_name()}
+        g = row["ops"]["gemm"]["ms"]
+        for name in row["ops"]:
+            row["ops"][name]["time_vs_gemm"] = round(row["ops"][name]["ms"] / g, 3)
+        out["level3"].append(row)
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -564,6 +607,7 @@ def main():
     ap.add_argument("--case", default="", help="profiling mode: CONFIG[:OP], e.g. C2:NT or C3:TN (1 GPU)")
     ap.add_argument("--batch", type=int, default=0, help="batch override for --case")
     ap.add_argument("--kernel", default="auto", help="forced kernel for --case")
+    ap.add_argument("--level3", action="store_true", help="time symm/hemm/trmm/syrk/herk beside gemm (1 GPU)")
     ap.add_argument("--splitk", action="store_true", help="--case through blb200_gemm_splitk with planned scratch")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -574,6 +618,9 @@ def main():
         return
     if args.case:
         run_case(args)
+        return
+    if args.level3:
+        run_level3(args)
         return
     if world != args.gpus and world == 1 and args.gpus > 1:
         raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")

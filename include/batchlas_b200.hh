@@ -581,6 +581,189 @@ inline Event gemm(Queue& ctx, const Matrix<T>& A, const Matrix<T>& B, const Matr
   return gemm<T>(ctx, A.view(), B.view(), C.view(), o);
 }
 
+// ---- level-3 calls the reference builds on gemm: symm, hemm, trmm, syrk, herk ---------------------
+// Same spellings as BatchLAS include/blas/functions/{symm,hemm,trmm,syrk,herk}.hh and the option
+// structs of include/blas/options.hh:56-116; the expanded triangle / the full product lives in a lease
+// from the queue's arena for the duration of the call.
+enum class Side { Left, Right };
+enum class Uplo { Upper, Lower };
+enum class Diag { NonUnit, Unit };
+
+template <typename T>
+struct SymmOptions {
+  T alpha = T(1);
+  T beta = T(0);
+  Side side = Side::Left;
+  Uplo uplo = Uplo::Lower;
+};
+template <typename T>
+struct HemmOptions {
+  T alpha = T(1);
+  T beta = T(0);
+  Side side = Side::Left;
+  Uplo uplo = Uplo::Lower;
+};
+template <typename T>
+struct HerkOptions {
+  float_t<T> alpha = float_t<T>(1);
+  float_t<T> beta = float_t<T>(0);
+  Uplo uplo = Uplo::Lower;
+  Transpose trans = Transpose::NoTrans;
+};
+template <typename T>
+struct SyrkOptions {
+  T alpha = T(1);
+  T beta = T(0);
+  Uplo uplo = Uplo::Lower;
+  Transpose trans = Transpose::NoTrans;
+};
+template <typename T>
+struct TrmmOptions {
+  T alpha = T(1);
+  Side side = Side::Left;
+  Uplo uplo = Uplo::Lower;
+  Transpose trans = Transpose::NoTrans;
+  Diag diag = Diag::NonUnit;
+};
+
+namespace detail {
+template <typename T>
+inline void set_scalar(double (&dst)[2], T v) {
+  if constexpr (std::is_floating_point_v<T>) {
+    dst[0] = v; dst[1] = 0.0;
+  } else {
+    dst[0] = v.real(); dst[1] = v.imag();
+  }
+}
+template <typename T>
+inline blb200_gemm_desc level3_desc(const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>* B,
+                                    const MatrixView<T, MatrixFormat::Dense>& C) {
+  blb200_gemm_desc d{};
+  d.a = A.data_ptr(); d.lda = A.ld(); d.stride_a = A.stride();
+  if (B) { d.b = B->data_ptr(); d.ldb = B->ld(); d.stride_b = B->stride(); } else { d.ldb = 1; }
+  d.c = C.data_ptr(); d.ldc = C.ld(); d.stride_c = C.stride();
+  d.batch = A.batch_size();
+  d.dtype = dtype_code<T>();
+  return d;
+}
+template <typename T>
+inline Event symm_like(Queue& ctx, const char* name, bool hermitian, const MatrixView<T, MatrixFormat::Dense>& A,
+                       const MatrixView<T, MatrixFormat::Dense>& B, const MatrixView<T, MatrixFormat::Dense>& C, T alpha,
+                       T beta, Side side, Uplo uplo) {
+  const std::string nm(name);
+  if (A.rows() != A.cols()) throw std::runtime_error(nm + ": A must be square");
+  if (A.batch_size() != B.batch_size() || A.batch_size() != C.batch_size())
+    throw std::runtime_error(nm + ": batch size mismatch");
+  const int m = C.rows(), n = C.cols(), k = side == Side::Left ? m : n;
+  if (A.rows() != k || B.rows() != m || B.cols() != n) throw std::runtime_error(nm + ": incompatible matrix dimensions");
+  blb200_gemm_desc d = level3_desc<T>(A, &B, C);
+  d.m = m; d.n = n; d.k = k;
+  set_scalar(d.alpha, alpha);
+  set_scalar(d.beta, beta);
+  ctx.make_current();
+  WorkspaceLease ws = ctx.workspace(std::max<size_t>(blb200_level3_workspace_bytes(d.dtype, k, d.batch), 16));
+  status_check(blb200_symm(&d, (int)side, (int)uplo, hermitian ? 1 : 0, ws.data(), ws.size(), ctx.native_stream()));
+  return ctx.create_event_after_external_work();
+}
+template <typename T>
+inline Event syrk_like(Queue& ctx, const char* name, bool hermitian, const MatrixView<T, MatrixFormat::Dense>& A,
+                       const MatrixView<T, MatrixFormat::Dense>& C, T alpha, T beta, Uplo uplo, Transpose transA) {
+  const std::string nm(name);
+  if (C.rows() != C.cols()) throw std::runtime_error(nm + ": C must be square");
+  if (A.batch_size() != C.batch_size()) throw std::runtime_error(nm + ": batch size mismatch");
+  const int n = C.rows();
+  const int k = transA == Transpose::NoTrans ? A.cols() : A.rows();
+  const int expected_n = transA == Transpose::NoTrans ? A.rows() : A.cols();
+  if (expected_n != n || k <= 0) throw std::runtime_error(nm + ": incompatible matrix dimensions");
+  blb200_gemm_desc d = level3_desc<T>(A, nullptr, C);
+  d.m = n; d.n = n; d.k = k;
+  d.op_a = (int)transA;
+  set_scalar(d.alpha, alpha);
+  set_scalar(d.beta, beta);
+  ctx.make_current();
+  WorkspaceLease ws = ctx.workspace(std::max<size_t>(blb200_level3_workspace_bytes(d.dtype, n, d.batch), 16));
+  status_check(blb200_syrk(&d, (int)uplo, hermitian ? 1 : 0, ws.data(), ws.size(), ctx.native_stream()));
+  return ctx.create_event_after_external_work();
+}
+}  // namespace detail
+
+template <Backend Back, typename T>
+inline Event symm(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
+                  const MatrixView<T, MatrixFormat::Dense>& C, T alpha, T beta, Side side, Uplo uplo) {
+  static_assert(Back == Backend::CUDA, "only the CUDA backend exists in this build");
+  return detail::symm_like<T>(ctx, "SYMM", false, A, B, C, alpha, beta, side, uplo);
+}
+template <typename T>
+inline Event symm(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
+                  const MatrixView<T, MatrixFormat::Dense>& C, const SymmOptions<std::type_identity_t<T>>& o = {}) {
+  return with_backend(ctx, [&](auto Bk) { return symm<Bk.value, T>(ctx, A, B, C, o.alpha, o.beta, o.side, o.uplo); });
+}
+
+// hemm exists for complex T only, as in the reference (ComplexScalar, include/blas/functions/hemm.hh).
+template <Backend Back, typename T>
+inline Event hemm(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
+                  const MatrixView<T, MatrixFormat::Dense>& C, T alpha, T beta, Side side, Uplo uplo) {
+  static_assert(Back == Backend::CUDA, "only the CUDA backend exists in this build");
+  static_assert(!std::is_floating_point_v<T>, "hemm needs a complex scalar; use symm for real data");
+  return detail::symm_like<T>(ctx, "HEMM", true, A, B, C, alpha, beta, side, uplo);
+}
+template <typename T>
+inline Event hemm(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
+                  const MatrixView<T, MatrixFormat::Dense>& C, const HemmOptions<std::type_identity_t<T>>& o = {}) {
+  return with_backend(ctx, [&](auto Bk) { return hemm<Bk.value, T>(ctx, A, B, C, o.alpha, o.beta, o.side, o.uplo); });
+}
+
+template <Backend Back, typename T>
+inline Event syrk(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& C,
+                  T alpha, T beta, Uplo uplo, Transpose transA) {
+  static_assert(Back == Backend::CUDA, "only the CUDA backend exists in this build");
+  return detail::syrk_like<T>(ctx, "SYRK", false, A, C, alpha, beta, uplo, transA);
+}
+template <typename T>
+inline Event syrk(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& C,
+                  const SyrkOptions<std::type_identity_t<T>>& o = {}) {
+  return with_backend(ctx, [&](auto Bk) { return syrk<Bk.value, T>(ctx, A, C, o.alpha, o.beta, o.uplo, o.trans); });
+}
+
+template <Backend Back, typename T>
+inline Event herk(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& C,
+                  float_t<T> alpha, float_t<T> beta, Uplo uplo, Transpose transA) {
+  static_assert(Back == Backend::CUDA, "only the CUDA backend exists in this build");
+  static_assert(!std::is_floating_point_v<T>, "herk needs a complex scalar; use syrk for real data");
+  return detail::syrk_like<T>(ctx, "HERK", true, A, C, T(alpha), T(beta), uplo, transA);
+}
+template <typename T>
+inline Event herk(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& C,
+                  const HerkOptions<std::type_identity_t<T>>& o = {}) {
+  return with_backend(ctx, [&](auto Bk) { return herk<Bk.value, T>(ctx, A, C, o.alpha, o.beta, o.uplo, o.trans); });
+}
+
+// Out of place, as the reference's trmm: C <- alpha * op(tri(A)) * B or alpha * B * op(tri(A)).
+template <Backend Back, typename T>
+inline Event trmm(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
+                  const MatrixView<T, MatrixFormat::Dense>& C, T alpha, Side side, Uplo uplo, Transpose transA, Diag diag) {
+  static_assert(Back == Backend::CUDA, "only the CUDA backend exists in this build");
+  if (A.rows() != A.cols()) throw std::runtime_error("TRMM: A must be square");
+  if (A.batch_size() != B.batch_size() || A.batch_size() != C.batch_size())
+    throw std::runtime_error("TRMM: batch size mismatch");
+  const int m = B.rows(), n = B.cols(), k = side == Side::Left ? m : n;
+  if (A.rows() != k || C.rows() != m || C.cols() != n) throw std::runtime_error("TRMM: incompatible matrix dimensions");
+  blb200_gemm_desc d = detail::level3_desc<T>(A, &B, C);
+  d.m = m; d.n = n; d.k = k;
+  d.op_a = (int)transA;
+  detail::set_scalar(d.alpha, alpha);
+  ctx.make_current();
+  WorkspaceLease ws = ctx.workspace(std::max<size_t>(blb200_level3_workspace_bytes(d.dtype, k, d.batch), 16));
+  detail::status_check(blb200_trmm(&d, (int)side, (int)uplo, diag == Diag::Unit ? 1 : 0, ws.data(), ws.size(),
+                                   ctx.native_stream()));
+  return ctx.create_event_after_external_work();
+}
+template <typename T>
+inline Event trmm(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
+                  const MatrixView<T, MatrixFormat::Dense>& C, const TrmmOptions<std::type_identity_t<T>>& o = {}) {
+  return with_backend(ctx, [&](auto Bk) { return trmm<Bk.value, T>(ctx, A, B, C, o.alpha, o.side, o.uplo, o.trans, o.diag); });
+}
+
 }  // namespace batchlas
 
 inline batchlas::WorkspaceLease Queue::workspace(size_t bytes) {

@@ -198,6 +198,39 @@ size_t blb200_arena_capacity(const blb200_arena* arena);
 size_t blb200_arena_block_count(const blb200_arena* arena);
 size_t blb200_arena_alignment(const blb200_arena* arena);
 
+/* ---- level-3 operations that BatchLAS builds on gemm -----------------------------------
+ * The reference's CUDA backend turns symm/hemm and trmm into "expand the stored triangle to a
+ * full matrix, then gemm" and syrk/herk into "gemm into scratch, then accumulate one triangle"
+ * (src/backends/cublas.cc:181-352 symm/hemm, :441-606 accumulate_hermitian + herk, :697-796 syrk,
+ * :905-997 trmm; src/backends/triangular_expand.hh).  These entry points do the same on the
+ * B200 gemm kernels.  `workspace` is device memory of at least
+ * blb200_level3_workspace_bytes(dtype, order, batch) bytes, 16-byte aligned — in BatchLAS a lease
+ * from the queue's arena; order = the side length of the square operand (m for side left,
+ * n for side right; n for syrk/herk).  Nothing is allocated.
+ * side: 0 = Left, 1 = Right; uplo: 0 = Upper, 1 = Lower (the reference's Side / Uplo). */
+size_t blb200_level3_workspace_bytes(int32_t dtype, int32_t order, int32_t batch);
+
+/* symm (hermitian 0) / hemm (hermitian 1, complex only): C <- alpha*A*B + beta*C (Left) or
+ * alpha*B*A + beta*C (Right); only the `uplo` triangle of A is read, for hemm the imaginary part
+ * of its diagonal is taken as zero.  desc: a = A, b = B (m x n), c = C (m x n); k, op_a, op_b are
+ * ignored.  Replaces symm_vendor / hemm_vendor, cublas.cc:181-352. */
+int blb200_symm(const blb200_gemm_desc* desc, int32_t side, int32_t uplo, int32_t hermitian, void* workspace,
+                size_t workspace_bytes, void* cuda_stream);
+
+/* trmm, out of place as the reference's: C <- alpha*op_a(tri(A))*B (Left) or alpha*B*op_a(tri(A))
+ * (Right); unit_diag != 0 takes the diagonal as ones.  beta, k, op_b are ignored.
+ * Replaces trmm_vendor_impl, cublas.cc:905-997. */
+int blb200_trmm(const blb200_gemm_desc* desc, int32_t side, int32_t uplo, int32_t unit_diag, void* workspace,
+                size_t workspace_bytes, void* cuda_stream);
+
+/* syrk (hermitian 0: op_a N -> A*A^T, T -> A^T*A) / herk (hermitian 1: op_a N -> A*A^H,
+ * H -> A^H*A; only the real parts of alpha and beta are used and the diagonal comes out real):
+ * the `uplo` triangle of C (n x n) <- alpha*product + beta*C; the other triangle is not touched.
+ * desc: a = A (n x k for op N, else k x n), c = C; b, m, op_b are ignored.
+ * Replaces herk_vendor (cublas.cc:504-606) and syrk_vendor (cublas.cc:697-796). */
+int blb200_syrk(const blb200_gemm_desc* desc, int32_t uplo, int32_t hermitian, void* workspace, size_t workspace_bytes,
+                void* cuda_stream);
+
 /* ---- synthetic inputs ------------------------------------------------------------------
  * Counter-based generator: element `i` of tensor `tensor_id` under `seed` depends only on
  * (seed, tensor_id, first_index + i), so any shard on any GPU count reproduces the same data.

@@ -240,6 +240,155 @@ void SlicedViews(Queue& ctx) {  // slices offset the base pointer: matrix.hh:855
   CHECK(C(0, 0, 0) == 0.0 && C(39, 39, 1) == 0.0 && C(4, 2, 0) == 0.0 && C(37, 2, 0) == 0.0);  // outside the slice
 }
 
+// ---- level-3 calls through gemm: each checked against gemm on the explicitly expanded operand, the
+// way the reference's tests do (symm_tests.cc:46-112, hemm_tests.cc, trmm_tests.cc:58-120,
+// herk_tests.cc:337-420, syrk_tests.cc).
+template <typename T>
+T conj_if_complex(T v) {
+  if constexpr (std::is_floating_point_v<T>) return v;
+  else return std::conj(v);
+}
+
+template <typename T>
+double max_diff(const Matrix<T>& X, const Matrix<T>& Y, int rows, int cols, int batch) {
+  double w = 0;
+  for (int b = 0; b < batch; ++b)
+    for (int j = 0; j < cols; ++j)
+      for (int i = 0; i < rows; ++i) w = std::max(w, (double)std::abs(X(i, j, b) - Y(i, j, b)));
+  return w;
+}
+
+template <typename T>
+void SymmMatchesSymmetrizedGemm(Queue& ctx) {
+  const int n = 96, m = 64, batch = 3;
+  const T alpha = T(1.25), beta = T(-0.5);
+  const double tol = tolerance<T>() * 12 * n;
+  for (bool herm : {false, true}) {
+    if (herm && std::is_floating_point_v<T>) continue;
+    for (auto side : {Side::Left, Side::Right})
+      for (auto uplo : {Uplo::Lower, Uplo::Upper}) {
+        const int rows = side == Side::Left ? n : m, cols = side == Side::Left ? m : n;
+        auto A = Matrix<T>::Random(n, n, false, batch);
+        auto B = Matrix<T>::Random(rows, cols, false, batch, 43);
+        auto C = Matrix<T>::Random(rows, cols, false, batch, 44);
+        auto C_ref = C.clone();
+        auto A_ref = A.clone();
+        ctx.wait();
+        for (int b = 0; b < batch; ++b)
+          for (int j = 0; j < n; ++j)
+            for (int i = 0; i < n; ++i) {
+              const bool stored = uplo == Uplo::Lower ? i >= j : i <= j;
+              T v = stored ? A(i, j, b) : (herm ? conj_if_complex(A(j, i, b)) : A(j, i, b));
+              if constexpr (!std::is_floating_point_v<T>) {
+                if (herm && i == j) v = T(v.real(), 0);
+              }
+              A_ref(i, j, b) = v;
+            }
+        if constexpr (!std::is_floating_point_v<T>) {
+          if (herm) hemm(ctx, A.view(), B.view(), C.view(), {.alpha = alpha, .beta = beta, .side = side, .uplo = uplo});
+          else symm(ctx, A.view(), B.view(), C.view(), {.alpha = alpha, .beta = beta, .side = side, .uplo = uplo});
+        } else {
+          symm(ctx, A.view(), B.view(), C.view(), {.alpha = alpha, .beta = beta, .side = side, .uplo = uplo});
+        }
+        if (side == Side::Left) gemm(ctx, A_ref.view(), B.view(), C_ref.view(), {.alpha = alpha, .beta = beta});
+        else gemm(ctx, B.view(), A_ref.view(), C_ref.view(), {.alpha = alpha, .beta = beta});
+        ctx.wait();
+        CHECK(max_diff(C, C_ref, rows, cols, batch) <= tol);
+      }
+  }
+}
+
+template <typename T>
+void TrmmAllCombinations(Queue& ctx) {
+  const int n = 64, batch = 4;
+  const double tol = tolerance<T>() * 12 * n;
+  for (auto trans : {Transpose::NoTrans, Transpose::Trans, Transpose::ConjTrans})
+    for (auto side : {Side::Right, Side::Left})
+      for (auto uplo : {Uplo::Lower, Uplo::Upper})
+        for (auto diag : {Diag::NonUnit, Diag::Unit}) {
+          auto A = Matrix<T>::Random(n, n, false, batch);
+          auto B = Matrix<T>::Random(n, n, false, batch, 43);
+          auto C = Matrix<T>::Zeros(n, n, batch);
+          auto C_ref = Matrix<T>::Zeros(n, n, batch);
+          auto A_tri = A.clone();
+          ctx.wait();
+          for (int b = 0; b < batch; ++b)
+            for (int j = 0; j < n; ++j)
+              for (int i = 0; i < n; ++i) {
+                const bool stored = uplo == Uplo::Lower ? i >= j : i <= j;
+                A_tri(i, j, b) = (i == j && diag == Diag::Unit) ? T(1) : (stored ? A(i, j, b) : T(0));
+              }
+          trmm(ctx, A.view(), B.view(), C.view(), {.alpha = T(0.9), .side = side, .uplo = uplo, .trans = trans, .diag = diag});
+          if (side == Side::Left) gemm(ctx, A_tri.view(), B.view(), C_ref.view(), {.alpha = T(0.9), .transA = trans});
+          else gemm(ctx, B.view(), A_tri.view(), C_ref.view(), {.alpha = T(0.9), .transB = trans});
+          ctx.wait();
+          CHECK(max_diff(C, C_ref, n, n, batch) <= tol);
+        }
+}
+
+template <typename T>
+void SyrkHerkMatchGemm(Queue& ctx) {
+  using R = batchlas::float_t<T>;
+  const int n = 65, k = 40, batch = 3;
+  const double tol = tolerance<T>() * 12 * k;
+  constexpr bool cplx = !std::is_floating_point_v<T>;
+  for (bool herm : {false, true}) {
+    if (herm && !cplx) continue;
+    const Transpose other = herm ? Transpose::ConjTrans : Transpose::Trans;
+    for (auto trans : {Transpose::NoTrans, other})
+      for (auto uplo : {Uplo::Lower, Uplo::Upper}) {
+        auto A = trans == Transpose::NoTrans ? Matrix<T>::Random(n, k, false, batch) : Matrix<T>::Random(k, n, false, batch);
+        auto C = Matrix<T>::Random(n, n, false, batch, 44);
+        ctx.wait();
+        if constexpr (cplx) {
+          if (herm)  // BLAS does not reference the imaginary part of a Hermitian diagonal
+            for (int b = 0; b < batch; ++b)
+              for (int d = 0; d < n; ++d) C(d, d, b) = T(C(d, d, b).real(), 0);
+        }
+        auto C0 = C.clone();
+        auto C_ref = C.clone();
+        if constexpr (cplx) {
+          if (herm) herk(ctx, A.view(), C.view(), {.alpha = R(0.9), .beta = R(-0.35), .uplo = uplo, .trans = trans});
+          else syrk(ctx, A.view(), C.view(), {.alpha = T(0.9), .beta = T(-0.35), .uplo = uplo, .trans = trans});
+        } else {
+          syrk(ctx, A.view(), C.view(), {.alpha = T(0.9), .beta = T(-0.35), .uplo = uplo, .trans = trans});
+        }
+        gemm(ctx, A.view(), A.view(), C_ref.view(),
+             {.alpha = T(0.9), .beta = T(-0.35), .transA = trans, .transB = trans == Transpose::NoTrans ? other : Transpose::NoTrans});
+        ctx.wait();
+        for (int b = 0; b < batch; ++b)
+          for (int j = 0; j < n; ++j)
+            for (int i = 0; i < n; ++i) {
+              const bool referenced = uplo == Uplo::Lower ? i >= j : i <= j;
+              if (!referenced) {
+                CHECK(C(i, j, b) == C0(i, j, b));  // the other triangle is neither read nor written
+              } else {
+                CHECK(std::abs(C(i, j, b) - C_ref(i, j, b)) <= tol);
+                if constexpr (cplx) {
+                  if (herm && i == j) CHECK(C(i, j, b).imag() == R(0));
+                }
+              }
+            }
+      }
+  }
+}
+
+template <typename T>
+void Level3ShapeErrors(Queue& ctx) {
+  auto A = Matrix<T>::Zeros(8, 8, 2);
+  auto R = Matrix<T>::Zeros(8, 4, 2);
+  auto expect = [&](auto&& call, const char* msg) {
+    bool threw = false;
+    try { call(); } catch (const std::runtime_error& e) { threw = std::strstr(e.what(), msg) != nullptr; }
+    return threw;
+  };
+  CHECK(expect([&] { symm(ctx, R.view(), R.view(), R.view()); }, "SYMM: A must be square"));
+  CHECK(expect([&] { symm(ctx, A.view(), R.view(), R.view(), {.side = Side::Right}); }, "SYMM: incompatible matrix dimensions"));
+  CHECK(expect([&] { trmm(ctx, A.view(), R.view(), A.view()); }, "TRMM: incompatible matrix dimensions"));
+  CHECK(expect([&] { syrk(ctx, R.view(), R.view()); }, "SYRK: C must be square"));
+  CHECK(expect([&] { syrk(ctx, R.view(), A.view(), {.trans = Transpose::Trans}); }, "SYRK: incompatible matrix dimensions"));
+}
+
 void WorkspaceLeases(Queue& ctx) {  // mempool_tests.cc:829-1078
   {
     auto a = ctx.workspace(1000);
@@ -298,6 +447,10 @@ int main(int argc, char** argv) {
   FOR_TYPES(DeducedBackendMatchesExplicit)
   FOR_TYPES(HeterogeneousBatchedGemm)
   FOR_TYPES(LongKUsesSplitKFromTheArena)
+  FOR_TYPES(SymmMatchesSymmetrizedGemm)
+  FOR_TYPES(TrmmAllCombinations)
+  FOR_TYPES(SyrkHerkMatchGemm)
+  FOR_TYPES(Level3ShapeErrors)
   run("OptionDefaultsAndErrors", [&] { OptionDefaultsAndErrors(ctx); });
   run("SlicedViews", [&] { SlicedViews(ctx); });
   run("WorkspaceLeases", [&] { WorkspaceLeases(ctx); });
