@@ -23,7 +23,48 @@ struct GemmParams {
   // element offsets s*split_a / s*split_b past the item, and writes its own partial at c + v*sc.
   int splits, kchunk;
   long long split_a, split_b;
+  // Structure hints, all 0 for a plain gemm (never combined with split-K).
+  //   tri_a / tri_b: op(A) (m x k) / op(B) (k x n) is triangular WITH the zeros of its other triangle
+  //     stored: 1 = lower (zero above the diagonal), 2 = upper.  A tile kernel trims each tile's k
+  //     range to the non-zero part; a kernel that ignores the hint still computes the same product.
+  //   out_tri: only the lower (1) / upper (2) triangle of a square C is computed and written.  A
+  //     kernel handed out_tri must honour it.  out_herm: C is Hermitian — the imaginary part of its
+  //     diagonal is neither read nor left non-zero.
+  int tri_a = 0, tri_b = 0, out_tri = 0, out_herm = 0;
 };
+
+struct StructureHints {
+  int tri_a, tri_b, out_tri, out_herm;
+};
+
+// What a CTA owning rows [m0, m0+BM) and columns [n0, n0+BN) has to do under the hints: the k range
+// [k_lo, k_hi) (k_lo a multiple of BK, so 16-byte alignment of the operand rows survives the shift)
+// or nothing at all when the tile lies wholly in the triangle of C that is not wanted.
+struct TileWork {
+  int k_lo, k_hi;
+  bool skip;
+};
+__device__ __forceinline__ TileWork tile_work(const GemmParams& p, int k, int m0, int BM, int n0, int BN, int BK) {
+  TileWork w{0, k, false};
+  if (p.out_tri == 1) w.skip = m0 + BM - 1 < n0;
+  if (p.out_tri == 2) w.skip = m0 > n0 + BN - 1;
+  if (p.tri_a == 1) w.k_hi = min(w.k_hi, m0 + BM);          // op(A)(i, l) = 0 for l > i
+  if (p.tri_a == 2) w.k_lo = max(w.k_lo, m0 / BK * BK);     // op(A)(i, l) = 0 for l < i
+  if (p.tri_b == 1) w.k_lo = max(w.k_lo, n0 / BK * BK);     // op(B)(l, j) = 0 for l < j
+  if (p.tri_b == 2) w.k_hi = min(w.k_hi, n0 + BN);          // op(B)(l, j) = 0 for l > j
+  return w;
+}
+// Element offsets of k = k_lo inside the stored operands.
+__device__ __forceinline__ long long a_k_offset(const GemmParams& p, int k_lo) {
+  return p.op_a == BLB200_N ? (long long)k_lo * p.lda : (long long)k_lo;
+}
+__device__ __forceinline__ long long b_k_offset(const GemmParams& p, int k_lo) {
+  return p.op_b == BLB200_N ? (long long)k_lo : (long long)k_lo * p.ldb;
+}
+// True when (row, col) lies outside the triangle of C that is wanted.
+__device__ __forceinline__ bool out_masked(const GemmParams& p, int row, int col) {
+  return p.out_tri == 1 ? row < col : (p.out_tri == 2 ? row > col : false);
+}
 
 // Resolves a virtual item into (real item, operand offsets in elements, K extent of this split).
 struct SplitView {
@@ -134,6 +175,10 @@ __device__ __forceinline__ T epilogue(T alpha, T acc, T beta, bool beta_zero, co
 
 // ---- per-thread launch bookkeeping (diagnostics exposed through the C ABI) -----------------------
 void note_launch(const char* kernel_name);
+// Kernel selection for one descriptor; the second form passes structure hints to a tile kernel and
+// answers BLB200_E_UNSUPPORTED when a triangular output is asked for and no tile kernel applies.
+int dispatch(const blb200_gemm_desc* d, cudaStream_t stream);
+int dispatch_structured(const blb200_gemm_desc* d, const StructureHints* hints, cudaStream_t stream);
 
 // ---- launchers implemented in the kernel translation units -------------------------------------
 // Each returns BLB200_OK / a cudaError_t, or BLB200_E_UNSUPPORTED when the kernel's preconditions

@@ -165,17 +165,19 @@ static GemmParams to_params(const blb200_gemm_desc* d) {
 
 GemmParams to_params_public(const blb200_gemm_desc* d) { return to_params(d); }
 
-static int dispatch_untraced(const blb200_gemm_desc* d, cudaStream_t stream);
+static int dispatch_untraced(const blb200_gemm_desc* d, const StructureHints* hints, cudaStream_t stream);
 
-int dispatch(const blb200_gemm_desc* d, cudaStream_t stream) {
+int dispatch(const blb200_gemm_desc* d, cudaStream_t stream) { return dispatch_structured(d, nullptr, stream); }
+
+int dispatch_structured(const blb200_gemm_desc* d, const StructureHints* hints, cudaStream_t stream) {
   Tracer& tr = tracer();
-  if (!tr.enabled) return dispatch_untraced(d, stream);
+  if (!tr.enabled) return dispatch_untraced(d, hints, stream);
   TraceRecord rec{};
   cudaGetDevice(&rec.device);
   if (cudaEventCreate(&rec.start) != cudaSuccess || cudaEventCreate(&rec.stop) != cudaSuccess)
-    return dispatch_untraced(d, stream);
+    return dispatch_untraced(d, hints, stream);
   cudaEventRecord(rec.start, stream);
-  const int rc = dispatch_untraced(d, stream);
+  const int rc = dispatch_untraced(d, hints, stream);
   cudaEventRecord(rec.stop, stream);
   if (d) {
     rec.m = d->m; rec.n = d->n; rec.k = d->k; rec.batch = d->batch;
@@ -186,10 +188,24 @@ int dispatch(const blb200_gemm_desc* d, cudaStream_t stream) {
   return rc;
 }
 
-static int dispatch_untraced(const blb200_gemm_desc* d, cudaStream_t stream) {
+static int dispatch_untraced(const blb200_gemm_desc* d, const StructureHints* hints, cudaStream_t stream) {
   int rc = validate(d);
   if (rc != BLB200_OK) return rc;
   if (d->m == 0 || d->n == 0 || d->batch == 0) return BLB200_OK;
+  if (hints && (hints->tri_a | hints->tri_b | hints->out_tri)) {
+    // Only the cp.async tile kernels read the hints.  An operand hint may be dropped (the zeros are
+    // stored); a triangular output may not, so without such a kernel the caller has to take
+    // another route.
+    GemmParams hp = to_params(d);
+    hp.tri_a = hints->tri_a;
+    hp.tri_b = hints->tri_b;
+    hp.out_tri = hints->out_tri;
+    hp.out_herm = hints->out_herm;
+    if (dmma_supported(hp, d->dtype)) return launch_dmma(hp, d->dtype, stream);
+    if (sgemm128_supported(hp, d->dtype)) return launch_sgemm128(hp, d->dtype, stream);
+    if (tiled_supported(hp, d->dtype)) return launch_tiled(hp, d->dtype, stream);
+    if (hints->out_tri) return BLB200_E_UNSUPPORTED;
+  }
   const GemmParams p = to_params(d);
   if (d->kernel_hint == BLB200_K_AUTO && env_forced_kernel() != BLB200_K_AUTO) {
     const int dt = d->dtype;

@@ -75,7 +75,9 @@ __host__ __device__ constexpr int pitched_stage_bytes() {
 constexpr int kStagesD = 3, kStagesZ = 3;  // copy-ring depth; 4 gains ~1 % on NN/NT and costs the second CTA per SM on TN/TT
 
 // ---- real double -------------------------------------------------------------------------------
-template <int OPA, int OPB>
+// HINTS = false is the plain gemm; HINTS = true reads the structure hints of GemmParams (a separate
+// instantiation, so that the plain kernel's code and register allocation stay what they were).
+template <int OPA, int OPB, bool HINTS>
 __global__ void __launch_bounds__(256, 2) gemm_dmma_d_kernel(GemmParams p, int tiles_m, int tiles_n) {
   constexpr int BM = 128, BN = 64, BK = 16, STAGES = kStagesD, THREADS = 256;
   constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
@@ -102,6 +104,13 @@ __global__ void __launch_bounds__(256, 2) gemm_dmma_d_kernel(GemmParams p, int t
   const unsigned char* A = (const unsigned char*)p.a + (item * p.sa + sv.a_off) * 8;
   const unsigned char* B = (const unsigned char*)p.b + (item * p.sb + sv.b_off) * 8;
   double* C = (double*)p.c + vitem * p.sc;
+  if constexpr (HINTS) {  // triangular operand: shorter k range; triangular output: maybe nothing
+    const TileWork w = tile_work(p, p.k, m0, BM, n0, BN, BK);
+    if (w.skip) return;
+    A += a_k_offset(p, w.k_lo) * 8;
+    B += b_k_offset(p, w.k_lo) * 8;
+    p.k = w.k_hi - w.k_lo;
+  }
 
   double acc[4][4][2];
 #pragma unroll
@@ -168,7 +177,7 @@ __global__ void __launch_bounds__(256, 2) gemm_dmma_d_kernel(GemmParams p, int t
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int row = m0 + wm * 32 + i * 8 + g;
-        if (row >= p.m) continue;
+        if (row >= p.m || (HINTS && out_masked(p, row, col))) continue;
         double out = alpha * acc[i][j][e];
         if (!beta_zero) out = fma(beta, ccol[row], out);
         ccol[row] = out;
@@ -178,7 +187,7 @@ __global__ void __launch_bounds__(256, 2) gemm_dmma_d_kernel(GemmParams p, int t
 
 // ---- complex double ------------------------------------------------------------------------------
 // CTA 64 x 64, 8 warps as 2 (m) x 4 (n), warp tile 32 x 16: 4 x 2 DMMA tiles, re and im planes.
-template <int OPA, int OPB>
+template <int OPA, int OPB, bool HINTS>
 __global__ void __launch_bounds__(256, 2) gemm_dmma_z_kernel(GemmParams p, int tiles_m, int tiles_n) {
   constexpr int BM = 64, BN = 64, BK = 8, STAGES = kStagesZ, THREADS = 256;
   constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
@@ -206,6 +215,13 @@ __global__ void __launch_bounds__(256, 2) gemm_dmma_z_kernel(GemmParams p, int t
   const unsigned char* A = (const unsigned char*)p.a + (item * p.sa + sv.a_off) * 16;
   const unsigned char* B = (const unsigned char*)p.b + (item * p.sb + sv.b_off) * 16;
   double2* C = (double2*)p.c + vitem * p.sc;
+  if constexpr (HINTS) {
+    const TileWork w = tile_work(p, p.k, m0, BM, n0, BN, BK);
+    if (w.skip) return;
+    A += a_k_offset(p, w.k_lo) * 16;
+    B += b_k_offset(p, w.k_lo) * 16;
+    p.k = w.k_hi - w.k_lo;
+  }
 
   double accr[4][2][2], acci[4][2][2];
 #pragma unroll
@@ -284,8 +300,15 @@ __global__ void __launch_bounds__(256, 2) gemm_dmma_z_kernel(GemmParams p, int t
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int row = m0 + wm * 32 + i * 8 + g;
-        if (row >= p.m) continue;
+        if (row >= p.m || (HINTS && out_masked(p, row, col))) continue;
         const double2 v = make_double2(accr[i][j][e], acci[i][j][e]);
+        if (HINTS && p.out_herm && row == col) {  // Hermitian diagonal: real in, real out
+          double2 o = Scalar<double2>::mul(alpha, v);
+          if (!beta_zero) o.x = fma(beta.x, ccol[row].x, o.x);
+          o.y = 0.0;
+          ccol[row] = o;
+          continue;
+        }
         ccol[row] = epilogue<double2>(alpha, v, beta, beta_zero, ccol + row);
       }
     }
@@ -311,16 +334,20 @@ template <int OPA, int OPB>
 int launch_d(const GemmParams& p, cudaStream_t stream) {
   constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
   constexpr size_t smem = kStagesD * (size_t)(pitched_stage_bytes<8, 128, 16, AK>() + pitched_stage_bytes<8, 64, 16, BKM>());
-  static thread_local int configured_for = -1;
-  return launch_kernel(gemm_dmma_d_kernel<OPA, OPB>, smem, p, 128, 64, stream, &configured_for);
+  static thread_local int configured_for = -1, configured_for_hints = -1;
+  if (p.tri_a | p.tri_b | p.out_tri)
+    return launch_kernel(gemm_dmma_d_kernel<OPA, OPB, true>, smem, p, 128, 64, stream, &configured_for_hints);
+  return launch_kernel(gemm_dmma_d_kernel<OPA, OPB, false>, smem, p, 128, 64, stream, &configured_for);
 }
 
 template <int OPA, int OPB>
 int launch_z(const GemmParams& p, cudaStream_t stream) {
   constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
   constexpr size_t smem = kStagesZ * (size_t)(pitched_stage_bytes<16, 64, 8, AK>() + pitched_stage_bytes<16, 64, 8, BKM>());
-  static thread_local int configured_for = -1;
-  return launch_kernel(gemm_dmma_z_kernel<OPA, OPB>, smem, p, 64, 64, stream, &configured_for);
+  static thread_local int configured_for = -1, configured_for_hints = -1;
+  if (p.tri_a | p.tri_b | p.out_tri)
+    return launch_kernel(gemm_dmma_z_kernel<OPA, OPB, true>, smem, p, 64, 64, stream, &configured_for_hints);
+  return launch_kernel(gemm_dmma_z_kernel<OPA, OPB, false>, smem, p, 64, 64, stream, &configured_for);
 }
 
 }  // namespace

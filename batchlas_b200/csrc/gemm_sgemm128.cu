@@ -78,7 +78,9 @@ __device__ __forceinline__ void load_b(unsigned char* dst, const float* __restri
   }
 }
 
-template <bool B_KMAJOR>
+// HINTS = false is the plain gemm; HINTS = true reads the structure hints of GemmParams (a separate
+// instantiation, so that the plain kernel's code and register allocation stay what they were).
+template <bool B_KMAJOR, bool HINTS>
 __global__ void __launch_bounds__(THREADS, 2) sgemm128_kernel(GemmParams p, int tiles_m, int tiles_n) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* As = smem;
@@ -93,11 +95,18 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm128_kernel(GemmParams p, int 
   const long long vitem = tile / tiles_per_item;
   const int rem = (int)(tile - vitem * tiles_per_item);
   const SplitView sv = resolve_split(p, vitem);
-  const int K = sv.k;
+  int K = sv.k;
   const int m0 = (rem % tiles_m) * BM, n0 = (rem / tiles_m) * BN;
   const float* A = (const float*)p.a + sv.item * p.sa + sv.a_off;
   const float* B = (const float*)p.b + sv.item * p.sb + sv.b_off;
   float* C = (float*)p.c + vitem * p.sc;
+  if constexpr (HINTS) {  // triangular operand: shorter k range; triangular output: maybe nothing
+    const TileWork w = tile_work(p, K, m0, BM, n0, BN, BK);
+    if (w.skip) return;
+    A += a_k_offset(p, w.k_lo);
+    B += b_k_offset(p, w.k_lo);
+    K = w.k_hi - w.k_lo;
+  }
 
   uint64_t accp[32];  // [row pair rp][col c]: rows (2rp, 2rp+1) of the lane's 8, column c of its 8
 #pragma unroll
@@ -188,7 +197,9 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm128_kernel(GemmParams p, int 
       float o[4];
       unpack2(accp[(2 * hgh) * 8 + c], o[0], o[1]);
       unpack2(accp[(2 * hgh + 1) * 8 + c], o[2], o[3]);
-      if (row + 4 <= p.m) {
+      // with a triangular output the vector store is used only strictly inside the wanted triangle
+      const bool whole = !HINTS || p.out_tri == 0 || (p.out_tri == 1 ? row >= col : row + 3 <= col);
+      if (row + 4 <= p.m && whole) {
         float4 out = make_float4(alpha * o[0], alpha * o[1], alpha * o[2], alpha * o[3]);
         if (!beta_zero) {
           const float4 pr = *reinterpret_cast<const float4*>(ccol + row);
@@ -201,7 +212,7 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm128_kernel(GemmParams p, int 
       } else {
 #pragma unroll
         for (int e = 0; e < 4; ++e)
-          if (row + e < p.m) {
+          if (row + e < p.m && !(HINTS && out_masked(p, row + e, col))) {
             float out = alpha * o[e];
             if (!beta_zero) out = fmaf(beta, ccol[row + e], out);
             ccol[row + e] = out;
@@ -211,13 +222,13 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm128_kernel(GemmParams p, int 
   }
 }
 
-template <bool B_KMAJOR>
+template <bool B_KMAJOR, bool HINTS>
 int launch_one(const GemmParams& p, cudaStream_t stream) {
   constexpr size_t smem = (size_t)STAGES * (A_STAGE + B_STAGE);
   const int tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BN - 1) / BN;
   const long long total = (long long)tiles_m * tiles_n * p.batch;
   if (total > 0x7fffffffLL) return BLB200_E_UNSUPPORTED;
-  auto kern = sgemm128_kernel<B_KMAJOR>;
+  auto kern = sgemm128_kernel<B_KMAJOR, HINTS>;
   static thread_local int configured_for = -1;
   int cur = 0;
   cudaGetDevice(&cur);
@@ -240,7 +251,9 @@ bool sgemm128_supported(const GemmParams& p, int dtype) {
 
 int launch_sgemm128(const GemmParams& p, int dtype, cudaStream_t stream) {
   if (!sgemm128_supported(p, dtype)) return BLB200_E_UNSUPPORTED;
-  const int rc = (p.op_b == BLB200_N) ? launch_one<true>(p, stream) : launch_one<false>(p, stream);
+  const bool hints = (p.tri_a | p.tri_b | p.out_tri) != 0;
+  const int rc = (p.op_b == BLB200_N) ? (hints ? launch_one<true, true>(p, stream) : launch_one<true, false>(p, stream))
+                                      : (hints ? launch_one<false, true>(p, stream) : launch_one<false, false>(p, stream));
   if (rc == BLB200_OK) note_launch("sgemm128");
   return rc;
 }

@@ -118,7 +118,9 @@ __device__ __forceinline__ void read_frag(const unsigned char* smem, int g, int 
   }
 }
 
-template <typename T, typename Cfg, int OPA, int OPB, int MIN_BLOCKS>
+// HINTS = false is the plain gemm; HINTS = true reads the structure hints of GemmParams (a separate
+// instantiation, so that the plain kernel's code and register allocation stay what they were).
+template <typename T, typename Cfg, int OPA, int OPB, int MIN_BLOCKS, bool HINTS>
 __global__ void __launch_bounds__(Cfg::THREADS, MIN_BLOCKS)
     gemm_tiled_kernel(GemmParams p, int tiles_m, int tiles_n) {
   constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, TM = Cfg::TM, TN = Cfg::TN, V = Cfg::V;
@@ -149,6 +151,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, MIN_BLOCKS)
   const T* A = (const T*)p.a + item * p.sa + sv.a_off;
   const T* B = (const T*)p.b + item * p.sb + sv.b_off;
   T* C = (T*)p.c + vitem * p.sc;
+  if constexpr (HINTS) {  // triangular operand: shorter k range; triangular output: maybe nothing
+    const TileWork w = tile_work(p, p.k, m0, BM, n0, BN, BK);
+    if (w.skip) return;
+    A += a_k_offset(p, w.k_lo);
+    B += b_k_offset(p, w.k_lo);
+    p.k = w.k_hi - w.k_lo;
+  }
 
   T acc[TM][TN];
 #pragma unroll
@@ -219,7 +228,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, MIN_BLOCKS)
 #pragma unroll
     for (int v = 0; v < TM / V; ++v) {
       const int row = m0 + v * (GM * V) + g * V;
-      if (row + V <= p.m) {
+      // with a triangular output the vector access is used only strictly inside the wanted triangle
+      const bool whole = !HINTS || p.out_tri == 0 || (p.out_tri == 1 ? row > col : row + V - 1 < col);
+      if (row + V <= p.m && whole) {
         union {
           uint4 u;
           T t[V];
@@ -235,21 +246,31 @@ __global__ void __launch_bounds__(Cfg::THREADS, MIN_BLOCKS)
       } else {
 #pragma unroll
         for (int e = 0; e < V; ++e) {
-          if (row + e < p.m) ccol[row + e] = epilogue<T>(alpha, acc[v * V + e][j], beta, beta_zero, ccol + row + e);
+          if (row + e >= p.m || (HINTS && out_masked(p, row + e, col))) continue;
+          if constexpr (HINTS && Scalar<T>::is_complex) {
+            if (p.out_herm && row + e == col) {  // Hermitian diagonal: real in, real out
+              T o = Scalar<T>::mul(alpha, acc[v * V + e][j]);
+              if (!beta_zero) o.x += beta.x * ccol[row + e].x;
+              o.y = 0;
+              ccol[row + e] = o;
+              continue;
+            }
+          }
+          ccol[row + e] = epilogue<T>(alpha, acc[v * V + e][j], beta, beta_zero, ccol + row + e);
         }
       }
     }
   }
 }
 
-template <typename T, typename Cfg, int OPA, int OPB, int MIN_BLOCKS>
+template <typename T, typename Cfg, int OPA, int OPB, int MIN_BLOCKS, bool HINTS>
 int launch_cfg(const GemmParams& p, cudaStream_t stream) {
   constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
   constexpr size_t smem = (size_t)Cfg::STAGES * (stage_bytes<T>(Cfg::BM, Cfg::BK, AK) + stage_bytes<T>(Cfg::BN, Cfg::BK, BKM));
   const int tiles_m = (p.m + Cfg::BM - 1) / Cfg::BM, tiles_n = (p.n + Cfg::BN - 1) / Cfg::BN;
   const long long total = (long long)tiles_m * tiles_n * p.batch;
   if (total > 0x7fffffffLL) return BLB200_E_UNSUPPORTED;
-  auto kern = gemm_tiled_kernel<T, Cfg, OPA, OPB, MIN_BLOCKS>;
+  auto kern = gemm_tiled_kernel<T, Cfg, OPA, OPB, MIN_BLOCKS, HINTS>;
   static thread_local int configured_for = -1;
   int cur = 0;
   cudaGetDevice(&cur);
@@ -265,8 +286,11 @@ int launch_cfg(const GemmParams& p, cudaStream_t stream) {
 template <typename T, typename Cfg, int MIN_BLOCKS>
 int launch_ops(const GemmParams& p, cudaStream_t stream) {
   const int oa = p.op_a, ob = p.op_b;
-#define BLB_OP(A_, B_) \
-  if (oa == A_ && ob == B_) return launch_cfg<T, Cfg, A_, B_, MIN_BLOCKS>(p, stream);
+  const bool hints = (p.tri_a | p.tri_b | p.out_tri) != 0;
+#define BLB_OP(A_, B_)                                                                    \
+  if (oa == A_ && ob == B_)                                                               \
+    return hints ? launch_cfg<T, Cfg, A_, B_, MIN_BLOCKS, true>(p, stream)                \
+                 : launch_cfg<T, Cfg, A_, B_, MIN_BLOCKS, false>(p, stream);
   BLB_OP(0, 0) BLB_OP(0, 1) BLB_OP(1, 0) BLB_OP(1, 1)
   if (Scalar<T>::is_complex) {
     BLB_OP(0, 2) BLB_OP(1, 2) BLB_OP(2, 0) BLB_OP(2, 1) BLB_OP(2, 2)

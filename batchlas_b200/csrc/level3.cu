@@ -14,8 +14,6 @@
 #include "common.cuh"
 
 namespace blb200 {
-int dispatch(const blb200_gemm_desc* d, cudaStream_t stream);
-
 namespace {
 
 size_t elem_bytes(int dtype) { return dtype == BLB200_S ? 4 : (dtype == BLB200_Z ? 16 : 8); }
@@ -72,12 +70,131 @@ __global__ void __launch_bounds__(256) accumulate_triangle_kernel(const T* __res
     if (lower ? (i < j) : (i > j)) continue;
     T v = prod[b * sp + (long long)j * ldp + i];
     T* c = C + b * sc + (long long)j * ldc + i;
-    if (!beta_zero) Scalar<T>::fma(v, beta, *c);
+    if (!beta_zero) {
+      T prior = *c;
+      if constexpr (Scalar<T>::is_complex) {
+        if (hermitian && i == j) prior.y = 0;  // not referenced: must not leak into the real part
+      }
+      Scalar<T>::fma(v, beta, prior);
+    }
     if constexpr (Scalar<T>::is_complex) {
       if (hermitian && i == j) v.y = 0;
     }
     *c = v;
   }
+}
+
+// ---- tiled versions for order >= 32 ------------------------------------------------------------------
+// One block per (item, pair of 32 x 32 tiles).  The stored tile is read once, coalesced, into shared
+// memory and written twice: as it is, and transposed (conjugated / zeroed as the mode asks) into the
+// mirror tile, so the unreferenced triangle is never read and every global access runs along rows.
+constexpr int kTile = 32;
+
+__device__ __forceinline__ void decode_pair(int idx, int nt, int& p, int& q) {  // idx -> (p >= q), column by column
+  q = 0;
+  while (idx >= nt - q) {
+    idx -= nt - q;
+    ++q;
+  }
+  p = q + idx;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) expand_tiled_kernel(const T* __restrict__ src, T* __restrict__ dst, int k,
+                                                           long long lds, long long ss, long long ldd, long long sd,
+                                                           int lower, int mode, int unit_diag) {
+  __shared__ T tile[kTile][kTile + 1];
+  const int nt = (k + kTile - 1) / kTile, pairs = nt * (nt + 1) / 2;
+  const T* s = src + (long long)blockIdx.x * ss;
+  T* d = dst + (long long)blockIdx.x * sd;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int pair = blockIdx.y; pair < pairs; pair += gridDim.y) {
+    int p, q;
+    decode_pair(pair, nt, p, q);
+    const int r0 = (lower ? p : q) * kTile, c0 = (lower ? q : p) * kTile;  // the stored tile: rows r0.., columns c0..
+    __syncthreads();
+    for (int jj = ty; jj < kTile; jj += 8) {
+      const int i = r0 + tx, j = c0 + jj;
+      const bool stored = lower ? (i >= j) : (i <= j);
+      if (i < k && j < k && stored) tile[jj][tx] = s[(long long)j * lds + i];
+    }
+    __syncthreads();
+    // the stored tile itself
+    for (int jj = ty; jj < kTile; jj += 8) {
+      const int i = r0 + tx, j = c0 + jj;
+      if (i >= k || j >= k) continue;
+      const bool stored = lower ? (i >= j) : (i <= j);
+      T v;
+      if (i == j) {
+        v = tile[jj][tx];
+        if (mode == kTriangular && unit_diag) v = Scalar<T>::make(1.0, 0.0);
+        if constexpr (Scalar<T>::is_complex) {
+          if (mode == kMirrorConj) v.y = 0;
+        }
+      } else if (stored) {
+        v = tile[jj][tx];
+      } else if (mode == kTriangular) {  // only in a diagonal tile
+        v = Scalar<T>::zero();
+      } else {
+        v = tile[tx][jj];
+        if (mode == kMirrorConj) v = Scalar<T>::conj(v);
+      }
+      d[(long long)j * ldd + i] = v;
+    }
+    if (p == q) continue;
+    // the mirror tile: rows c0.., columns r0..
+    for (int jj = ty; jj < kTile; jj += 8) {
+      const int i = c0 + tx, j = r0 + jj;
+      if (i >= k || j >= k) continue;
+      T v;
+      if (mode == kTriangular) {
+        v = Scalar<T>::zero();
+      } else {
+        v = tile[tx][jj];
+        if (mode == kMirrorConj) v = Scalar<T>::conj(v);
+      }
+      d[(long long)j * ldd + i] = v;
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) accumulate_tiled_kernel(const T* __restrict__ prod, T* __restrict__ C, int n,
+                                                               long long ldp, long long sp, long long ldc, long long sc,
+                                                               int lower, T beta, bool beta_zero, int hermitian) {
+  const int nt = (n + kTile - 1) / kTile, pairs = nt * (nt + 1) / 2;
+  const T* pr = prod + (long long)blockIdx.x * sp;
+  T* c = C + (long long)blockIdx.x * sc;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int pair = blockIdx.y; pair < pairs; pair += gridDim.y) {
+    int p, q;
+    decode_pair(pair, nt, p, q);
+    const int r0 = (lower ? p : q) * kTile, c0 = (lower ? q : p) * kTile;
+#pragma unroll 4
+    for (int jj = ty; jj < kTile; jj += 8) {
+      const int i = r0 + tx, j = c0 + jj;
+      if (i >= n || j >= n || (lower ? (i < j) : (i > j))) continue;
+      T v = pr[(long long)j * ldp + i];
+      T* dst = c + (long long)j * ldc + i;
+      if (!beta_zero) {
+        T prior = *dst;
+        if constexpr (Scalar<T>::is_complex) {
+          if (hermitian && i == j) prior.y = 0;
+        }
+        Scalar<T>::fma(v, beta, prior);
+      }
+      if constexpr (Scalar<T>::is_complex) {
+        if (hermitian && i == j) v.y = 0;
+      }
+      *dst = v;
+    }
+  }
+}
+
+dim3 pair_grid(int order, int batch) {
+  const int nt = (order + kTile - 1) / kTile;
+  const long long pairs = (long long)nt * (nt + 1) / 2;
+  return dim3((unsigned)batch, (unsigned)(pairs < 65535 ? pairs : 65535), 1);
 }
 
 template <typename F>
@@ -101,8 +218,12 @@ int expand(int dtype, const void* src, void* dst, int k, int batch, long long ld
   if (k == 0 || batch == 0) return BLB200_OK;
   return for_dtype(dtype, [&](auto* tag) {
     using T = std::remove_pointer_t<decltype(tag)>;
-    expand_kernel<T><<<grid_for((long long)k * k * batch), 256, 0, stream>>>((const T*)src, (T*)dst, k, batch, lds, ss,
-                                                                            ldd, sd, lower, mode, unit_diag);
+    if (k >= kTile)
+      expand_tiled_kernel<T><<<pair_grid(k, batch), 256, 0, stream>>>((const T*)src, (T*)dst, k, lds, ss, ldd, sd, lower,
+                                                                      mode, unit_diag);
+    else
+      expand_kernel<T><<<grid_for((long long)k * k * batch), 256, 0, stream>>>((const T*)src, (T*)dst, k, batch, lds, ss,
+                                                                              ldd, sd, lower, mode, unit_diag);
     return (int)cudaGetLastError();
   });
 }
@@ -184,15 +305,21 @@ int blb200_trmm(const blb200_gemm_desc* desc, int32_t side, int32_t uplo, int32_
   g.k = k;
   g.beta[0] = g.beta[1] = 0.0;
   g.kernel_hint = 0;
+  // The expanded operand keeps its zeros, and the tile kernels are told where they are so that each
+  // output tile stops (or starts) its k loop at the diagonal: about half the work for a square B.
+  const bool lower_after_op = (uplo == 1) == (desc->op_a == BLB200_N);
+  StructureHints hints{0, 0, 0, 0};
   if (side == 0) {
     g.a = workspace; g.lda = ld; g.stride_a = ld * k;
     g.op_a = desc->op_a; g.op_b = BLB200_N;
+    hints.tri_a = lower_after_op ? 1 : 2;
   } else {
     g.a = desc->b; g.lda = desc->ldb; g.stride_a = desc->stride_b;
     g.b = workspace; g.ldb = ld; g.stride_b = ld * k;
     g.op_a = BLB200_N; g.op_b = desc->op_a;
+    hints.tri_b = lower_after_op ? 1 : 2;
   }
-  return dispatch(&g, stream);
+  return dispatch_structured(&g, &hints, stream);
 }
 
 // syrk (hermitian = 0: op_a N or T) / herk (hermitian = 1: op_a N or H, alpha/beta real).
@@ -212,29 +339,43 @@ int blb200_syrk(const blb200_gemm_desc* desc, int32_t uplo, int32_t hermitian, v
   if (n == 0 || desc->batch == 0) return BLB200_OK;
   if (desc->lda < (opa == BLB200_N ? n : (k > 1 ? k : 1)) || desc->ldc < n) return BLB200_E_SHAPE;
   if (!desc->c || (k > 0 && !desc->a)) return BLB200_E_NULL;
-  const size_t need = blb200_level3_workspace_bytes(desc->dtype, n, desc->batch);
-  if (!workspace) return BLB200_E_NULL;
-  if (workspace_bytes < need) return BLB200_E_TOO_LARGE;
   cudaStream_t stream = (cudaStream_t)cuda_stream;
-  const long long ld = expanded_ld(desc->dtype, n);
   blb200_gemm_desc g = *desc;
   g.m = n; g.n = n; g.k = k;
   g.b = desc->a; g.ldb = desc->lda; g.stride_b = desc->stride_a;
-  g.c = workspace; g.ldc = ld; g.stride_c = ld * n;
   g.op_a = opa;
   g.op_b = (opa == BLB200_N) ? (hermitian ? BLB200_H : BLB200_T) : BLB200_N;
-  g.beta[0] = g.beta[1] = 0.0;
-  if (hermitian) g.alpha[1] = 0.0;
+  if (hermitian) g.alpha[1] = g.beta[1] = 0.0;
   g.kernel_hint = 0;
+  // First choice: a tile kernel writes the wanted triangle of C itself — tiles wholly in the other
+  // triangle do nothing, tiles on the diagonal mask their stores — so there is no scratch, no second
+  // pass and about half the arithmetic.
+  if (k > 0) {
+    const StructureHints hints{0, 0, uplo == 1 ? 1 : 2, hermitian ? 1 : 0};
+    rc = dispatch_structured(&g, &hints, stream);
+    if (rc != BLB200_E_UNSUPPORTED) return rc;
+  }
+  // Otherwise (operands the tile kernels do not take): full product into scratch, then accumulate.
+  const size_t need = blb200_level3_workspace_bytes(desc->dtype, n, desc->batch);
+  if (!workspace) return BLB200_E_NULL;
+  if (workspace_bytes < need) return BLB200_E_TOO_LARGE;
+  const long long ld = expanded_ld(desc->dtype, n);
+  g.c = workspace; g.ldc = ld; g.stride_c = ld * n;
+  g.beta[0] = g.beta[1] = 0.0;
   rc = dispatch(&g, stream);
   if (rc != BLB200_OK) return rc;
   return for_dtype(desc->dtype, [&](auto* tag) {
     using T = std::remove_pointer_t<decltype(tag)>;
     const T beta = Scalar<T>::make(desc->beta[0], hermitian ? 0.0 : desc->beta[1]);
     const bool beta_zero = desc->beta[0] == 0.0 && (hermitian || desc->dtype < BLB200_C || desc->beta[1] == 0.0);
-    accumulate_triangle_kernel<T><<<grid_for((long long)n * n * desc->batch), 256, 0, stream>>>(
-        (const T*)workspace, (T*)desc->c, n, desc->batch, ld, ld * n, desc->ldc, desc->stride_c, uplo == 1, beta,
-        beta_zero, hermitian);
+    if (n >= kTile)
+      accumulate_tiled_kernel<T><<<pair_grid(n, desc->batch), 256, 0, stream>>>(
+          (const T*)workspace, (T*)desc->c, n, ld, ld * n, desc->ldc, desc->stride_c, uplo == 1, beta, beta_zero,
+          hermitian);
+    else
+      accumulate_triangle_kernel<T><<<grid_for((long long)n * n * desc->batch), 256, 0, stream>>>(
+          (const T*)workspace, (T*)desc->c, n, desc->batch, ld, ld * n, desc->ldc, desc->stride_c, uplo == 1, beta,
+          beta_zero, hermitian);
     return (int)cudaGetLastError();
   });
 }

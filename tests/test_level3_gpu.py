@@ -103,9 +103,16 @@ def test_symm_beta_zero_ignores_nan_in_c(bl):
     assert ok, worst
 
 
+def apad(rows, aligned, odd):
+    """Padding rows: `odd` as given, or what makes the leading dimension a multiple of 4 elements
+    (16-byte aligned columns for every dtype) when the tile kernels are to be reached."""
+    return (-rows) % 4 + 4 if aligned else odd
+
+
+@pytest.mark.parametrize("aligned", [False, True], ids=["oddld", "alignedld"])
 @pytest.mark.parametrize("dt", "sdcz")
-@pytest.mark.parametrize("shape", [(48, 32, 2), (17, 33, 3), (128, 128, 4)], ids=str)
-def test_trmm_all_combinations(bl, dt, shape):
+@pytest.mark.parametrize("shape", [(48, 32, 2), (17, 33, 3), (128, 128, 4), (200, 136, 2)], ids=str)
+def test_trmm_all_combinations(bl, dt, shape, aligned):
     dtype = NP_DT[dt]
     m, n, batch = shape
     rng = np.random.default_rng(200 + m)
@@ -113,12 +120,12 @@ def test_trmm_all_combinations(bl, dt, shape):
     for side in (0, 1):
         k = m if side == 0 else n
         a, b = rnd(rng, (batch, k, k), dtype), rnd(rng, (batch, m, n), dtype)
-        dB, _ = to_dev(b, pad=2)
+        dB, _ = to_dev(b, pad=apad(m, aligned, 2))
         for uplo in (0, 1):
             for unit in (False, True):
                 dA, _ = to_dev(poison_other_triangle(a, uplo, diag_too=unit), pad=1)
                 for op in (0, 1, 2):
-                    dC, backC = to_dev(np.full((batch, m, n), np.nan, dtype), pad=4)
+                    dC, backC = to_dev(np.full((batch, m, n), np.nan, dtype), pad=apad(m, aligned, 5))
                     bl.trmm(dA, dB, dC, alpha, side, uplo, op, int(unit))
                     exact, bound = L.trmm_exact(a, b, alpha, side, uplo, op, unit)
                     ok, worst = L.within(from_dev(dC), exact, bound, k, dtype)
@@ -126,9 +133,10 @@ def test_trmm_all_combinations(bl, dt, shape):
                     assert bool((backC[:, :, m:] == 7.0).all())
 
 
+@pytest.mark.parametrize("aligned", [False, True], ids=["oddld", "alignedld"])
 @pytest.mark.parametrize("dt", "sdcz")
-@pytest.mark.parametrize("shape", [(65, 40, 4), (32, 24, 3), (128, 200, 3), (7, 1, 2)], ids=str)
-def test_syrk_herk(bl, dt, shape):
+@pytest.mark.parametrize("shape", [(65, 40, 4), (32, 24, 3), (128, 200, 3), (7, 1, 2), (300, 72, 2)], ids=str)
+def test_syrk_herk(bl, dt, shape, aligned):
     dtype = NP_DT[dt]
     n, k, batch = shape
     rng = np.random.default_rng(300 + n)
@@ -137,7 +145,7 @@ def test_syrk_herk(bl, dt, shape):
         for op in ((0, 2) if herm else (0, 1)):
             a = rnd(rng, (batch, n, k) if op == 0 else (batch, k, n), dtype)
             c0 = rnd(rng, (batch, n, n), dtype)
-            dA, _ = to_dev(a, pad=2)
+            dA, _ = to_dev(a, pad=apad(a.shape[1], aligned, 2))
             for uplo in (0, 1):
                 for alpha, beta in [(0.9, -0.35), (1.5, 0.0)]:
                     if not herm and dt in "cz":
@@ -146,7 +154,11 @@ def test_syrk_herk(bl, dt, shape):
                     if beta == 0:  # C is not an input at all then
                         mask_ref = np.tril(np.ones((n, n), bool)) if uplo == 1 else np.triu(np.ones((n, n), bool))
                         c_in[:, mask_ref] = np.nan
-                    dC, backC = to_dev(c_in, pad=3)
+                    if herm:  # the imaginary part of a Hermitian diagonal is not an input either
+                        diag = c_in[:, idx, idx].copy()
+                        diag.imag = np.nan
+                        c_in[:, idx, idx] = diag
+                    dC, backC = to_dev(c_in, pad=apad(n, aligned, 3))
                     bl.syrk(dA, dC, alpha, beta, uplo, op, hermitian=herm)
                     got = from_dev(dC)
                     exact, bound, mask = L.syrk_exact(a, c_in, alpha, beta, uplo, op, herm)
@@ -173,6 +185,24 @@ def test_herk_triangles_agree_across_uplo(bl):
     l, u = from_dev(lo), from_dev(up)
     assert np.allclose(np.tril(l), np.conj(np.swapaxes(np.triu(u), 1, 2)), rtol=0, atol=1e-12)
     assert np.all(np.triu(l, 1) == 0) and np.all(np.tril(u, -1) == 0)
+
+
+def test_syrk_needs_no_scratch_on_aligned_operands(bl, lib):
+    """16-byte aligned operands go straight to a tile kernel that writes the triangle itself, so the
+    scratch may be absent; anything else needs it and says so."""
+    rng = np.random.default_rng(23)
+    n, k, batch = 160, 96, 3
+    a, c0 = rnd(rng, (batch, n, k), np.float64), rnd(rng, (batch, n, n), np.float64)
+    dA, _ = to_dev(a)
+    dC, _ = to_dev(c0)
+    d = bl.make_desc(dA.data_ptr(), 0, dC.data_ptr(), 1, 0, 0, n, n, k, batch, n, 1, n, n * k, 0, n * n, 0.9, -0.35)
+    assert lib.blb200_syrk(d, 1, 0, None, 0, torch.cuda.current_stream().cuda_stream) == 0
+    exact, bound, mask = L.syrk_exact(a, c0, 0.9, -0.35, 1, 0)
+    ok, worst = L.within(from_dev(dC), exact, bound, k, np.float64, mask)
+    assert ok, worst
+    dA2, _ = to_dev(a, pad=1)  # ld 161: columns no longer 16-byte aligned
+    d2 = bl.make_desc(dA2.data_ptr(), 0, dC.data_ptr(), 1, 0, 0, n, n, k, batch, n + 1, 1, n, (n + 1) * k, 0, n * n)
+    assert lib.blb200_syrk(d2, 1, 0, None, 0, None) == bl._lib.E_NULL
 
 
 def test_level3_error_paths(bl, lib):
