@@ -9,10 +9,10 @@ from . import _lib
 from ._lib import BlasError, GemmDesc, KERNEL_IDS
 from .gemm import (DTYPE_CODES, Transpose, device_status, fill, gemm, gemm_host, gemm_strided_batched,
                    last_kernel_name, launch_count, make_desc, measure_pipe_peak)
-from .level3 import Diag, Side, Uplo, hemm, herk, symm, syrk, trmm
+from .level3 import Diag, Side, Uplo, hemm, her2k, herk, symm, syr2k, syrk, trmm
 from .sharding import shard_range
 
 __all__ = ["_lib", "BlasError", "GemmDesc", "KERNEL_IDS", "DTYPE_CODES", "Transpose", "device_status",
            "fill", "gemm", "gemm_host", "gemm_strided_batched", "last_kernel_name", "launch_count",
            "make_desc", "measure_pipe_peak", "shard_range", "Side", "Uplo", "Diag", "symm", "hemm", "trmm", "syrk",
-           "herk"]
+           "herk", "syr2k", "her2k"]

@@ -58,6 +58,8 @@ SIGNATURES = {
                                    ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     "blb200_syrk": (ctypes.c_int, [ctypes.POINTER(GemmDesc), ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
                                    ctypes.c_size_t, ctypes.c_void_p]),
+    "blb200_syr2k": (ctypes.c_int, [ctypes.POINTER(GemmDesc), ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
+                                    ctypes.c_size_t, ctypes.c_void_p]),
     "blb200_gemm_strided_batched_host": (ctypes.c_int, [ctypes.POINTER(GemmDesc), ctypes.c_int, ctypes.c_int32]),
     "blb200_last_kernel_name": (ctypes.c_char_p, []),
     "blb200_launch_count": (ctypes.c_uint64, []),

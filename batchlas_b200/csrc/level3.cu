@@ -191,6 +191,57 @@ __global__ void __launch_bounds__(256) accumulate_tiled_kernel(const T* __restri
   }
 }
 
+// Two-sided accumulate of syr2k / her2k: the `lower`/upper triangle of C <- P + P^T|H + beta * C,
+// P = alpha * op(A) * op(B)^T|H already in scratch (BatchLAS accumulate_hermitian<T, TwoSided>,
+// src/backends/cublas.cc:441-502).  Both tiles of P that meet in an output tile go through shared
+// memory, so P is read along its rows only.
+template <typename T>
+__global__ void __launch_bounds__(256) accumulate2_tiled_kernel(const T* __restrict__ prod, T* __restrict__ C, int n,
+                                                                long long ldp, long long sp, long long ldc, long long sc,
+                                                                int lower, T beta, bool beta_zero, int hermitian) {
+  __shared__ T mirror[kTile][kTile + 1];
+  const int nt = (n + kTile - 1) / kTile, pairs = nt * (nt + 1) / 2;
+  const T* pr = prod + (long long)blockIdx.x * sp;
+  T* c = C + (long long)blockIdx.x * sc;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int pair = blockIdx.y; pair < pairs; pair += gridDim.y) {
+    int p, q;
+    decode_pair(pair, nt, p, q);
+    const int r0 = (lower ? p : q) * kTile, c0 = (lower ? q : p) * kTile;  // output tile: rows r0.., columns c0..
+    __syncthreads();
+    for (int jj = ty; jj < kTile; jj += 8) {  // the tile of P across the diagonal: rows c0.., columns r0..
+      const int i = c0 + tx, j = r0 + jj;
+      if (i < n && j < n) mirror[jj][tx] = pr[(long long)j * ldp + i];
+    }
+    __syncthreads();
+    for (int jj = ty; jj < kTile; jj += 8) {
+      const int i = r0 + tx, j = c0 + jj;
+      if (i >= n || j >= n || (lower ? (i < j) : (i > j))) continue;
+      T v = pr[(long long)j * ldp + i];
+      T w = mirror[tx][jj];  // P(j, i)
+      if (hermitian) w = Scalar<T>::conj(w);
+      if constexpr (Scalar<T>::is_complex) {
+        v.x += w.x;
+        v.y += w.y;
+      } else {
+        v += w;
+      }
+      T* dst = c + (long long)j * ldc + i;
+      if (!beta_zero) {
+        T prior = *dst;
+        if constexpr (Scalar<T>::is_complex) {
+          if (hermitian && i == j) prior.y = 0;
+        }
+        Scalar<T>::fma(v, beta, prior);
+      }
+      if constexpr (Scalar<T>::is_complex) {
+        if (hermitian && i == j) v.y = 0;
+      }
+      *dst = v;
+    }
+  }
+}
+
 dim3 pair_grid(int order, int batch) {
   const int nt = (order + kTile - 1) / kTile;
   const long long pairs = (long long)nt * (nt + 1) / 2;
@@ -376,6 +427,49 @@ int blb200_syrk(const blb200_gemm_desc* desc, int32_t uplo, int32_t hermitian, v
       accumulate_triangle_kernel<T><<<grid_for((long long)n * n * desc->batch), 256, 0, stream>>>(
           (const T*)workspace, (T*)desc->c, n, desc->batch, ld, ld * n, desc->ldc, desc->stride_c, uplo == 1, beta,
           beta_zero, hermitian);
+    return (int)cudaGetLastError();
+  });
+}
+
+// syr2k (hermitian = 0: C_tri <- alpha*op(A)*op(B)^T + alpha*op(B)*op(A)^T + beta*C_tri, op_a N or T)
+// her2k (hermitian = 1: C_tri <- alpha*op(A)*op(B)^H + conj(alpha)*op(B)*op(A)^H + beta*C_tri, op_a N or
+// H, beta real, diagonal real).  One gemm P = alpha*op(A)*op(B)^T|H into scratch, then P + P^T|H is
+// accumulated into the wanted triangle.  desc: a = A, b = B (same shape as A), c = C (n x n).
+int blb200_syr2k(const blb200_gemm_desc* desc, int32_t uplo, int32_t hermitian, void* workspace, size_t workspace_bytes,
+                 void* cuda_stream) {
+  using namespace blb200;
+  int rc = check_common(desc, 0, uplo);
+  if (rc != BLB200_OK) return rc;
+  if (hermitian && desc->dtype < BLB200_C) return BLB200_E_DTYPE;
+  const int n = desc->n, k = desc->k;
+  if (k < 0) return BLB200_E_SHAPE;
+  int opa = desc->op_a;
+  if (!hermitian && opa == BLB200_H && desc->dtype < BLB200_C) opa = BLB200_T;
+  if (hermitian ? (opa != BLB200_N && opa != BLB200_H) : (opa != BLB200_N && opa != BLB200_T)) return BLB200_E_DTYPE;
+  if (n == 0 || desc->batch == 0) return BLB200_OK;
+  const long long min_ld = opa == BLB200_N ? n : (k > 1 ? k : 1);
+  if (desc->lda < min_ld || desc->ldb < min_ld || desc->ldc < n) return BLB200_E_SHAPE;
+  if (!desc->c || (k > 0 && (!desc->a || !desc->b))) return BLB200_E_NULL;
+  const size_t need = blb200_level3_workspace_bytes(desc->dtype, n, desc->batch);
+  if (!workspace) return BLB200_E_NULL;
+  if (workspace_bytes < need) return BLB200_E_TOO_LARGE;
+  cudaStream_t stream = (cudaStream_t)cuda_stream;
+  const long long ld = expanded_ld(desc->dtype, n);
+  blb200_gemm_desc g = *desc;
+  g.m = n; g.n = n; g.k = k;
+  g.op_a = opa;
+  g.op_b = (opa == BLB200_N) ? (hermitian ? BLB200_H : BLB200_T) : BLB200_N;
+  g.c = workspace; g.ldc = ld; g.stride_c = ld * n;
+  g.beta[0] = g.beta[1] = 0.0;
+  g.kernel_hint = 0;
+  rc = dispatch(&g, stream);
+  if (rc != BLB200_OK) return rc;
+  return for_dtype(desc->dtype, [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    const T beta = Scalar<T>::make(desc->beta[0], hermitian ? 0.0 : desc->beta[1]);
+    const bool beta_zero = desc->beta[0] == 0.0 && (hermitian || desc->dtype < BLB200_C || desc->beta[1] == 0.0);
+    accumulate2_tiled_kernel<T><<<pair_grid(n, desc->batch), 256, 0, stream>>>(
+        (const T*)workspace, (T*)desc->c, n, ld, ld * n, desc->ldc, desc->stride_c, uplo == 1, beta, beta_zero, hermitian);
     return (int)cudaGetLastError();
   });
 }

@@ -1,5 +1,5 @@
 """Host-side mirror of the level-3 calls BatchLAS implements through gemm — ``symm``, ``hemm``,
-``trmm``, ``syrk``, ``herk`` — over torch tensors (device memory and streams only).
+``trmm``, ``syrk``, ``herk``, ``syr2k``, ``her2k`` — over torch tensors (device memory and streams only).
 
 Tensors use the convention of :mod:`batchlas_b200.gemm`: a column-major ``rows x cols`` matrix is a
 tensor of shape ``(batch, cols, rows)`` with unit stride along ``rows``.  Argument meaning follows
@@ -159,6 +159,47 @@ def syrk(A, C, alpha=1.0, beta=0.0, uplo: Uplo = Uplo.Lower, transA: Transpose =
         check(load().blb200_syrk(d, int(uplo), int(bool(hermitian)), ws.data_ptr(), ws.numel(), _stream(stream)))
         ws.record_stream(torch.cuda.current_stream())
     return C
+
+
+def syr2k(A, B, C, alpha=1.0, beta=0.0, uplo: Uplo = Uplo.Lower, transA: Transpose = Transpose.NoTrans, *,
+          hermitian=False, workspace=None, stream=None):
+    """The `uplo` triangle of C <- alpha*op(A)*op(B)^T + alpha*op(B)*op(A)^T + beta*C (syr2k) or
+    alpha*op(A)*op(B)^H + conj(alpha)*op(B)*op(A)^H + beta*C (her2k: beta real, real diagonal)."""
+    name = "HER2K" if hermitian else "SYR2K"
+    A, B, C = _prep(A, B, C)
+    if C.shape[1] != C.shape[2]:
+        raise RuntimeError(f"{name}: C must be square")
+    if not (A.shape[0] == B.shape[0] == C.shape[0]):
+        raise RuntimeError(f"{name}: batch size mismatch")
+    ta = Transpose(transA)
+    if hermitian:
+        if not A.is_complex():
+            raise TypeError("HER2K needs a complex dtype")
+        if ta == Transpose.Trans:
+            raise RuntimeError("HER2K: transA must be NoTrans or ConjTrans")
+        beta = float(beta)
+    elif ta == Transpose.ConjTrans:
+        if A.is_complex():
+            raise RuntimeError("SYR2K: transA must be NoTrans or Trans for complex types")
+        ta = Transpose.Trans
+    n = C.shape[2]
+    no_trans = ta == Transpose.NoTrans
+    expected_n, k = (A.shape[2], A.shape[1]) if no_trans else (A.shape[1], A.shape[2])
+    b_n, b_k = (B.shape[2], B.shape[1]) if no_trans else (B.shape[1], B.shape[2])
+    if expected_n != n or b_n != n or b_k != k or k <= 0:
+        raise RuntimeError(f"{name}: incompatible matrix dimensions")
+    d = make_desc(A.data_ptr(), B.data_ptr(), C.data_ptr(), DTYPE_CODES[A.dtype], ta, 0, n, n, k, A.shape[0],
+                  _ld(A), _ld(B), _ld(C), _st(A), _st(B), _st(C), alpha, beta)
+    with torch.cuda.device(C.device):
+        need = workspace_bytes(A.dtype, n, A.shape[0])
+        ws = _scratch(workspace, need, C.device)
+        check(load().blb200_syr2k(d, int(uplo), int(bool(hermitian)), ws.data_ptr(), ws.numel(), _stream(stream)))
+        ws.record_stream(torch.cuda.current_stream())
+    return C
+
+
+def her2k(A, B, C, alpha=1.0, beta=0.0, uplo: Uplo = Uplo.Lower, transA: Transpose = Transpose.NoTrans, **kw):
+    return syr2k(A, B, C, alpha, beta, uplo, transA, hermitian=True, **kw)
 
 
 def herk(A, C, alpha=1.0, beta=0.0, uplo: Uplo = Uplo.Lower, transA: Transpose = Transpose.NoTrans, **kw):

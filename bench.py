@@ -553,7 +553,7 @@ def run_case(args):
 
 
 def run_level3(args):
-    """symm / hemm / trmm / syrk / herk (the calls BatchLAS builds on gemm) on square operands, each
+    """symm / hemm / trmm / syrk / herk / syr2k / her2k (the calls BatchLAS builds on gemm) on square operands, each
     beside the plain gemm of the same shape: the difference is the cost of expanding the triangle
     (or of accumulating one).  One JSON line; times are CUDA events per call, after warm-up."""
     import torch
@@ -576,10 +576,12 @@ def run_level3(args):
             "symm": (lambda: bl.symm(A, B, C, 1.0, 0.5, 0, 1, workspace=ws), 2.0 * n * n * n),
             "trmm": (lambda: bl.trmm(A, B, C, 1.0, 0, 1, 0, 0, workspace=ws), 1.0 * n * n * n),
             "syrk": (lambda: bl.syrk(A, C, 1.0, 0.5, 1, 0, workspace=ws), 1.0 * n * n * (n + 1)),
+            "syr2k": (lambda: bl.syr2k(A, B, C, 1.0, 0.5, 1, 0, workspace=ws), 2.0 * n * n * (n + 1)),
         }
         if cplx:
             calls["hemm"] = (lambda: bl.hemm(A, B, C, 1.0, 0.5, 0, 1, workspace=ws), 2.0 * n * n * n)
             calls["herk"] = (lambda: bl.herk(A, C, 1.0, 0.5, 1, 0, workspace=ws), 1.0 * n * n * (n + 1))
+            calls["her2k"] = (lambda: bl.her2k(A, B, C, 1.0, 0.5, 1, 0, workspace=ws), 2.0 * n * n * (n + 1))
         row = {"dtype": dt, "n": n, "batch": batch, "ops": {}}
         for name, (fn, fl) in calls.items():
             for _ in range(max(args.warmup, 3)):

@@ -738,6 +738,72 @@ inline Event herk(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const
   return with_backend(ctx, [&](auto Bk) { return herk<Bk.value, T>(ctx, A, C, o.alpha, o.beta, o.uplo, o.trans); });
 }
 
+template <typename T>
+struct Syr2kOptions {
+  T alpha = T(1);
+  T beta = T(0);
+  Uplo uplo = Uplo::Lower;
+  Transpose trans = Transpose::NoTrans;
+};
+template <typename T>
+struct Her2kOptions {
+  T alpha = T(1);
+  float_t<T> beta = float_t<T>(0);
+  Uplo uplo = Uplo::Lower;
+  Transpose trans = Transpose::NoTrans;
+};
+
+namespace detail {
+template <typename T>
+inline Event syr2k_like(Queue& ctx, const char* name, bool hermitian, const MatrixView<T, MatrixFormat::Dense>& A,
+                        const MatrixView<T, MatrixFormat::Dense>& B, const MatrixView<T, MatrixFormat::Dense>& C, T alpha,
+                        T beta, Uplo uplo, Transpose transA) {
+  const std::string nm(name);
+  if (C.rows() != C.cols()) throw std::runtime_error(nm + ": C must be square");
+  if (A.batch_size() != B.batch_size() || A.batch_size() != C.batch_size())
+    throw std::runtime_error(nm + ": batch size mismatch");
+  if (hermitian && transA == Transpose::Trans) throw std::runtime_error(nm + ": transA must be NoTrans or ConjTrans");
+  const bool no_trans = transA == Transpose::NoTrans;
+  const int n = C.rows(), k = no_trans ? A.cols() : A.rows(), expected_n = no_trans ? A.rows() : A.cols();
+  const int b_n = no_trans ? B.rows() : B.cols(), b_k = no_trans ? B.cols() : B.rows();
+  if (expected_n != n || b_n != n || b_k != k || k <= 0) throw std::runtime_error(nm + ": incompatible matrix dimensions");
+  blb200_gemm_desc d = level3_desc<T>(A, &B, C);
+  d.m = n; d.n = n; d.k = k;
+  d.op_a = (int)transA;
+  set_scalar(d.alpha, alpha);
+  set_scalar(d.beta, beta);
+  ctx.make_current();
+  WorkspaceLease ws = ctx.workspace(std::max<size_t>(blb200_level3_workspace_bytes(d.dtype, n, d.batch), 16));
+  status_check(blb200_syr2k(&d, (int)uplo, hermitian ? 1 : 0, ws.data(), ws.size(), ctx.native_stream()));
+  return ctx.create_event_after_external_work();
+}
+}  // namespace detail
+
+template <Backend Back, typename T>
+inline Event syr2k(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
+                   const MatrixView<T, MatrixFormat::Dense>& C, T alpha, T beta, Uplo uplo, Transpose transA) {
+  static_assert(Back == Backend::CUDA, "only the CUDA backend exists in this build");
+  return detail::syr2k_like<T>(ctx, "SYR2K", false, A, B, C, alpha, beta, uplo, transA);
+}
+template <typename T>
+inline Event syr2k(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
+                   const MatrixView<T, MatrixFormat::Dense>& C, const Syr2kOptions<std::type_identity_t<T>>& o = {}) {
+  return with_backend(ctx, [&](auto Bk) { return syr2k<Bk.value, T>(ctx, A, B, C, o.alpha, o.beta, o.uplo, o.trans); });
+}
+// her2k: complex alpha, real beta (include/blas/functions/her2k.hh; src/backends/cublas.cc:609-666).
+template <Backend Back, typename T>
+inline Event her2k(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
+                   const MatrixView<T, MatrixFormat::Dense>& C, T alpha, float_t<T> beta, Uplo uplo, Transpose transA) {
+  static_assert(Back == Backend::CUDA, "only the CUDA backend exists in this build");
+  static_assert(!std::is_floating_point_v<T>, "her2k needs a complex scalar; use syr2k for real data");
+  return detail::syr2k_like<T>(ctx, "HER2K", true, A, B, C, alpha, T(beta), uplo, transA);
+}
+template <typename T>
+inline Event her2k(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
+                   const MatrixView<T, MatrixFormat::Dense>& C, const Her2kOptions<std::type_identity_t<T>>& o = {}) {
+  return with_backend(ctx, [&](auto Bk) { return her2k<Bk.value, T>(ctx, A, B, C, o.alpha, o.beta, o.uplo, o.trans); });
+}
+
 // Out of place, as the reference's trmm: C <- alpha * op(tri(A)) * B or alpha * B * op(tri(A)).
 template <Backend Back, typename T>
 inline Event trmm(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,

@@ -231,6 +231,15 @@ int blb200_trmm(const blb200_gemm_desc* desc, int32_t side, int32_t uplo, int32_
 int blb200_syrk(const blb200_gemm_desc* desc, int32_t uplo, int32_t hermitian, void* workspace, size_t workspace_bytes,
                 void* cuda_stream);
 
+/* syr2k (hermitian 0: op_a N or T) / her2k (hermitian 1: op_a N or H, complex only, only the real
+ * part of beta is used, the diagonal comes out real): the `uplo` triangle of C (n x n) <-
+ * alpha*op(A)*op(B)^T + alpha*op(B)*op(A)^T + beta*C, resp. alpha*op(A)*op(B)^H +
+ * conj(alpha)*op(B)*op(A)^H + beta*C.  desc: a = A, b = B (same shape: n x k for op N, else k x n),
+ * c = C; m, op_b are ignored.  Replaces her2k_vendor's gemm route (cublas.cc:609-666) and
+ * syr2k_vendor (cublas.cc:799-902). */
+int blb200_syr2k(const blb200_gemm_desc* desc, int32_t uplo, int32_t hermitian, void* workspace, size_t workspace_bytes,
+                 void* cuda_stream);
+
 /* ---- synthetic inputs ------------------------------------------------------------------
  * Counter-based generator: element `i` of tensor `tensor_id` under `seed` depends only on
  * (seed, tensor_id, first_index + i), so any shard on any GPU count reproduces the same data.

@@ -3,7 +3,7 @@ nothing in the product imports this module.
 
 Two independent statements of each operation:
 
-* ``*_blas``  — the BLAS routine itself (``?symm``, ``?hemm``, ``?trmm``, ``?syrk``, ``?herk`` from the
+* ``*_blas``  — the BLAS routine itself (``?symm``, ``?hemm``, ``?trmm``, ``?syrk``, ``?herk``, ``?syr2k``, ``?her2k`` from the
   OpenBLAS that SciPy ships), called once per batch item.  This is what the reference's host
   backend does: a serial loop of ``cblas_?symm`` / ``?hemm`` / ``?herk`` / ``?syrk`` / ``?trmm`` over the
   batch (BatchLAS src/backends/netlib_lapack.cc:333-760).
@@ -99,6 +99,27 @@ def syrk_exact(a, c, alpha, beta, uplo, op, hermitian=False):
     return exact, bound, mask
 
 
+def syr2k_exact(a, b, c, alpha, beta, uplo, op, hermitian=False):
+    """The `uplo` triangle of C <- alpha*op(A)*op(B)^T + alpha*op(B)*op(A)^T + beta*C (syr2k) or
+    alpha*op(A)*op(B)^H + conj(alpha)*op(B)*op(A)^H + beta*C (her2k: beta real, diagonal real)."""
+    la, lb = apply_op(a, op), apply_op(b, op)
+    t = 2 if hermitian else 1
+    p1, m1 = _mm_exact(la, apply_op(lb, t))
+    p2, m2 = _mm_exact(lb, apply_op(la, t))
+    alpha2 = np.conj(alpha) if hermitian else alpha
+    cw = _wide(c).copy()
+    n = c.shape[-1]
+    idx = np.arange(n)
+    if hermitian:
+        cw[..., idx, idx] = cw[..., idx, idx].real
+    full = alpha * p1 + alpha2 * p2 + (beta * cw if beta != 0 else 0)
+    if hermitian:
+        full[..., idx, idx] = full[..., idx, idx].real
+    bound = abs(alpha) * (m1 + m2) + (abs(beta) * np.abs(cw).real if beta != 0 else 0)
+    mask = np.tril(np.ones((n, n), bool)) if uplo == 1 else np.triu(np.ones((n, n), bool))
+    return np.where(mask, full, _wide(c)), bound, mask
+
+
 # ---- the BLAS routines themselves -----------------------------------------------------------------
 def _blas(name: str, dtype):
     import scipy.linalg.blas as sb
@@ -128,6 +149,15 @@ def syrk_blas(a, c, alpha, beta, uplo, op, hermitian=False):
     out = np.empty_like(c)
     for i in range(c.shape[0]):
         out[i] = f(alpha, np.asfortranarray(a[i]), beta=beta, c=np.asfortranarray(c[i]), trans=op, lower=uplo)
+    return out
+
+
+def syr2k_blas(a, b, c, alpha, beta, uplo, op, hermitian=False):
+    f = _blas("her2k" if hermitian else "syr2k", c.dtype)
+    out = np.empty_like(c)
+    for i in range(c.shape[0]):
+        out[i] = f(alpha, np.asfortranarray(a[i]), np.asfortranarray(b[i]), beta=beta, c=np.asfortranarray(c[i]),
+                   trans=op, lower=uplo)
     return out
 
 

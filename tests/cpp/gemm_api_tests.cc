@@ -374,6 +374,62 @@ void SyrkHerkMatchGemm(Queue& ctx) {
 }
 
 template <typename T>
+void Syr2kHer2kMatchTwoGemms(Queue& ctx) {  // her2k_tests.cc / syr2k_tests.cc: against gemm + gemm
+  using R = batchlas::float_t<T>;
+  const int n = 48, k = 20, batch = 3;
+  const double tol = tolerance<T>() * 24 * k;
+  constexpr bool cplx = !std::is_floating_point_v<T>;
+  for (bool herm : {false, true}) {
+    if (herm && !cplx) continue;
+    const Transpose other = herm ? Transpose::ConjTrans : Transpose::Trans;
+    for (auto trans : {Transpose::NoTrans, other})
+      for (auto uplo : {Uplo::Lower, Uplo::Upper}) {
+        const bool nt = trans == Transpose::NoTrans;
+        auto A = nt ? Matrix<T>::Random(n, k, false, batch) : Matrix<T>::Random(k, n, false, batch);
+        auto B = nt ? Matrix<T>::Random(n, k, false, batch, 43) : Matrix<T>::Random(k, n, false, batch, 43);
+        auto C = Matrix<T>::Random(n, n, false, batch, 44);
+        ctx.wait();
+        if constexpr (cplx) {
+          if (herm)
+            for (int b = 0; b < batch; ++b)
+              for (int d = 0; d < n; ++d) C(d, d, b) = T(C(d, d, b).real(), 0);
+        }
+        auto C0 = C.clone();
+        auto C_ref = C.clone();
+        T alpha = T(0.9), alpha2 = alpha;
+        if constexpr (cplx) {
+          alpha = T(0.9, -0.4);
+          alpha2 = herm ? std::conj(alpha) : alpha;
+        }
+        if constexpr (cplx) {
+          if (herm) her2k(ctx, A.view(), B.view(), C.view(), {.alpha = alpha, .beta = R(-0.35), .uplo = uplo, .trans = trans});
+          else syr2k(ctx, A.view(), B.view(), C.view(), {.alpha = alpha, .beta = T(-0.35), .uplo = uplo, .trans = trans});
+        } else {
+          syr2k(ctx, A.view(), B.view(), C.view(), {.alpha = alpha, .beta = T(-0.35), .uplo = uplo, .trans = trans});
+        }
+        const Transpose tb = nt ? other : Transpose::NoTrans;
+        gemm(ctx, A.view(), B.view(), C_ref.view(), {.alpha = alpha, .beta = T(-0.35), .transA = trans, .transB = tb});
+        gemm(ctx, B.view(), A.view(), C_ref.view(), {.alpha = alpha2, .beta = T(1), .transA = trans, .transB = tb});
+        ctx.wait();
+        for (int b = 0; b < batch; ++b)
+          for (int j = 0; j < n; ++j)
+            for (int i = 0; i < n; ++i) {
+              const bool referenced = uplo == Uplo::Lower ? i >= j : i <= j;
+              if (!referenced) {
+                CHECK(C(i, j, b) == C0(i, j, b));
+              } else if (herm && i == j) {
+                if constexpr (cplx) {
+                  CHECK(std::abs(C(i, j, b).real() - C_ref(i, j, b).real()) <= tol && C(i, j, b).imag() == R(0));
+                }
+              } else {
+                CHECK(std::abs(C(i, j, b) - C_ref(i, j, b)) <= tol);
+              }
+            }
+      }
+  }
+}
+
+template <typename T>
 void Level3ShapeErrors(Queue& ctx) {
   auto A = Matrix<T>::Zeros(8, 8, 2);
   auto R = Matrix<T>::Zeros(8, 4, 2);
@@ -450,6 +506,7 @@ int main(int argc, char** argv) {
   FOR_TYPES(SymmMatchesSymmetrizedGemm)
   FOR_TYPES(TrmmAllCombinations)
   FOR_TYPES(SyrkHerkMatchGemm)
+  FOR_TYPES(Syr2kHer2kMatchTwoGemms)
   FOR_TYPES(Level3ShapeErrors)
   run("OptionDefaultsAndErrors", [&] { OptionDefaultsAndErrors(ctx); });
   run("SlicedViews", [&] { SlicedViews(ctx); });

@@ -171,6 +171,46 @@ def test_syrk_herk(bl, dt, shape, aligned):
                         assert np.all(got[:, idx, idx].imag == 0), "herk left an imaginary part on the diagonal"
 
 
+@pytest.mark.parametrize("aligned", [False, True], ids=["oddld", "alignedld"])
+@pytest.mark.parametrize("dt", "sdcz")
+@pytest.mark.parametrize("shape", [(48, 20, 3), (65, 40, 2), (130, 70, 2), (5, 3, 4)], ids=str)
+def test_syr2k_her2k(bl, dt, shape, aligned):
+    dtype = NP_DT[dt]
+    n, k, batch = shape
+    rng = np.random.default_rng(400 + n)
+    idx = np.arange(n)
+    for herm in ([False, True] if dt in "cz" else [False]):
+        for op in ((0, 2) if herm else (0, 1)):
+            shp = (batch, n, k) if op == 0 else (batch, k, n)
+            a, b, c0 = rnd(rng, shp, dtype), rnd(rng, shp, dtype), rnd(rng, (batch, n, n), dtype)
+            dA, _ = to_dev(a, pad=apad(shp[1], aligned, 1))
+            dB, _ = to_dev(b, pad=apad(shp[1], aligned, 2))
+            for uplo in (0, 1):
+                for alpha, beta in [(0.9, -0.35), (1.5, 0.0)]:
+                    if dt in "cz":
+                        alpha = alpha - 0.4j
+                        if not herm:
+                            beta = beta * (1 + 0.5j)
+                    c_in = c0.copy()
+                    if beta == 0:
+                        mask_ref = np.tril(np.ones((n, n), bool)) if uplo == 1 else np.triu(np.ones((n, n), bool))
+                        c_in[:, mask_ref] = np.nan
+                    if herm:
+                        diag = c_in[:, idx, idx].copy()
+                        diag.imag = np.nan
+                        c_in[:, idx, idx] = diag
+                    dC, backC = to_dev(c_in, pad=apad(n, aligned, 3))
+                    bl.syr2k(dA, dB, dC, alpha, beta, uplo, op, hermitian=herm)
+                    got = from_dev(dC)
+                    exact, bound, mask = L.syr2k_exact(a, b, c_in, alpha, beta, uplo, op, herm)
+                    ok, worst = L.within(got, exact, bound, 2 * k, dtype, mask)
+                    assert ok, f"herm={herm} op={op} uplo={uplo} beta={beta} worst {worst:.3g}"
+                    assert np.ascontiguousarray(got[:, ~mask]).tobytes() == np.ascontiguousarray(c_in[:, ~mask]).tobytes()
+                    assert bool((backC[:, :, n:] == 7.0).all())
+                    if herm:
+                        assert np.all(got[:, idx, idx].imag == 0)
+
+
 def test_herk_triangles_agree_across_uplo(bl):
     """A*A^H is Hermitian: what Lower writes below the diagonal is the conjugate of what Upper writes
     above it (tests/herk_tests.cc:238-280)."""

@@ -72,6 +72,24 @@ def test_syrk_herk_restatement_matches_blas(dtype):
                         assert np.all(got[:, idx, idx].imag == 0) and np.all(exact[:, idx, idx].imag == 0)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_syr2k_her2k_restatement_matches_blas(dtype):
+    rng = np.random.default_rng(8)
+    n, k, batch = 48, 20, 3
+    cplx = np.issubdtype(dtype, np.complexfloating)
+    for herm in ([False, True] if cplx else [False]):
+        for op in ((0, 2) if herm else (0, 1)):
+            shape = (batch, n, k) if op == 0 else (batch, k, n)
+            a, b, c = rnd(rng, shape, dtype), rnd(rng, shape, dtype), rnd(rng, (batch, n, n), dtype)
+            for uplo in (0, 1):
+                alpha = dtype(0.9 - 0.4j) if cplx else dtype(0.9)
+                beta = -0.35 if herm else dtype(-0.35)
+                exact, bound, mask = L.syr2k_exact(a, b, c, alpha, beta, uplo, op, herm)
+                got = L.syr2k_blas(a, b, c, alpha, beta, uplo, op, herm)
+                ok, worst = L.within(got, exact, bound, 2 * k, dtype, mask)
+                assert ok, (herm, op, uplo, worst)
+
+
 def test_expansions():
     a = np.arange(1, 10, dtype=np.complex128).reshape(1, 3, 3) * (1 + 1j)
     full = L.expand_full(a, 1, hermitian=True)[0]
