@@ -40,6 +40,26 @@ class Lease(ctypes.Structure):
 
 
 # Every symbol include/blb200.h declares, with its signature.
+class GemvDesc(ctypes.Structure):
+    """Mirror of blb200_gemv_desc."""
+    _fields_ = [("a", ctypes.c_void_p), ("x", ctypes.c_void_p), ("y", ctypes.c_void_p),
+                ("m", ctypes.c_int32), ("n", ctypes.c_int32), ("batch", ctypes.c_int32),
+                ("lda", ctypes.c_int64), ("stride_a", ctypes.c_int64),
+                ("incx", ctypes.c_int64), ("stride_x", ctypes.c_int64),
+                ("incy", ctypes.c_int64), ("stride_y", ctypes.c_int64),
+                ("alpha", ctypes.c_double * 2), ("beta", ctypes.c_double * 2),
+                ("dtype", ctypes.c_int32), ("op_a", ctypes.c_int32)]
+
+
+class EwiseDesc(ctypes.Structure):
+    """Mirror of blb200_ewise_desc."""
+    _fields_ = [("a", ctypes.c_void_p), ("b", ctypes.c_void_p), ("c", ctypes.c_void_p),
+                ("rows", ctypes.c_int32), ("cols", ctypes.c_int32), ("batch", ctypes.c_int32),
+                ("lda", ctypes.c_int64), ("ldb", ctypes.c_int64), ("ldc", ctypes.c_int64),
+                ("stride_a", ctypes.c_int64), ("stride_b", ctypes.c_int64), ("stride_c", ctypes.c_int64),
+                ("dtype", ctypes.c_int32)]
+
+
 SIGNATURES = {
     "blb200_gemm_validate": (ctypes.c_int, [ctypes.POINTER(GemmDesc)]),
     "blb200_gemm_strided_batched": (ctypes.c_int, [ctypes.POINTER(GemmDesc), ctypes.c_void_p]),
@@ -60,6 +80,10 @@ SIGNATURES = {
                                    ctypes.c_size_t, ctypes.c_void_p]),
     "blb200_syr2k": (ctypes.c_int, [ctypes.POINTER(GemmDesc), ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p,
                                     ctypes.c_size_t, ctypes.c_void_p]),
+    "blb200_gemv_strided_batched": (ctypes.c_int, [ctypes.POINTER(GemvDesc), ctypes.c_void_p]),
+    "blb200_elementwise": (ctypes.c_int, [ctypes.POINTER(EwiseDesc), ctypes.c_int32, ctypes.c_void_p]),
+    "blb200_axpby": (ctypes.c_int, [ctypes.POINTER(EwiseDesc), ctypes.POINTER(ctypes.c_double),
+                                    ctypes.POINTER(ctypes.c_double), ctypes.c_void_p]),
     "blb200_gemm_strided_batched_host": (ctypes.c_int, [ctypes.POINTER(GemmDesc), ctypes.c_int, ctypes.c_int32]),
     "blb200_last_kernel_name": (ctypes.c_char_p, []),
     "blb200_launch_count": (ctypes.c_uint64, []),

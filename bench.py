@@ -597,6 +597,58 @@ def run_level3(args):
     print(json.dumps(out), flush=True)
 
 
+def run_aux(args):
+    """gemv and the elementwise helpers (the steps either side of gemm): achieved HBM GB/s against the
+    measured copy bandwidth.  Algorithmic bytes: gemv reads A once (m*n*sizeof(T); x and y are noise and
+    not counted); elementwise / axpby read two operands and write one (3*rows*cols*sizeof(T))."""
+    import torch
+
+    import batchlas_b200 as bl
+    torch.cuda.set_device(0)
+    peak, src = measured_peaks()
+    tdt = {"s": torch.float32, "d": torch.float64, "c": torch.complex64, "z": torch.complex128}
+    out = {"hbm_peak_gbs": peak, "peak_source": src, "gemv": [], "elementwise": []}
+    for dt, m, n, batch in [("s", 32, 32, 1_000_000), ("s", 64, 64, 200_000), ("d", 256, 256, 8192), ("d", 1024, 1024, 512),
+                            ("s", 8192, 8192, 8), ("d", 16384, 16384, 1), ("z", 128, 128, 8192)]:
+        t = tdt[dt]
+        A = bl.fill(torch.empty(batch, n, m, dtype=t, device="cuda"), 42, 0)
+        row = {"dtype": dt, "m": m, "n": n, "batch": batch, "ops": {}}
+        nbytes = A.numel() * A.element_size()
+        for op, name in ((0, "N"), (1, "T")):
+            X = bl.fill(torch.empty(batch, n if op == 0 else m, dtype=t, device="cuda"), 42, 1)
+            Y = bl.fill(torch.empty(batch, m if op == 0 else n, dtype=t, device="cuda"), 42, 2)
+            fn = lambda: bl.linalg.gemv(A, X, Y, 1.5, -0.5, op)
+            for _ in range(max(args.warmup, 3)):
+                fn()
+            torch.cuda.synchronize()
+            ms = time_launches(torch, fn, args.steps)
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            row["ops"][name] = {"ms": round(ms, 4), "hbm_gbs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak, 3)}
+        out["gemv"].append(row)
+        del A
+    for dt, rows, cols, batch, packed in [("s", 32, 32, 1_000_000, True), ("d", 1024, 1024, 128, True),
+                                          ("d", 1000, 1000, 128, False), ("s", 32, 32, 500_000, False)]:
+        t = tdt[dt]
+        ld = rows if packed else rows + 8
+        def mk(i):
+            back = bl.fill(torch.empty(batch, cols, ld, dtype=t, device="cuda"), 42, i)
+            return back[:, :, :rows]
+        A, B, C = mk(0), mk(1), mk(2)
+        nbytes = 3 * batch * rows * cols * A.element_size()
+        row = {"dtype": dt, "rows": rows, "cols": cols, "batch": batch, "packed": packed, "ops": {}}
+        for name, fn in (("add", lambda: bl.linalg.add_into(A, B, C)),
+                         ("axpby", lambda: bl.linalg.axpby_into(1.5, A, -0.5, B, C))):
+            for _ in range(max(args.warmup, 3)):
+                fn()
+            torch.cuda.synchronize()
+            ms = time_launches(torch, fn, args.steps)
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            row["ops"][name] = {"ms": round(ms, 4), "hbm_gbs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak, 3)}
+        out["elementwise"].append(row)
+        del A, B, C
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -609,6 +661,7 @@ def main():
     ap.add_argument("--case", default="", help="profiling mode: CONFIG[:OP], e.g. C2:NT or C3:TN (1 GPU)")
     ap.add_argument("--batch", type=int, default=0, help="batch override for --case")
     ap.add_argument("--kernel", default="auto", help="forced kernel for --case")
+    ap.add_argument("--aux", action="store_true", help="time gemv and the elementwise helpers against HBM bandwidth (1 GPU)")
     ap.add_argument("--level3", action="store_true", help="time symm/hemm/trmm/syrk/herk beside gemm (1 GPU)")
     ap.add_argument("--splitk", action="store_true", help="--case through blb200_gemm_splitk with planned scratch")
     args = ap.parse_args()
@@ -623,6 +676,9 @@ def main():
         return
     if args.level3:
         run_level3(args)
+        return
+    if args.aux:
+        run_aux(args)
         return
     if world != args.gpus and world == 1 and args.gpus > 1:
         raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")

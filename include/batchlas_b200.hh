@@ -830,6 +830,142 @@ inline Event trmm(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const
   return with_backend(ctx, [&](auto Bk) { return trmm<Bk.value, T>(ctx, A, B, C, o.alpha, o.side, o.uplo, o.trans, o.diag); });
 }
 
+// ---- the calls either side of gemm: gemv and the linalg:: elementwise layer -------------------------
+// VectorView: `batch` vectors of `size` elements, element i of item b at data[b*stride + i*inc]
+// (BatchLAS include/blas/matrix.hh:1320-1380; same constructor defaults: stride = size*inc).
+template <typename T>
+class VectorView {
+ public:
+  VectorView() = default;
+  VectorView(T* data, int size, int batch_size = 1, int inc = 1, int stride = 0)
+      : data_(data), size_(size), inc_(inc), stride_(stride > 0 ? stride : size * inc), batch_size_(batch_size) {}
+  T* data_ptr() const { return data_; }
+  int size() const { return size_; }
+  int inc() const { return inc_; }
+  int stride() const { return stride_; }
+  int batch_size() const { return batch_size_; }
+  T& at(int i, int b = 0) const { return data_[(int64_t)b * stride_ + (int64_t)i * inc_]; }
+
+ private:
+  T* data_ = nullptr;
+  int size_ = 0, inc_ = 1, stride_ = 0, batch_size_ = 1;
+};
+
+template <typename T>
+struct GemvOptions {
+  T alpha = T(1);
+  T beta = T(0);
+  Transpose transA = Transpose::NoTrans;
+};
+
+// gemv<Backend::CUDA, T> (replaces gemv_vendor, BatchLAS src/backends/cublas.cc:1092-1113).
+template <Backend Back, typename T>
+inline Event gemv(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const VectorView<T>& X, const VectorView<T>& Y,
+                  T alpha, T beta, Transpose transA) {
+  static_assert(Back == Backend::CUDA, "only the CUDA backend exists in this build");
+  blb200_gemv_desc d{};
+  d.a = A.data_ptr(); d.x = X.data_ptr(); d.y = Y.data_ptr();
+  d.m = A.rows(); d.n = A.cols(); d.batch = A.batch_size();
+  d.lda = A.ld(); d.stride_a = A.stride();
+  d.incx = X.inc(); d.stride_x = X.stride();
+  d.incy = Y.inc(); d.stride_y = Y.stride();
+  detail::set_scalar(d.alpha, alpha);
+  detail::set_scalar(d.beta, beta);
+  d.dtype = detail::dtype_code<T>();
+  d.op_a = (int)transA;
+  const int xl = transA == Transpose::NoTrans ? d.n : d.m, yl = transA == Transpose::NoTrans ? d.m : d.n;
+  if (X.size() != xl || Y.size() != yl || (d.batch > 1 && (X.batch_size() != d.batch || Y.batch_size() != d.batch)))
+    throw std::runtime_error("GEMV: incompatible dimensions");
+  ctx.make_current();
+  detail::status_check(blb200_gemv_strided_batched(&d, ctx.native_stream()));
+  return ctx.create_event_after_external_work();
+}
+template <typename T>
+inline Event gemv(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const VectorView<T>& X, const VectorView<T>& Y,
+                  const GemvOptions<std::type_identity_t<T>>& o = {}) {
+  return with_backend(ctx, [&](auto Bk) { return gemv<Bk.value, T>(ctx, A, X, Y, o.alpha, o.beta, o.transA); });
+}
+
+namespace linalg {
+enum class BinaryOp { Add, Subtract, Multiply, Divide };
+
+namespace detail_ew {
+template <typename T>
+inline blb200_ewise_desc desc(const char* where, const MatrixView<T, MatrixFormat::Dense>& A,
+                              const MatrixView<T, MatrixFormat::Dense>& B, const MatrixView<T, MatrixFormat::Dense>& C) {
+  auto same = [](const auto& X, const auto& Y) {
+    return X.rows() == Y.rows() && X.cols() == Y.cols() && X.batch_size() == Y.batch_size();
+  };
+  if (!same(A, B) || !same(A, C)) throw std::invalid_argument(std::string(where) + ": operands must have the same shape");
+  blb200_ewise_desc d{};
+  d.a = A.data_ptr(); d.b = B.data_ptr(); d.c = C.data_ptr();
+  d.rows = A.rows(); d.cols = A.cols(); d.batch = A.batch_size();
+  d.lda = A.ld(); d.ldb = B.ld(); d.ldc = C.ld();
+  d.stride_a = A.stride(); d.stride_b = B.stride(); d.stride_c = C.stride();
+  d.dtype = batchlas::detail::dtype_code<T>();
+  return d;
+}
+}  // namespace detail_ew
+
+// C = op(A, B) elementwise; C may alias A or B (src/extra/elementwise.cc:42-79).
+template <typename T, BinaryOp Op>
+inline Event elementwise_into(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A,
+                              const MatrixView<T, MatrixFormat::Dense>& B, const MatrixView<T, MatrixFormat::Dense>& C) {
+  blb200_ewise_desc d = detail_ew::desc<T>("linalg::elementwise_into", A, B, C);
+  ctx.make_current();
+  batchlas::detail::status_check(blb200_elementwise(&d, (int)Op, ctx.native_stream()));
+  return ctx.get_event();
+}
+// C = alpha*A + beta*B (src/extra/elementwise.cc:81-112).
+template <typename T>
+inline Event axpby_into(Queue& ctx, T alpha, const MatrixView<T, MatrixFormat::Dense>& A, T beta,
+                        const MatrixView<T, MatrixFormat::Dense>& B, const MatrixView<T, MatrixFormat::Dense>& C) {
+  blb200_ewise_desc d = detail_ew::desc<T>("linalg::axpby_into", A, B, C);
+  double al[2], be[2];
+  batchlas::detail::set_scalar(al, alpha);
+  batchlas::detail::set_scalar(be, beta);
+  ctx.make_current();
+  batchlas::detail::status_check(blb200_axpby(&d, al, be, ctx.native_stream()));
+  return ctx.get_event();
+}
+template <typename T>
+inline Event scale(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, T alpha) {
+  return axpby_into<T>(ctx, alpha, A, T(0), A, A);
+}
+template <typename T>
+inline Event add_into(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
+                      const MatrixView<T, MatrixFormat::Dense>& C) {
+  return elementwise_into<T, BinaryOp::Add>(ctx, A, B, C);
+}
+template <typename T>
+inline Event subtract_into(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A,
+                           const MatrixView<T, MatrixFormat::Dense>& B, const MatrixView<T, MatrixFormat::Dense>& C) {
+  return elementwise_into<T, BinaryOp::Subtract>(ctx, A, B, C);
+}
+template <typename T>
+inline Event multiply_into(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A,
+                           const MatrixView<T, MatrixFormat::Dense>& B, const MatrixView<T, MatrixFormat::Dense>& C) {
+  return elementwise_into<T, BinaryOp::Multiply>(ctx, A, B, C);
+}
+template <typename T>
+inline Event divide_into(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
+                         const MatrixView<T, MatrixFormat::Dense>& C) {
+  return elementwise_into<T, BinaryOp::Divide>(ctx, A, B, C);
+}
+// alpha * op(A) * op(B) as a new matrix; beta is forced to zero so the fresh storage is never read
+// (include/blas/linalg-ops.hh:168-184).
+template <typename T>
+inline Matrix<T> matmul(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
+                        const GemmOptions<std::type_identity_t<T>>& opts = {}) {
+  const bool ta = opts.transA != Transpose::NoTrans, tb = opts.transB != Transpose::NoTrans;
+  Matrix<T> C(ta ? A.cols() : A.rows(), tb ? B.rows() : B.cols(), A.batch_size());
+  auto o = opts;
+  o.beta = T(0);
+  gemm(ctx, A, B, C.view(), o);
+  return C;
+}
+}  // namespace linalg
+
 }  // namespace batchlas
 
 inline batchlas::WorkspaceLease Queue::workspace(size_t bytes) {

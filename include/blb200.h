@@ -240,6 +240,46 @@ int blb200_syrk(const blb200_gemm_desc* desc, int32_t uplo, int32_t hermitian, v
 int blb200_syr2k(const blb200_gemm_desc* desc, int32_t uplo, int32_t hermitian, void* workspace, size_t workspace_bytes,
                  void* cuda_stream);
 
+/* ---- the steps either side of gemm: gemv and elementwise helpers ---------------------------
+ * Strided-batched gemv:  y_b <- alpha * op_a(A_b) * x_b + beta * y_b.  A_b is the stored m x n
+ * column-major matrix; op N reads x of length n and writes y of length m, op T / H the other way
+ * round (H conjugates A; for real dtypes H = T).  Vector element i of item b is at
+ * base[b*stride + i*inc], inc >= 1 (BatchLAS VectorView, include/blas/matrix.hh:1320-1380).
+ * BLAS rules: an empty y is a no-op, an empty x scales y by beta, beta == 0 never reads y.
+ * Replaces gemv_vendor (cublasXgemv / cublasXgemvStridedBatched), src/backends/cublas.cc:1092-1113;
+ * public call include/blas/functions/gemv.hh:22-43. */
+typedef struct blb200_gemv_desc {
+  const void* a;
+  const void* x;
+  void* y;
+  int32_t m, n, batch;       /* stored shape of A, number of items */
+  int64_t lda, stride_a;     /* elements */
+  int64_t incx, stride_x;
+  int64_t incy, stride_y;
+  double alpha[2], beta[2];
+  int32_t dtype, op_a;       /* blb200_dtype, blb200_op */
+} blb200_gemv_desc;
+int blb200_gemv_strided_batched(const blb200_gemv_desc* desc, void* cuda_stream);
+
+/* Elementwise helpers on batched column-major views of one shape (rows x cols x batch), each with
+ * its own ld / stride; C may alias A or B (every element is read and written by one thread).
+ * blb200_elementwise: C <- A (op) B, op 0 add, 1 subtract, 2 multiply (Hadamard), 3 divide.
+ * blb200_axpby:       C <- alpha*A + beta*B (both products are always formed, as the reference does).
+ * Scaling in place is axpby with B = C = A and beta = 0.
+ * Replaces linalg::elementwise_into / axpby_into / scale, BatchLAS src/extra/elementwise.cc:42-112
+ * (declared include/blas/linalg-ops.hh:59-83). */
+typedef struct blb200_ewise_desc {
+  const void* a;
+  const void* b;
+  void* c;
+  int32_t rows, cols, batch;
+  int64_t lda, ldb, ldc;
+  int64_t stride_a, stride_b, stride_c;
+  int32_t dtype;
+} blb200_ewise_desc;
+int blb200_elementwise(const blb200_ewise_desc* desc, int32_t op, void* cuda_stream);
+int blb200_axpby(const blb200_ewise_desc* desc, const double alpha[2], const double beta[2], void* cuda_stream);
+
 /* ---- synthetic inputs ------------------------------------------------------------------
  * Counter-based generator: element `i` of tensor `tensor_id` under `seed` depends only on
  * (seed, tensor_id, first_index + i), so any shard on any GPU count reproduces the same data.

@@ -429,6 +429,82 @@ void Syr2kHer2kMatchTwoGemms(Queue& ctx) {  // her2k_tests.cc / syr2k_tests.cc: 
   }
 }
 
+// gemv on views (gemv_tests.cc:120-285: single / batched, N and T, alpha and beta) against the
+// triple loop of its fixture.
+template <typename T>
+void GemvMatrixView(Queue& ctx) {
+  const int rows = 10, cols = 10, batch = 3;
+  auto A = Matrix<T>::Random(rows, cols, false, batch);
+  auto X = Matrix<T>::Random(rows, 1, false, batch, 43);  // managed storage for the vectors
+  auto Y = Matrix<T>::Random(rows, 1, false, batch, 44);
+  ctx.wait();
+  for (auto trans : {Transpose::NoTrans, Transpose::Trans})
+    for (auto ab : {std::pair<double, double>{1.0, 0.0}, {2.5, 0.0}, {1.5, 0.8}}) {
+      const T alpha = T(ab.first), beta = T(ab.second);
+      auto Y0 = Y.clone();
+      ctx.wait();
+      VectorView<T> x(X.data_ptr(), rows, batch), y(Y.data_ptr(), rows, batch);
+      gemv(ctx, A.view(), x, y, {.alpha = alpha, .beta = beta, .transA = trans});
+      ctx.wait();
+      for (int b = 0; b < batch; ++b)
+        for (int i = 0; i < rows; ++i) {
+          using W = std::conditional_t<std::is_floating_point_v<T>, long double, std::complex<long double>>;
+          W s = 0;
+          for (int l = 0; l < cols; ++l) s += W(trans == Transpose::NoTrans ? A(i, l, b) : A(l, i, b)) * W(X(l, 0, b));
+          W ref = W(alpha) * s + W(beta) * W(Y0(i, 0, b));
+          CHECK(std::abs(W(Y(i, 0, b)) - ref) <= tolerance<T>() * 20);
+        }
+    }
+}
+
+// linalg layer (linalg_layer_tests.cc): *_into helpers, axpby, scale, matmul.
+template <typename T>
+void LinalgElementwiseLayer(Queue& ctx) {
+  const int rows = 7, cols = 5, batch = 3;
+  auto A = Matrix<T>::Random(rows, cols, false, batch);
+  auto B = Matrix<T>::Random(rows, cols, false, batch, 43);
+  auto C = Matrix<T>::Zeros(rows, cols, batch);
+  ctx.wait();
+  for (int b = 0; b < batch; ++b)
+    for (int j = 0; j < cols; ++j)
+      for (int i = 0; i < rows; ++i) B(i, j, b) += T(3);  // away from zero
+  const double tol = tolerance<T>() * 10;
+  auto check = [&](auto&& f) {
+    ctx.wait();
+    double w = 0;
+    for (int b = 0; b < batch; ++b)
+      for (int j = 0; j < cols; ++j)
+        for (int i = 0; i < rows; ++i) w = std::max(w, (double)std::abs(C(i, j, b) - f(A(i, j, b), B(i, j, b))));
+    return w <= tol;
+  };
+  linalg::add_into(ctx, A.view(), B.view(), C.view());
+  CHECK(check([](T a, T b) { return a + b; }));
+  linalg::subtract_into(ctx, A.view(), B.view(), C.view());
+  CHECK(check([](T a, T b) { return a - b; }));
+  linalg::multiply_into(ctx, A.view(), B.view(), C.view());
+  CHECK(check([](T a, T b) { return a * b; }));
+  linalg::divide_into(ctx, A.view(), B.view(), C.view());
+  CHECK(check([](T a, T b) { return a / b; }));
+  linalg::axpby_into(ctx, T(1.5), A.view(), T(-0.25), B.view(), C.view());
+  CHECK(check([](T a, T b) { return T(1.5) * a + T(-0.25) * b; }));
+  auto A0 = A.clone();
+  linalg::scale(ctx, A.view(), T(2));
+  ctx.wait();
+  for (int i = 0; i < rows; ++i) CHECK(std::abs(A(i, 1, 2) - T(2) * A0(i, 1, 2)) <= tol);
+  auto P = linalg::matmul(ctx, A0.view(), B.view(), {.transB = Transpose::Trans});
+  auto P_ref = Matrix<T>::Zeros(rows, rows, batch);
+  gemm(ctx, A0.view(), B.view(), P_ref.view(), {.transB = Transpose::Trans});
+  ctx.wait();
+  CHECK(P.rows() == rows && P.cols() == rows && max_diff(P, P_ref, rows, rows, batch) == 0.0);
+  bool threw = false;
+  try {
+    linalg::add_into(ctx, A.view(), P.view(), C.view());
+  } catch (const std::invalid_argument& e) {
+    threw = std::strstr(e.what(), "linalg::elementwise_into: operands must have the same shape") != nullptr;
+  }
+  CHECK(threw);
+}
+
 template <typename T>
 void Level3ShapeErrors(Queue& ctx) {
   auto A = Matrix<T>::Zeros(8, 8, 2);
@@ -508,6 +584,8 @@ int main(int argc, char** argv) {
   FOR_TYPES(SyrkHerkMatchGemm)
   FOR_TYPES(Syr2kHer2kMatchTwoGemms)
   FOR_TYPES(Level3ShapeErrors)
+  FOR_TYPES(GemvMatrixView)
+  FOR_TYPES(LinalgElementwiseLayer)
   run("OptionDefaultsAndErrors", [&] { OptionDefaultsAndErrors(ctx); });
   run("SlicedViews", [&] { SlicedViews(ctx); });
   run("WorkspaceLeases", [&] { WorkspaceLeases(ctx); });
