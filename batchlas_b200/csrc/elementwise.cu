@@ -98,16 +98,25 @@ __global__ void __launch_bounds__(256) ewise_strided_kernel(EwiseParams p, T alp
     const T* a = (const T*)p.a + item * p.sa;
     const T* b = (const T*)p.b + item * p.sb;
     T* c = (T*)p.c + item * p.sc;
-    if (p.rows >= 128) {
-      for (int j = c0; j < c1; ++j)
-        for (int i = threadIdx.x; i < p.rows; i += blockDim.x)
-          c[(long long)j * p.ldc + i] = apply<T, OP>(a[(long long)j * p.lda + i], b[(long long)j * p.ldb + i], alpha, beta);
-    } else {  // short columns: spread the threads over (row, column) pairs of the block
-      const int n = (c1 - c0) * p.rows;
-      for (int f = threadIdx.x; f < n; f += blockDim.x) {
-        const int j = c0 + f / p.rows, i = f % p.rows;
-        c[(long long)j * p.ldc + i] = apply<T, OP>(a[(long long)j * p.lda + i], b[(long long)j * p.ldb + i], alpha, beta);
+    // (row, column) pairs of the block flattened, four independent triples in flight per thread
+    const int n = (c1 - c0) * p.rows;
+    for (int base = threadIdx.x; base < n; base += 4 * (int)blockDim.x) {
+      T av[4], bv[4];
+      long long oc[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int f = base + u * (int)blockDim.x;
+        oc[u] = -1;
+        if (f < n) {
+          const int jj = f / p.rows, i = f - jj * p.rows, j = c0 + jj;
+          av[u] = a[(long long)j * p.lda + i];
+          bv[u] = b[(long long)j * p.ldb + i];
+          oc[u] = (long long)j * p.ldc + i;
+        }
       }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (oc[u] >= 0) c[oc[u]] = apply<T, OP>(av[u], bv[u], alpha, beta);
     }
   }
 }

@@ -5,22 +5,31 @@
 //   * A warp always reads A along its columns (consecutive rows = consecutive addresses), 32 lanes
 //     = one 128..512-byte run per request, several independent requests in flight per lane.
 //   * op N  (y = A x):   a lane owns RV rows (i = lane + 32 r) of a row tile and walks the columns,
-//     eight at a time; x[j] is a uniform (broadcast) load.
-//   * op T/H (y = A^T x): a warp owns CT = 8 columns and walks the rows in chunks of 32; each lane
-//     keeps 8 partial sums that are folded across the warp once at the end.
+//     128 bytes of A per lane in flight at a time; x comes in 32 values per coalesced request and is
+//     handed round the warp by shuffle.
+//   * op T/H (y = A^T x): a warp owns a group of columns (8, or up to 32 for short columns) and
+//     walks the rows in chunks of 32; each lane keeps one partial sum per column, folded across the
+//     warp once at the end with a halving butterfly.  Units start at staggered rows.
 //   * A unit of work is (item, row tile) or (item, column group).  When units are plentiful (large
 //     batch of small matrices) every warp takes whole units, eight independent warps per CTA and a
 //     grid-stride loop, so tiny matrices do not pay a CTA launch each.  When they are few (one big
 //     matrix) the eight warps of a CTA split the reduction dimension of one unit and combine their
 //     partial sums through shared memory, which keeps enough bytes in flight to fill HBM.
-// Everything is predicated: any m, n, lda, inc, alignment.
+// Everything is predicated: any m, n, lda, inc, alignment.  Large batches of small packed matrices
+// take the TMA-ring kernel of gemv_ring.cu instead.
 #include "common.cuh"
 
 namespace blb200 {
+// The TMA-ring kernel for large batches of small packed matrices (gemv_ring.cu).
+bool gemv_ring_supported(int dtype, const void* a, const void* x, const void* y, int m, int n, int batch, long long lda,
+                         long long sa, long long incx, long long sx, long long incy, long long sy, bool trans,
+                         bool beta_zero);
+int launch_gemv_ring(int dtype, const void* a, const void* x, void* y, int m, int n, int batch, long long sa, long long sx,
+                     long long sy, const double* alpha, const double* beta, bool trans, bool conj, cudaStream_t stream);
+
 namespace {
 
 constexpr int kWarps = 8, kThreads = kWarps * 32;
-constexpr int kColsPerStep = 8;  // op T: columns per unit
 
 struct GemvParams {
   const void* a;
@@ -51,9 +60,15 @@ __device__ __forceinline__ T add(T a, T b) {
 }
 
 template <typename T>
-__device__ __forceinline__ T shfl_down(T v, int d) {
-  if constexpr (Scalar<T>::is_complex) return T{__shfl_down_sync(0xffffffffu, v.x, d), __shfl_down_sync(0xffffffffu, v.y, d)};
-  else return __shfl_down_sync(0xffffffffu, v, d);
+__device__ __forceinline__ T shfl_xor(T v, int d) {
+  if constexpr (Scalar<T>::is_complex) return T{__shfl_xor_sync(0xffffffffu, v.x, d), __shfl_xor_sync(0xffffffffu, v.y, d)};
+  else return __shfl_xor_sync(0xffffffffu, v, d);
+}
+
+template <typename T>
+__device__ __forceinline__ T shfl_idx(T v, int src) {
+  if constexpr (Scalar<T>::is_complex) return T{__shfl_sync(0xffffffffu, v.x, src), __shfl_sync(0xffffffffu, v.y, src)};
+  else return __shfl_sync(0xffffffffu, v, src);
 }
 
 template <typename T>
@@ -64,8 +79,8 @@ __device__ __forceinline__ void store_y(T* y, T alpha, T sum, T beta, bool beta_
 // ---- op N ------------------------------------------------------------------------------------------
 template <typename T, int RV>
 __global__ void __launch_bounds__(kThreads) gemv_n_kernel(GemvParams p) {
-  // columns per unrolled step: RV * CS independent loads per lane, 128 bytes of registers at most
-  constexpr int CS = sizeof(T) >= 16 ? 2 : (sizeof(T) == 8 ? 4 : 8);
+  // columns per unrolled step: RV * CS independent loads per lane = 128 bytes of registers
+  constexpr int CS = 128 / (RV * (int)sizeof(T));
   __shared__ T part[kWarps][32 * RV];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int per_cta = kWarps / p.ksplit;  // units a CTA works on at a time
@@ -77,9 +92,9 @@ __global__ void __launch_bounds__(kThreads) gemv_n_kernel(GemvParams p) {
   for (long long grp = blockIdx.x; grp < groups; grp += gridDim.x) {
     const long long unit = grp * per_cta + slot;
     const bool live = unit < p.units;
-    T acc[RV];
+    T acc[RV], prior[RV];
 #pragma unroll
-    for (int r = 0; r < RV; ++r) acc[r] = Scalar<T>::zero();
+    for (int r = 0; r < RV; ++r) acc[r] = prior[r] = Scalar<T>::zero();
     long long item = 0;
     int row0 = 0;
     if (live) {
@@ -93,28 +108,34 @@ __global__ void __launch_bounds__(kThreads) gemv_n_kernel(GemvParams p) {
       bool in[RV];
 #pragma unroll
       for (int r = 0; r < RV; ++r) in[r] = row0 + lane + 32 * r < p.m;
-      const T* col = A + (long long)j_begin * p.lda + row0 + lane;
-      int j = j_begin;
-      for (; j + CS <= j_end; j += CS) {
-        T av[CS][RV], xv[CS];
-#pragma unroll
-        for (int c = 0; c < CS; ++c) {
-          xv[c] = x[(long long)(j + c) * p.incx];
-#pragma unroll
-          for (int r = 0; r < RV; ++r) av[c][r] = in[r] ? col[(long long)c * p.lda + 32 * r] : Scalar<T>::zero();
-        }
-#pragma unroll
-        for (int c = 0; c < CS; ++c)
-#pragma unroll
-          for (int r = 0; r < RV; ++r) Scalar<T>::fma(acc[r], av[c][r], xv[c]);
-        col += (long long)CS * p.lda;
-      }
-      for (; j < j_end; ++j) {
-        const T xv = x[(long long)j * p.incx];
+      if (p.ksplit == 1 && !beta_zero) {  // ask for y now, so that its latency hides behind the walk over A
 #pragma unroll
         for (int r = 0; r < RV; ++r)
-          if (in[r]) Scalar<T>::fma(acc[r], col[32 * r], xv);
-        col += p.lda;
+          if (in[r]) prior[r] = ((const T*)p.y)[item * p.sy + (long long)(row0 + lane + 32 * r) * p.incy];
+      }
+      // Columns in blocks of 32: lane l fetches x[jb + l] once (one coalesced request) and the block's
+      // values are handed round by shuffle, CS columns of A in flight at a time.
+      for (int jb = j_begin; jb < j_end; jb += 32) {
+        const T xl = jb + lane < j_end ? x[(long long)(jb + lane) * p.incx] : Scalar<T>::zero();
+        const T* col = A + (long long)jb * p.lda + row0 + lane;
+        const int nb = min(32, j_end - jb);
+#pragma unroll
+        for (int c0 = 0; c0 < 32; c0 += CS) {
+          if (c0 < nb) {  // warp-uniform
+            T av[CS][RV];
+#pragma unroll
+            for (int c = 0; c < CS; ++c)
+#pragma unroll
+              for (int r = 0; r < RV; ++r)
+                av[c][r] = (in[r] && c0 + c < nb) ? col[(long long)(c0 + c) * p.lda + 32 * r] : Scalar<T>::zero();
+#pragma unroll
+            for (int c = 0; c < CS; ++c) {
+              const T xv = shfl_idx(xl, c0 + c);
+#pragma unroll
+              for (int r = 0; r < RV; ++r) Scalar<T>::fma(acc[r], av[c][r], xv);
+            }
+          }
+        }
       }
     }
     if (p.ksplit > 1) {  // the CTA works on one unit: fold the eight column shares
@@ -135,16 +156,40 @@ __global__ void __launch_bounds__(kThreads) gemv_n_kernel(GemvParams p) {
 #pragma unroll
       for (int r = 0; r < RV; ++r) {
         const int row = row0 + lane + 32 * r;
-        if (row < p.m) store_y<T>((T*)p.y + item * p.sy + (long long)row * p.incy, alpha, acc[r], beta, beta_zero);
+        if (row < p.m) ((T*)p.y)[item * p.sy + (long long)row * p.incy] = epilogue<T>(alpha, acc[r], beta, beta_zero, &prior[r]);
       }
     }
   }
 }
 
 // ---- op T / H --------------------------------------------------------------------------------------
-template <typename T>
+// Folds N per-lane partial sums (one per column) across the 32 lanes with N-1 + (5 - log2 N) shuffles
+// instead of 5 N: while more than one column is left, a lane keeps one half of the columns and hands
+// the other half to its partner.  Afterwards v[0] of lane L is the total of column (L >> (5 - log2 N)).
+template <typename T, int N>
+__device__ __forceinline__ void fold_columns(T (&v)[N], int lane) {
+#pragma unroll
+  for (int step = 0; step < 5; ++step) {
+    const int off = 16 >> step;
+    const int h = N >> (step + 1);  // columns kept per lane after this step
+    if (h >= 1) {
+      const bool upper = (lane & off) != 0;
+#pragma unroll
+      for (int k = 0; k < h; ++k) {
+        const T send = upper ? v[k] : v[k + h];
+        const T keep = upper ? v[k + h] : v[k];
+        v[k] = add(keep, shfl_xor(send, off));
+      }
+    } else {
+      v[0] = add(v[0], shfl_xor(v[0], off));
+    }
+  }
+}
+
+// CT columns per unit, RC row chunks of 32 per unrolled step (CT * RC loads in flight per lane).
+template <typename T, int CT, int RC>
 __global__ void __launch_bounds__(kThreads) gemv_t_kernel(GemvParams p) {
-  constexpr int CT = kColsPerStep;
+  constexpr int LOG_CT = CT == 32 ? 5 : (CT == 16 ? 4 : (CT == 8 ? 3 : (CT == 4 ? 2 : 1)));
   __shared__ T part[kWarps][CT];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int per_cta = kWarps / p.ksplit;
@@ -153,6 +198,8 @@ __global__ void __launch_bounds__(kThreads) gemv_t_kernel(GemvParams p) {
   const T alpha = Scalar<T>::make(p.alpha[0], p.alpha[1]), beta = Scalar<T>::make(p.beta[0], p.beta[1]);
   const bool beta_zero = p.beta[0] == 0.0 && p.beta[1] == 0.0;
   const bool conj = p.conj_a != 0;
+  const int my_col = lane >> (5 - LOG_CT);                       // column this lane ends up holding
+  const bool writer = (lane & ((1 << (5 - LOG_CT)) - 1)) == 0;
 
   for (long long grp = blockIdx.x; grp < groups; grp += gridDim.x) {
     const long long unit = grp * per_cta + slot;
@@ -160,11 +207,14 @@ __global__ void __launch_bounds__(kThreads) gemv_t_kernel(GemvParams p) {
     T acc[CT];
 #pragma unroll
     for (int c = 0; c < CT; ++c) acc[c] = Scalar<T>::zero();
+    T prior = Scalar<T>::zero();
     long long item = 0;
     int col0 = 0;
     if (live) {
       item = unit / p.tiles;
       col0 = (int)(unit - item * p.tiles) * CT;
+      if (p.ksplit == 1 && !beta_zero && writer && col0 + my_col < p.n)  // asked for now, needed after the walk
+        prior = ((const T*)p.y)[item * p.sy + (long long)(col0 + my_col) * p.incy];
       const T* A = (const T*)p.a + item * p.sa + (long long)col0 * p.lda;
       const T* x = (const T*)p.x + item * p.sx;
       const int ncol = min(CT, p.n - col0);
@@ -172,25 +222,27 @@ __global__ void __launch_bounds__(kThreads) gemv_t_kernel(GemvParams p) {
       const int chunks = (p.m + 31) / 32, share = (chunks + p.ksplit - 1) / p.ksplit;
       const int i_begin = kpart * share * 32, i_end = min(p.m, i_begin + share * 32);
       if (ncol == CT) {
-        int i = i_begin + lane;
-        for (; sizeof(T) <= 8 && i + 32 < i_end; i += 64) {  // two row chunks per step: 16 loads in flight per lane
-          T a0[CT], a1[CT];
-          const T x0 = x[(long long)i * p.incx], x1 = x[(long long)(i + 32) * p.incx];
+        // Units start at different rows and wrap round, so that warps walking columns whose starts
+        // are a power of two apart do not all ask the same memory channels at the same time.
+        const int steps = (i_end - i_begin + 32 * RC - 1) / (32 * RC);
+        const int first = steps > 1 ? (int)((((unsigned long long)unit * 2654435761ull) >> 12) % (unsigned)steps) : 0;
+        for (int sidx = 0; sidx < steps; ++sidx) {
+          int st = first + sidx;
+          if (st >= steps) st -= steps;
+          const int i0 = i_begin + st * (32 * RC) + lane;
+          T av[RC][CT], xv[RC];
 #pragma unroll
-          for (int c = 0; c < CT; ++c) {
-            a0[c] = ld_conj(A + (long long)c * p.lda + i, conj);
-            a1[c] = ld_conj(A + (long long)c * p.lda + i + 32, conj);
+          for (int r = 0; r < RC; ++r) {
+            const int i = i0 + 32 * r;
+            const bool in = i < i_end;
+            xv[r] = in ? x[(long long)i * p.incx] : Scalar<T>::zero();
+#pragma unroll
+            for (int c = 0; c < CT; ++c) av[r][c] = in ? ld_conj(A + (long long)c * p.lda + i, conj) : Scalar<T>::zero();
           }
 #pragma unroll
-          for (int c = 0; c < CT; ++c) {
-            Scalar<T>::fma(acc[c], a0[c], x0);
-            Scalar<T>::fma(acc[c], a1[c], x1);
-          }
-        }
-        for (; i < i_end; i += 32) {
-          const T xv = x[(long long)i * p.incx];
+          for (int r = 0; r < RC; ++r)
 #pragma unroll
-          for (int c = 0; c < CT; ++c) Scalar<T>::fma(acc[c], ld_conj(A + (long long)c * p.lda + i, conj), xv);
+            for (int c = 0; c < CT; ++c) Scalar<T>::fma(acc[c], av[r][c], xv[r]);
         }
       } else {
         for (int i = i_begin + lane; i < i_end; i += 32) {
@@ -201,16 +253,9 @@ __global__ void __launch_bounds__(kThreads) gemv_t_kernel(GemvParams p) {
         }
       }
     }
-    // fold the 32 lanes: after the loop lane 0 holds the column sums
-#pragma unroll
-    for (int c = 0; c < CT; ++c)
-#pragma unroll
-      for (int d = 16; d > 0; d >>= 1) acc[c] = add(acc[c], shfl_down(acc[c], d));
+    fold_columns<T, CT>(acc, lane);  // lane L now holds the sum of column L >> (5 - log2 CT) in acc[0]
     if (p.ksplit > 1) {
-      if (lane == 0) {
-#pragma unroll
-        for (int c = 0; c < CT; ++c) part[warp][c] = acc[c];
-      }
+      if (writer) part[warp][my_col] = acc[0];
       __syncthreads();
       if (live && threadIdx.x < CT && col0 + (int)threadIdx.x < p.n) {
         T s = part[0][threadIdx.x];
@@ -219,10 +264,8 @@ __global__ void __launch_bounds__(kThreads) gemv_t_kernel(GemvParams p) {
         store_y<T>((T*)p.y + item * p.sy + (long long)(col0 + threadIdx.x) * p.incy, alpha, s, beta, beta_zero);
       }
       __syncthreads();
-    } else if (live && lane == 0) {
-#pragma unroll
-      for (int c = 0; c < CT; ++c)
-        if (col0 + c < p.n) store_y<T>((T*)p.y + item * p.sy + (long long)(col0 + c) * p.incy, alpha, acc[c], beta, beta_zero);
+    } else if (live && writer && col0 + my_col < p.n) {
+      ((T*)p.y)[item * p.sy + (long long)(col0 + my_col) * p.incy] = epilogue<T>(alpha, acc[0], beta, beta_zero, &prior);
     }
   }
 }
@@ -272,7 +315,14 @@ int launch_typed(GemvParams p, bool trans, cudaStream_t stream) {
     kern<<<(unsigned)(groups < fit ? groups : fit), kThreads, 0, stream>>>(p);
   };
   if (trans) {
-    go(gemv_t_kernel<T>, plan((p.n + kColsPerStep - 1) / kColsPerStep));
+    // Short columns: as many columns per warp as 128 bytes of registers hold, one row chunk per step.
+    // Long columns: 8 (4 for 16-byte elements) columns, several row chunks per step.
+    constexpr int WIDE = 128 / (int)sizeof(T) > 32 ? 32 : 128 / (int)sizeof(T);   // 32, 16, 16, 8
+    constexpr int NARROW = sizeof(T) >= 16 ? 4 : 8;
+    constexpr int RC = 128 / (NARROW * (int)sizeof(T)) > 4 ? 4 : 128 / (NARROW * (int)sizeof(T));  // 4, 2, 2, 2
+    const bool wide = p.m <= 64 && p.n >= WIDE && (long long)((p.n + WIDE - 1) / WIDE) * p.batch * kWarps >= enough;
+    if (wide) go(gemv_t_kernel<T, WIDE, 1>, plan((p.n + WIDE - 1) / WIDE));
+    else go(gemv_t_kernel<T, NARROW, RC>, plan((p.n + NARROW - 1) / NARROW));
   } else {
     // rows per lane: as many as the matrix offers, fewer when that leaves too few units in flight
     int rv = p.m > 64 ? 4 : (p.m > 32 ? 2 : 1);
@@ -310,6 +360,13 @@ extern "C" int blb200_gemv_strided_batched(const blb200_gemv_desc* d, void* cuda
   p.conj_a = cplx && d->op_a == BLB200_H;
   cudaStream_t stream = (cudaStream_t)cuda_stream;
   int rc;
+  if (red_len > 0 && gemv_ring_supported(d->dtype, d->a, d->x, d->y, d->m, d->n, d->batch, d->lda, d->stride_a, d->incx,
+                                         d->stride_x, d->incy, d->stride_y, trans, p.beta[0] == 0.0 && p.beta[1] == 0.0)) {
+    rc = launch_gemv_ring(d->dtype, d->a, d->x, d->y, d->m, d->n, d->batch, d->stride_a, d->stride_x, d->stride_y, p.alpha,
+                          p.beta, trans, p.conj_a != 0, stream);
+    if (rc == BLB200_OK) note_launch("gemv_ring");
+    if (rc != BLB200_E_UNSUPPORTED) return rc;
+  }
   switch (d->dtype) {
     case BLB200_S: rc = launch_typed<float>(p, trans, stream); break;
     case BLB200_D: rc = launch_typed<double>(p, trans, stream); break;

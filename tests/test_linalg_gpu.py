@@ -101,6 +101,39 @@ def test_gemv_large_batch_of_small_matrices(bl):
         assert ok, worst
 
 
+@pytest.mark.parametrize("dt", "sdcz")
+@pytest.mark.parametrize("shape", [(32, 32), (64, 64), (24, 40), (128, 8), (8, 128), (20, 20), (100, 12)], ids=str)
+def test_gemv_ring_kernel(bl, dt, shape):
+    """Large batches of small packed matrices go through the TMA ring; every dtype, both operand
+    transforms, ragged shapes whose item size is still a multiple of 16 bytes."""
+    dtype = NP_DT[dt]
+    m, n = shape
+    if m * n * np.dtype(dtype).itemsize > 16384:
+        pytest.skip("item larger than a ring slot")
+    batch = 1500 if m * n >= 1024 else 2500
+    rng = np.random.default_rng(700 + m * n)
+    a = rnd(rng, (batch, m, n), dtype)
+    dA, _ = mat_to_dev(a)
+    for op in (0, 1, 2):
+        xl, yl = (n, m) if op == 0 else (m, n)
+        x, y0 = rnd(rng, (batch, xl), dtype), rnd(rng, (batch, yl), dtype)
+        for alpha, beta in [(1.5, -0.5), (2.0, 0.0)]:
+            if dt in "cz":
+                alpha = alpha + 0.5j
+            y_in = y0.copy()
+            if beta == 0:
+                y_in[:] = np.nan
+            dX, _ = vec_to_dev(x)
+            dY, backY = vec_to_dev(y_in, gap=4)  # items stay 16-byte aligned
+            bl.linalg.gemv(dA, dX, dY, alpha, beta, op)
+            assert bl.last_kernel_name() == "gemv_ring"
+            exact, bound = LA.gemv_exact(a, x, y_in, alpha, beta, op)
+            ok, worst = LA.gemv_within(dY.cpu().numpy(), exact, bound, xl, dtype)
+            assert ok, f"op={op} beta={beta} worst {worst:.3g}"
+            assert bool((backY[:, yl:] == 7.0).all())
+    assert bl.device_status() == 0
+
+
 def test_gemv_empty_and_errors(bl, lib):
     y = torch.full((2, 5), 3.0, device="cuda", dtype=torch.float64)
     a = torch.zeros((2, 0, 5), device="cuda", dtype=torch.float64)  # 5 x 0: empty x scales y by beta
