@@ -31,7 +31,22 @@ struct GemmParams {
   //     kernel handed out_tri must honour it.  out_herm: C is Hermitian — the imaginary part of its
   //     diagonal is neither read nor left non-zero.
   int tri_a = 0, tri_b = 0, out_tri = 0, out_herm = 0;
+  // Heterogeneous batch: optional device-readable per-item dims (null = every item uses m / n / k,
+  // which are then the capacities the tile grid is laid over).  Read by the same instantiations of
+  // the tile kernels that read the structure hints.
+  const int* het_m = nullptr;
+  const int* het_n = nullptr;
+  const int* het_k = nullptr;
 };
+__host__ __device__ inline bool has_hints(const GemmParams& p) {
+  return (p.tri_a | p.tri_b | p.out_tri) != 0 || p.het_m || p.het_n || p.het_k;
+}
+// Per-item dims of a heterogeneous batch, clamped to [0, capacity].
+__device__ __forceinline__ int item_dim(const int* dims, long long item, int cap) {
+  if (!dims) return cap;
+  const int v = dims[item];
+  return v < 0 ? 0 : (v < cap ? v : cap);
+}
 
 struct StructureHints {
   int tri_a, tri_b, out_tri, out_herm;
@@ -198,6 +213,7 @@ bool small64_supported(const GemmParams& p, int dtype);
 bool tiled_supported(const GemmParams& p, int dtype);
 bool dmma_supported(const GemmParams& p, int dtype);
 bool sgemm128_supported(const GemmParams& p, int dtype);
+bool sgemm128_preferred(const GemmParams& p);  // against the tiled kernel, by padded work
 
 // Device properties cached per device.
 struct DeviceInfo {

@@ -167,6 +167,17 @@ GemmParams to_params_public(const blb200_gemm_desc* d) { return to_params(d); }
 
 static int dispatch_untraced(const blb200_gemm_desc* d, const StructureHints* hints, cudaStream_t stream);
 
+// The cp.async tile kernels in order of preference for this problem; the generic kernel (or
+// BLB200_E_UNSUPPORTED) when none of them takes it.
+static int launch_tile_kernel(const GemmParams& p, int dtype, cudaStream_t stream, bool generic_fallback = true) {
+  // double, one tile or less: the 64 x 64 DFMA tile beats a mostly empty 128 x 64 DMMA tile
+  const bool small_d = dtype == BLB200_D && p.m <= 64 && p.n <= 64 && tiled_supported(p, dtype);
+  if (!small_d && dmma_supported(p, dtype)) return launch_dmma(p, dtype, stream);
+  if (sgemm128_supported(p, dtype) && sgemm128_preferred(p)) return launch_sgemm128(p, dtype, stream);
+  if (tiled_supported(p, dtype)) return launch_tiled(p, dtype, stream);
+  return generic_fallback ? launch_generic(p, dtype, stream) : BLB200_E_UNSUPPORTED;
+}
+
 int dispatch(const blb200_gemm_desc* d, cudaStream_t stream) { return dispatch_structured(d, nullptr, stream); }
 
 int dispatch_structured(const blb200_gemm_desc* d, const StructureHints* hints, cudaStream_t stream) {
@@ -201,10 +212,8 @@ static int dispatch_untraced(const blb200_gemm_desc* d, const StructureHints* hi
     hp.tri_b = hints->tri_b;
     hp.out_tri = hints->out_tri;
     hp.out_herm = hints->out_herm;
-    if (dmma_supported(hp, d->dtype)) return launch_dmma(hp, d->dtype, stream);
-    if (sgemm128_supported(hp, d->dtype)) return launch_sgemm128(hp, d->dtype, stream);
-    if (tiled_supported(hp, d->dtype)) return launch_tiled(hp, d->dtype, stream);
-    if (hints->out_tri) return BLB200_E_UNSUPPORTED;
+    const int rc_tile = launch_tile_kernel(hp, d->dtype, stream, /*generic_fallback=*/false);
+    if (rc_tile != BLB200_E_UNSUPPORTED || hints->out_tri) return rc_tile;
   }
   const GemmParams p = to_params(d);
   if (d->kernel_hint == BLB200_K_AUTO && env_forced_kernel() != BLB200_K_AUTO) {
@@ -230,10 +239,7 @@ static int dispatch_untraced(const blb200_gemm_desc* d, const StructureHints* hi
   }
   if (small32_supported(p, d->dtype)) return launch_small32(p, d->dtype, stream);
   if (small64_supported(p, d->dtype)) return launch_small64(p, d->dtype, stream);
-  if (dmma_supported(p, d->dtype)) return launch_dmma(p, d->dtype, stream);
-  if (sgemm128_supported(p, d->dtype)) return launch_sgemm128(p, d->dtype, stream);
-  if (tiled_supported(p, d->dtype)) return launch_tiled(p, d->dtype, stream);
-  return launch_generic(p, d->dtype, stream);
+  return launch_tile_kernel(p, d->dtype, stream);
 }
 
 int dispatch_hetero(const blb200_gemm_desc* d, const int32_t* m_items, const int32_t* n_items,
@@ -242,7 +248,17 @@ int dispatch_hetero(const blb200_gemm_desc* d, const int32_t* m_items, const int
   int rc = validate(d);
   if (rc != BLB200_OK) return rc;
   if (d->m == 0 || d->n == 0 || d->batch == 0) return BLB200_OK;
-  const GemmParams p = to_params(d);
+  GemmParams p = to_params(d);
+  // The tile kernels take per-item dims when the capacity problem meets their preconditions (16-byte
+  // aligned operands, more than 32 x 32); everything else goes to the generic kernel.
+  if (d->kernel_hint == BLB200_K_AUTO && env_forced_kernel() == BLB200_K_AUTO) {
+    GemmParams hp = p;
+    hp.het_m = m_items;
+    hp.het_n = n_items;
+    hp.het_k = k_items;
+    const int rc_tile = launch_tile_kernel(hp, d->dtype, stream, /*generic_fallback=*/false);
+    if (rc_tile != BLB200_E_UNSUPPORTED) return rc_tile;
+  }
   HeteroDims het{m_items, n_items, k_items, d->m, d->n, d->k};
   return launch_generic_hetero(p, het, d->dtype, stream);
 }

@@ -104,7 +104,11 @@ __global__ void __launch_bounds__(256, 2) gemm_dmma_d_kernel(GemmParams p, int t
   const unsigned char* A = (const unsigned char*)p.a + (item * p.sa + sv.a_off) * 8;
   const unsigned char* B = (const unsigned char*)p.b + (item * p.sb + sv.b_off) * 8;
   double* C = (double*)p.c + vitem * p.sc;
-  if constexpr (HINTS) {  // triangular operand: shorter k range; triangular output: maybe nothing
+  if constexpr (HINTS) {  // per-item dims; triangular operand: shorter k range; triangular output: maybe nothing
+    p.m = item_dim(p.het_m, item, p.m);
+    p.n = item_dim(p.het_n, item, p.n);
+    p.k = item_dim(p.het_k, item, p.k);
+    if (m0 >= p.m || n0 >= p.n) return;
     const TileWork w = tile_work(p, p.k, m0, BM, n0, BN, BK);
     if (w.skip) return;
     A += a_k_offset(p, w.k_lo) * 8;
@@ -216,6 +220,10 @@ __global__ void __launch_bounds__(256, 2) gemm_dmma_z_kernel(GemmParams p, int t
   const unsigned char* B = (const unsigned char*)p.b + (item * p.sb + sv.b_off) * 16;
   double2* C = (double2*)p.c + vitem * p.sc;
   if constexpr (HINTS) {
+    p.m = item_dim(p.het_m, item, p.m);
+    p.n = item_dim(p.het_n, item, p.n);
+    p.k = item_dim(p.het_k, item, p.k);
+    if (m0 >= p.m || n0 >= p.n) return;
     const TileWork w = tile_work(p, p.k, m0, BM, n0, BN, BK);
     if (w.skip) return;
     A += a_k_offset(p, w.k_lo) * 16;
@@ -335,7 +343,7 @@ int launch_d(const GemmParams& p, cudaStream_t stream) {
   constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
   constexpr size_t smem = kStagesD * (size_t)(pitched_stage_bytes<8, 128, 16, AK>() + pitched_stage_bytes<8, 64, 16, BKM>());
   static thread_local int configured_for = -1, configured_for_hints = -1;
-  if (p.tri_a | p.tri_b | p.out_tri)
+  if (has_hints(p))
     return launch_kernel(gemm_dmma_d_kernel<OPA, OPB, true>, smem, p, 128, 64, stream, &configured_for_hints);
   return launch_kernel(gemm_dmma_d_kernel<OPA, OPB, false>, smem, p, 128, 64, stream, &configured_for);
 }
@@ -345,7 +353,7 @@ int launch_z(const GemmParams& p, cudaStream_t stream) {
   constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
   constexpr size_t smem = kStagesZ * (size_t)(pitched_stage_bytes<16, 64, 8, AK>() + pitched_stage_bytes<16, 64, 8, BKM>());
   static thread_local int configured_for = -1, configured_for_hints = -1;
-  if (p.tri_a | p.tri_b | p.out_tri)
+  if (has_hints(p))
     return launch_kernel(gemm_dmma_z_kernel<OPA, OPB, true>, smem, p, 64, 64, stream, &configured_for_hints);
   return launch_kernel(gemm_dmma_z_kernel<OPA, OPB, false>, smem, p, 64, 64, stream, &configured_for);
 }

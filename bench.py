@@ -597,6 +597,51 @@ def run_level3(args):
     print(json.dumps(out), flush=True)
 
 
+def run_hetero(args):
+    """Heterogeneous batches (per-item m, n inside a common capacity) on the reference's benchmark
+    pattern (benchmarks/gemm_heterogeneous_benchmark.cc:47-110): items cycle full size / half size /
+    empty, float, k = 32; plus a double case with a long k.  GFLOP/s counts the active sizes only."""
+    import ctypes
+
+    import numpy as np
+    import torch
+
+    import batchlas_b200 as bl
+    from batchlas_b200 import _lib
+    torch.cuda.set_device(0)
+    tdt = {"s": torch.float32, "d": torch.float64}
+    out = {"hetero": []}
+    for dt, mx, nx, k, batch in [("s", 64, 64, 32, 4096), ("s", 128, 128, 32, 1024), ("s", 256, 256, 32, 256),
+                                 ("s", 256, 256, 256, 2048), ("d", 256, 256, 256, 2048)]:
+        t = tdt[dt]
+        A = bl.fill(torch.empty(batch, k, mx, dtype=t, device="cuda"), 42, 0)
+        B = bl.fill(torch.empty(batch, nx, k, dtype=t, device="cuda"), 42, 1)
+        C = bl.fill(torch.empty(batch, nx, mx, dtype=t, device="cuda"), 42, 2)
+        idx = np.arange(batch) % 3
+        m_items = np.where(idx == 0, mx, np.where(idx == 1, mx // 2, 0)).astype(np.int32)
+        n_items = np.where(idx == 0, nx, np.where(idx == 1, nx // 2, 0)).astype(np.int32)
+        flops = float(np.sum(2.0 * m_items.astype(np.float64) * n_items * k))
+        dm, dn = torch.from_numpy(m_items).cuda(), torch.from_numpy(n_items).cuda()
+        d = bl.make_desc(A.data_ptr(), B.data_ptr(), C.data_ptr(), bl.DTYPE_CODES[t], 0, 0, mx, nx, k, batch, mx, k, mx,
+                         mx * k, k * nx, mx * nx, 1.0, 0.0)
+        stream = torch.cuda.current_stream().cuda_stream
+        fn = lambda: _lib.check(_lib.load().blb200_gemm_heterogeneous(d, dm.data_ptr(), dn.data_ptr(), None, stream))
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        ms = time_launches(torch, fn, args.steps)
+        kernel = bl.last_kernel_name()
+        full = lambda: bl.gemm_strided_batched(d)
+        for _ in range(3):
+            full()
+        torch.cuda.synchronize()
+        ms_full = time_launches(torch, full, args.steps)
+        out["hetero"].append({"dtype": dt, "max_m": mx, "max_n": nx, "k": k, "batch": batch, "ms": round(ms, 4),
+                              "gflops_active": round(flops / (ms * 1e-3) / 1e9, 1), "kernel": kernel,
+                              "ms_full_size_homogeneous": round(ms_full, 4)})
+    print(json.dumps(out), flush=True)
+
+
 def run_aux(args):
     """gemv and the elementwise helpers (the steps either side of gemm): achieved HBM GB/s against the
     measured copy bandwidth.  Algorithmic bytes: gemv reads A once (m*n*sizeof(T); x and y are noise and
@@ -661,6 +706,7 @@ def main():
     ap.add_argument("--case", default="", help="profiling mode: CONFIG[:OP], e.g. C2:NT or C3:TN (1 GPU)")
     ap.add_argument("--batch", type=int, default=0, help="batch override for --case")
     ap.add_argument("--kernel", default="auto", help="forced kernel for --case")
+    ap.add_argument("--hetero", action="store_true", help="time heterogeneous batches on the reference's pattern (1 GPU)")
     ap.add_argument("--aux", action="store_true", help="time gemv and the elementwise helpers against HBM bandwidth (1 GPU)")
     ap.add_argument("--level3", action="store_true", help="time symm/hemm/trmm/syrk/herk beside gemm (1 GPU)")
     ap.add_argument("--splitk", action="store_true", help="--case through blb200_gemm_splitk with planned scratch")
@@ -679,6 +725,9 @@ def main():
         return
     if args.aux:
         run_aux(args)
+        return
+    if args.hetero:
+        run_hetero(args)
         return
     if world != args.gpus and world == 1 and args.gpus > 1:
         raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")

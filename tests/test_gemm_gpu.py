@@ -140,6 +140,29 @@ def test_both_fp64_tile_kernels_on_ragged_and_aligned_shapes(bl, kernel, dt):
                 assert_parity(p, A, B, C0, C, what=f"{kernel} {dt} {oa}{ob} {m}x{n}x{k}")
 
 
+@pytest.mark.parametrize("dt", ["s", "d", "c"])
+def test_64x64_tiles_of_the_tiled_kernel(bl, dt):
+    """The 64 x 64 tile configuration (float below 1024^2, double and complex<float> up to one tile):
+    every op pair on full, ragged and tiny-k shapes; float also on shapes of several tiles."""
+    code = oracle.DTYPES[dt]
+    ops = ["N", "T"] if dt in "sd" else ["N", "T", "C"]
+    shapes = [(64, 64, 32, 3, 1.0, 0.0), (48, 48, 48, 2, 1.5, -0.5), (40, 36, 72, 2, 2.0, 1.0), (64, 20, 5, 2, 1.0, 0.5)]
+    if dt == "s":
+        shapes += [(200, 132, 70, 2, 2.0, -1.0), (320, 100, 64, 1, 1.0, 0.0), (96, 96, 96, 2, 1.0, 1.0)]
+    for oa in ops:
+        for ob in ops:
+            for (m, n, k, batch, alpha, beta) in shapes:
+                al = 4 if dt == "s" else 2  # elements per 16 bytes: the tile kernels want aligned columns
+                up = lambda rows: (rows + al - 1) // al * al
+                p = oracle.make_problem(dt, oa, ob, m, n, k, batch, lda=up(m if oa == "N" else k),
+                                        ldb=up(k if ob == "N" else n), ldc=up(m), alpha=scalar_for(code, alpha),
+                                        beta=scalar_for(code, beta))
+                A, B, C0 = make_inputs(p)
+                C, kern = run_device(bl, p, A, B, C0, kernel="tiled")
+                assert kern == "tiled"
+                assert_parity(p, A, B, C0, C, what=f"tiled {dt} {oa}{ob} {m}x{n}x{k}")
+
+
 def test_large_float_tiles_with_packed_fma(bl):
     """sgemm128 (A not transposed, B either way): aligned and ragged shapes, beta on and off; the
     float shapes the reference tunes by hand (256^3 aligned, 200 x 130 x 70 ragged with alpha = 2,
@@ -151,10 +174,15 @@ def test_large_float_tiles_with_packed_fma(bl):
                                              (100, 260, 44, 1, 1.0, 0.0)]:
             p = oracle.make_problem("s", "N", ob, m, n, k, batch, alpha=alpha, beta=beta)
             A, B, C0 = make_inputs(p)
-            C, kern = run_device(bl, p, A, B, C0)
             aligned = p.lda % 4 == 0 and p.ldb % 4 == 0 and p.ldc % 4 == 0
-            assert kern == ("sgemm128" if aligned else "generic"), kern  # unaligned ld must decline the fast path
+            C, kern = run_device(bl, p, A, B, C0)
+            # unaligned ld must decline the fast paths; aligned shapes go to whichever tile wastes less
+            assert kern in (("sgemm128", "tiled") if aligned else ("generic",)), kern
             assert_parity(p, A, B, C0, C, what=f"{kern} N{ob} {m}x{n}x{k}")
+            if aligned:
+                C, kern = run_device(bl, p, A, B, C0, kernel="sgemm128")
+                assert kern == "sgemm128"
+                assert_parity(p, A, B, C0, C, what=f"forced sgemm128 N{ob} {m}x{n}x{k}")
             Cn = C0.copy()
             Cn[:] = np.nan if beta == 0.0 else Cn
             if beta == 0.0:
@@ -202,7 +230,8 @@ def test_heterogeneous_batch_in_one_launch(bl, dt):
         bl._lib.check(bl._lib.load().blb200_gemm_heterogeneous(desc, dm.data_ptr(), dn.data_ptr(), dk.data_ptr(),
                                                                torch.cuda.current_stream().cuda_stream))
         torch.cuda.synchronize()
-        assert bl.last_kernel_name() == "generic_hetero"
+        # 16-byte aligned capacities (double, complex here) are taken by a tile kernel, the rest by the generic one
+        assert bl.last_kernel_name() in ("generic_hetero", "dmma", "tiled"), bl.last_kernel_name()
         C = dC.cpu().numpy()
         expect_untouched = np.ones(C.size, bool)
         es = A.itemsize
@@ -220,6 +249,43 @@ def test_heterogeneous_batch_in_one_launch(bl, dt):
     bl._lib.check(bl._lib.load().blb200_gemm_heterogeneous(desc, None, None, None, torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
     assert bl.last_kernel_name() != "generic_hetero"
+
+
+@pytest.mark.parametrize("dt", DTYPE_NAMES)
+def test_heterogeneous_batch_on_the_tile_kernels(bl, dt):
+    """Capacities of a tile and more with 16-byte aligned operands: the per-item dims are read by the
+    tile kernels themselves (one launch, tiles outside an item's dims return at once).  Includes the
+    reference benchmark's pattern of full / half / empty items (benchmarks/gemm_heterogeneous_benchmark.cc:47-97)."""
+    code = oracle.DTYPES[dt]
+    cap_m, cap_n, cap_k = 160, 136, 72
+    ms = [160, 80, 0, 129, 1, 160, 33]
+    ns = [136, 68, 0, 136, 136, 0, 7]
+    ks = [72, 72, 72, 0, 5, 72, 72]
+    batch = len(ms)
+    for oa, ob in [("N", "N"), ("T", "N"), ("N", "C"), ("C", "T")]:
+        p = oracle.make_problem(dt, oa, ob, cap_m, cap_n, cap_k, batch, alpha=scalar_for(code, 1.5),
+                                beta=scalar_for(code, -0.5))
+        A, B, C0 = make_inputs(p)
+        dA, dB, dC = (torch.from_numpy(x).cuda() for x in (A, B, C0))
+        dm, dn, dk = (torch.tensor(v, dtype=torch.int32, device="cuda") for v in (ms, ns, ks))
+        desc = bl.make_desc(dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), p.dtype, p.op_a, p.op_b, cap_m, cap_n, cap_k,
+                            batch, p.lda, p.ldb, p.ldc, p.stride_a, p.stride_b, p.stride_c, p.alpha, p.beta)
+        bl._lib.check(bl._lib.load().blb200_gemm_heterogeneous(desc, dm.data_ptr(), dn.data_ptr(), dk.data_ptr(),
+                                                               torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert bl.last_kernel_name() in ("dmma", "sgemm128", "tiled"), bl.last_kernel_name()
+        C = dC.cpu().numpy()
+        expect_untouched = np.ones(C.size, bool)
+        for b in range(batch):
+            pi = oracle.make_problem(dt, oa, ob, ms[b], ns[b], ks[b], 1, lda=p.lda, ldb=p.ldb, ldc=p.ldc,
+                                     alpha=p.alpha, beta=p.beta)
+            sl = lambda x, st: x[b * st:]
+            bad, worst = oracle.check(pi, sl(A, p.stride_a), sl(B, p.stride_b), sl(C0, p.stride_c), sl(C, p.stride_c))
+            assert bad == 0, (dt, oa, ob, b, worst)
+            for j in range(ns[b]):
+                expect_untouched[b * p.stride_c + j * p.ldc: b * p.stride_c + j * p.ldc + ms[b]] = False
+        assert np.array_equal(C.view(np.uint8).reshape(C.size, -1)[expect_untouched],
+                              C0.view(np.uint8).reshape(C0.size, -1)[expect_untouched])
 
 
 def run_splitk(bl, p, A, B, C0, splits):
