@@ -170,9 +170,7 @@ static int dispatch_untraced(const blb200_gemm_desc* d, const StructureHints* hi
 // The cp.async tile kernels in order of preference for this problem; the generic kernel (or
 // BLB200_E_UNSUPPORTED) when none of them takes it.
 static int launch_tile_kernel(const GemmParams& p, int dtype, cudaStream_t stream, bool generic_fallback = true) {
-  // double, one tile or less: the 64 x 64 DFMA tile beats a mostly empty 128 x 64 DMMA tile
-  const bool small_d = dtype == BLB200_D && p.m <= 64 && p.n <= 64 && tiled_supported(p, dtype);
-  if (!small_d && dmma_supported(p, dtype)) return launch_dmma(p, dtype, stream);
+  if (dmma_supported(p, dtype)) return launch_dmma(p, dtype, stream);
   if (sgemm128_supported(p, dtype) && sgemm128_preferred(p)) return launch_sgemm128(p, dtype, stream);
   if (tiled_supported(p, dtype)) return launch_tiled(p, dtype, stream);
   return generic_fallback ? launch_generic(p, dtype, stream) : BLB200_E_UNSUPPORTED;

@@ -13,8 +13,8 @@
 //   M-major A (op N):   stage rows are k, BM doubles each;    fragment (m = g, k = t) at [k][m]
 //   K-major A (op T/C): stage rows are m, BK doubles each;    fragment at [m][k]
 //   (g = lane >> 2, t = lane & 3; B likewise with n in place of m.)
-// A warp owns a 32 x 32 block of C as 4 x 4 DMMA tiles (16 accumulator pairs); a CTA of 8 warps
-// owns 128 x 64.  Complex operands keep (re, im) interleaved, one 16-byte fragment load per lane,
+// A warp owns a 32 x 32 block of C as 4 x 4 DMMA tiles (16 accumulator pairs); a CTA of 4 warps
+// owns 64 x 64, four CTAs share an SM.  Complex operands keep (re, im) interleaved, one 16-byte fragment load per lane,
 // and each complex tile product is four real DMMAs; conjugation flips the sign of the imaginary
 // fragment in registers.
 //
@@ -77,9 +77,10 @@ constexpr int kStagesD = 3, kStagesZ = 3;  // copy-ring depth; 4 gains ~1 % on N
 // ---- real double -------------------------------------------------------------------------------
 // HINTS = false is the plain gemm; HINTS = true reads the structure hints of GemmParams (a separate
 // instantiation, so that the plain kernel's code and register allocation stay what they were).
-template <int OPA, int OPB, bool HINTS>
-__global__ void __launch_bounds__(256, 2) gemm_dmma_d_kernel(GemmParams p, int tiles_m, int tiles_n) {
-  constexpr int BM = 128, BN = 64, BK = 16, STAGES = kStagesD, THREADS = 256;
+// WM x WN warps of 32 x 32 each; 16 / (WM * WN) CTAs per SM.
+template <int OPA, int OPB, bool HINTS, int WM, int WN>
+__global__ void __launch_bounds__(32 * WM * WN, 16 / (WM * WN)) gemm_dmma_d_kernel(GemmParams p, int tiles_m, int tiles_n) {
+  constexpr int BM = 32 * WM, BN = 32 * WN, BK = 16, STAGES = kStagesD, THREADS = 32 * WM * WN;
   constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
   constexpr int A_STAGE = pitched_stage_bytes<8, BM, BK, AK>(), B_STAGE = pitched_stage_bytes<8, BN, BK, BKM>();
   constexpr int A_PITCH = AK ? BK * 8 + pad_for(8, true) : BM * 8 + pad_for(8, false);
@@ -91,7 +92,7 @@ __global__ void __launch_bounds__(256, 2) gemm_dmma_d_kernel(GemmParams p, int t
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int wm = warp & 3, wn = warp >> 2;  // 4 x 2 warps, 32 x 32 each
+  const int wm = warp % WM, wn = warp / WM;  // WM x WN warps, 32 x 32 each
 
   const long long tiles_per_item = (long long)tiles_m * tiles_n;
   const long long tile = blockIdx.x;
@@ -191,9 +192,9 @@ __global__ void __launch_bounds__(256, 2) gemm_dmma_d_kernel(GemmParams p, int t
 
 // ---- complex double ------------------------------------------------------------------------------
 // CTA 64 x 64, 8 warps as 2 (m) x 4 (n), warp tile 32 x 16: 4 x 2 DMMA tiles, re and im planes.
-template <int OPA, int OPB, bool HINTS>
-__global__ void __launch_bounds__(256, 2) gemm_dmma_z_kernel(GemmParams p, int tiles_m, int tiles_n) {
-  constexpr int BM = 64, BN = 64, BK = 8, STAGES = kStagesZ, THREADS = 256;
+template <int OPA, int OPB, bool HINTS, int WM, int WN>
+__global__ void __launch_bounds__(32 * WM * WN, 16 / (WM * WN)) gemm_dmma_z_kernel(GemmParams p, int tiles_m, int tiles_n) {
+  constexpr int BM = 32 * WM, BN = 16 * WN, BK = 8, STAGES = kStagesZ, THREADS = 32 * WM * WN;
   constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
   constexpr bool CONJ_A = (OPA == BLB200_H), CONJ_B = (OPB == BLB200_H);
   constexpr int A_STAGE = pitched_stage_bytes<16, BM, BK, AK>(), B_STAGE = pitched_stage_bytes<16, BN, BK, BKM>();
@@ -206,7 +207,7 @@ __global__ void __launch_bounds__(256, 2) gemm_dmma_z_kernel(GemmParams p, int t
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int wm = warp & 1, wn = warp >> 1;  // 2 x 4 warps, 32 x 16 each
+  const int wm = warp % WM, wn = warp / WM;  // WM x WN warps, 32 x 16 each
 
   const long long tiles_per_item = (long long)tiles_m * tiles_n;
   const long long tile = blockIdx.x;
@@ -323,7 +324,8 @@ __global__ void __launch_bounds__(256, 2) gemm_dmma_z_kernel(GemmParams p, int t
 }
 
 template <typename Kern>
-int launch_kernel(Kern kern, size_t smem, const GemmParams& p, int BM, int BN, cudaStream_t stream, int* configured_for) {
+int launch_kernel(Kern kern, size_t smem, const GemmParams& p, int BM, int BN, cudaStream_t stream, int* configured_for,
+                  int threads = 256) {
   const int tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BN - 1) / BN;
   const long long total = (long long)tiles_m * tiles_n * p.batch;
   if (total > 0x7fffffffLL) return BLB200_E_UNSUPPORTED;
@@ -334,28 +336,48 @@ int launch_kernel(Kern kern, size_t smem, const GemmParams& p, int BM, int BN, c
     if (e != cudaSuccess) return (int)e;
     *configured_for = cur;
   }
-  kern<<<(unsigned)total, 256, smem, stream>>>(p, tiles_m, tiles_n);
+  kern<<<(unsigned)total, threads, smem, stream>>>(p, tiles_m, tiles_n);
   return (int)cudaGetLastError();
 }
 
-template <int OPA, int OPB>
-int launch_d(const GemmParams& p, cudaStream_t stream) {
+template <int OPA, int OPB, int WM, int WN>
+int launch_d_tile(const GemmParams& p, cudaStream_t stream) {
   constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
-  constexpr size_t smem = kStagesD * (size_t)(pitched_stage_bytes<8, 128, 16, AK>() + pitched_stage_bytes<8, 64, 16, BKM>());
+  constexpr size_t smem =
+      kStagesD * (size_t)(pitched_stage_bytes<8, 32 * WM, 16, AK>() + pitched_stage_bytes<8, 32 * WN, 16, BKM>());
   static thread_local int configured_for = -1, configured_for_hints = -1;
   if (has_hints(p))
-    return launch_kernel(gemm_dmma_d_kernel<OPA, OPB, true>, smem, p, 128, 64, stream, &configured_for_hints);
-  return launch_kernel(gemm_dmma_d_kernel<OPA, OPB, false>, smem, p, 128, 64, stream, &configured_for);
+    return launch_kernel(gemm_dmma_d_kernel<OPA, OPB, true, WM, WN>, smem, p, 32 * WM, 32 * WN, stream,
+                         &configured_for_hints, 32 * WM * WN);
+  return launch_kernel(gemm_dmma_d_kernel<OPA, OPB, false, WM, WN>, smem, p, 32 * WM, 32 * WN, stream, &configured_for,
+                       32 * WM * WN);
 }
 
+// 2 x 2 warps (CTA 64 x 64, four CTAs per SM).  Measured against 4 x 2 (128 x 64, two CTAs per SM),
+// 2 x 4, 4 x 1 and 2 x 1: 256^3 b2048 31.7-32.0 TFLOP/s (TN 29.5) against 28.8-29.3, 1024^3 33.5
+// against 32.0, and shapes that are not multiples of 128 gain more (160^3: 19.9 against 13.8).
 template <int OPA, int OPB>
-int launch_z(const GemmParams& p, cudaStream_t stream) {
+int launch_d(const GemmParams& p, cudaStream_t stream) {
+  return launch_d_tile<OPA, OPB, 2, 2>(p, stream);
+}
+
+template <int OPA, int OPB, int WM, int WN>
+int launch_z_tile(const GemmParams& p, cudaStream_t stream) {
   constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
-  constexpr size_t smem = kStagesZ * (size_t)(pitched_stage_bytes<16, 64, 8, AK>() + pitched_stage_bytes<16, 64, 8, BKM>());
+  constexpr size_t smem =
+      kStagesZ * (size_t)(pitched_stage_bytes<16, 32 * WM, 8, AK>() + pitched_stage_bytes<16, 16 * WN, 8, BKM>());
   static thread_local int configured_for = -1, configured_for_hints = -1;
   if (has_hints(p))
-    return launch_kernel(gemm_dmma_z_kernel<OPA, OPB, true>, smem, p, 64, 64, stream, &configured_for_hints);
-  return launch_kernel(gemm_dmma_z_kernel<OPA, OPB, false>, smem, p, 64, 64, stream, &configured_for);
+    return launch_kernel(gemm_dmma_z_kernel<OPA, OPB, true, WM, WN>, smem, p, 32 * WM, 16 * WN, stream,
+                         &configured_for_hints, 32 * WM * WN);
+  return launch_kernel(gemm_dmma_z_kernel<OPA, OPB, false, WM, WN>, smem, p, 32 * WM, 16 * WN, stream, &configured_for,
+                       32 * WM * WN);
+}
+
+// 2 x 4 warps of 32 x 16 (CTA 64 x 64); 2 x 2, 1 x 4 and 1 x 2 measured within 1 % of it.
+template <int OPA, int OPB>
+int launch_z(const GemmParams& p, cudaStream_t stream) {
+  return launch_z_tile<OPA, OPB, 2, 4>(p, stream);
 }
 
 }  // namespace

@@ -32,7 +32,7 @@ SplitPlan plan_split(const blb200_gemm_desc& d, int splits_wanted) {
   if (d.m <= 0 || d.n <= 0 || d.batch <= 0 || d.k <= 0) return pl;
   int splits = splits_wanted;
   if (splits <= 0) {
-    const int bm = (d.dtype == BLB200_Z) ? 64 : 128, bn = (d.dtype == BLB200_S) ? 128 : 64;
+    const int bm = (d.dtype == BLB200_S) ? 128 : 64, bn = (d.dtype == BLB200_S) ? 128 : 64;  // CTA tiles of the kernels used
     const long long tiles = (long long)((d.m + bm - 1) / bm) * ((d.n + bn - 1) / bn) * d.batch;
     const long long sms = device_info().sm_count;
     if (tiles >= sms) return pl;

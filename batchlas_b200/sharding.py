@@ -20,15 +20,17 @@ def shard_range(batch: int, rank: int, world: int) -> tuple[int, int]:
 
 
 def shard_desc(desc, rank: int, world: int, elem_bytes: int):
-    """Copy of a GemmDesc restricted to `rank`'s contiguous batch range: base pointers advance by
-    b0*stride elements, ld/stride are unchanged, batch becomes the shard's item count."""
+    """Copy of a descriptor (GemmDesc, EwiseDesc or GemvDesc) restricted to `rank`'s contiguous batch
+    range: every base pointer advances by b0*stride elements of its own operand, ld/inc/stride are
+    unchanged, batch becomes the shard's item count."""
     import ctypes
     b0, nb = shard_range(desc.batch, rank, world)
     sub = type(desc)()
     ctypes.memmove(ctypes.byref(sub), ctypes.byref(desc), ctypes.sizeof(desc))
-    sub.a = (desc.a or 0) + b0 * desc.stride_a * elem_bytes
-    sub.b = (desc.b or 0) + b0 * desc.stride_b * elem_bytes
-    sub.c = (desc.c or 0) + b0 * desc.stride_c * elem_bytes
+    names = {f[0] for f in desc._fields_}
+    for ptr in ("a", "b", "c", "x", "y"):
+        if ptr in names:
+            setattr(sub, ptr, (getattr(desc, ptr) or 0) + b0 * getattr(desc, "stride_" + ptr) * elem_bytes)
     sub.batch = nb
     return sub
 

@@ -181,3 +181,19 @@ def test_shard_ranges_partition_the_batch():
     assert shard_range(512, 3, 8) == (192, 64)
     with pytest.raises(ValueError):
         shard_range(10, 2, 2)
+
+
+def test_shard_desc_advances_every_operand_of_every_descriptor():
+    from batchlas_b200.sharding import shard_desc
+    g = _lib.GemmDesc()
+    g.a, g.b, g.c, g.batch, g.stride_a, g.stride_b, g.stride_c = 1000, 2000, 3000, 10, 6, 8, 12
+    sub = shard_desc(g, 1, 4, 8)   # items [2, 5)
+    assert (sub.a, sub.b, sub.c, sub.batch) == (1000 + 2 * 6 * 8, 2000 + 2 * 8 * 8, 3000 + 2 * 12 * 8, 3)
+    v = _lib.GemvDesc()
+    v.a, v.x, v.y, v.batch, v.stride_a, v.stride_x, v.stride_y, v.incx = 1000, 2000, 3000, 9, 20, 5, 4, 2
+    sub = shard_desc(v, 2, 3, 4)   # items [6, 9)
+    assert (sub.a, sub.x, sub.y, sub.batch, sub.incx) == (1000 + 6 * 20 * 4, 2000 + 6 * 5 * 4, 3000 + 6 * 4 * 4, 3, 2)
+    e = _lib.EwiseDesc()
+    e.a, e.b, e.c, e.batch, e.stride_a, e.stride_b, e.stride_c = 16, 32, 48, 4, 100, 100, 200
+    sub = shard_desc(e, 3, 4, 16)  # item 3
+    assert (sub.a, sub.b, sub.c, sub.batch) == (16 + 3 * 100 * 16, 32 + 3 * 100 * 16, 48 + 3 * 200 * 16, 1)
