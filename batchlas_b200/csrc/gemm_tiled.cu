@@ -305,6 +305,11 @@ int launch_ops(const GemmParams& p, cudaStream_t stream) {
 
 inline bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
 
+// Work after rounding m and n up to whole bm x bn tiles.
+inline long long padded_work(int m, int n, int bm, int bn) {
+  return (long long)((m + bm - 1) / bm) * bm * ((n + bn - 1) / bn) * bn;
+}
+
 }  // namespace
 
 bool tiled_supported(const GemmParams& p, int dtype) {
@@ -322,9 +327,11 @@ int launch_tiled(const GemmParams& p, int dtype, cudaStream_t stream) {
   int rc;
   switch (dtype) {
     // Two tile sizes per type.  The 64 x 64 tile (4 x 4 register blocks, three CTAs per SM) wastes
-    // less on shapes that are not multiples of 128 and was at least as fast as the 128-wide one up to
-    // 512^3 (float 320^3: 38.6 against 23.7 TFLOP/s); the wide tile keeps the largest problems, where
-    // its reuse of A and B through shared memory counts.
+    // less on shapes that are not multiples of 128.  float: it was at least as fast as the 128-wide
+    // one up to 512^3 (320^3: 38.6 against 23.7 TFLOP/s), so the wide tile keeps only the largest
+    // problems.  complex<float>: the wide tile is about 5 % faster on full tiles (256^3: 50.0 against
+    // 47.4), so the small one takes over when it saves more than that in padding (160^3: 32.3
+    // against 25.6).
     case BLB200_S:
       if (p.m >= 1024 && p.n >= 1024) rc = launch_ops<float, Tile<float, 128, 128, 16, 8, 8, 3>, 1>(p, stream);
       else rc = launch_ops<float, Tile<float, 64, 64, 16, 4, 4, 3>, 3>(p, stream);
@@ -334,7 +341,8 @@ int launch_tiled(const GemmParams& p, int dtype, cudaStream_t stream) {
       else rc = launch_ops<double, Tile<double, 128, 64, 16, 8, 4, 3>, 2>(p, stream);
       break;
     case BLB200_C:
-      if (p.m <= 64 && p.n <= 64) rc = launch_ops<float2, Tile<float2, 64, 64, 16, 4, 4, 3>, 3>(p, stream);
+      if ((p.m <= 64 && p.n <= 64) || 20 * padded_work(p.m, p.n, 128, 64) > 21 * padded_work(p.m, p.n, 64, 64))
+        rc = launch_ops<float2, Tile<float2, 64, 64, 16, 4, 4, 3>, 3>(p, stream);
       else rc = launch_ops<float2, Tile<float2, 128, 64, 16, 8, 4, 3>, 2>(p, stream);
       break;
     case BLB200_Z: rc = launch_ops<double2, Tile<double2, 64, 64, 16, 4, 4, 3>, 2>(p, stream); break;

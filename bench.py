@@ -653,8 +653,14 @@ def run_aux(args):
     peak, src = measured_peaks()
     tdt = {"s": torch.float32, "d": torch.float64, "c": torch.complex64, "z": torch.complex128}
     out = {"hbm_peak_gbs": peak, "peak_source": src, "gemv": [], "elementwise": []}
-    for dt, m, n, batch in [("s", 32, 32, 1_000_000), ("s", 64, 64, 200_000), ("d", 256, 256, 8192), ("d", 1024, 1024, 512),
-                            ("s", 8192, 8192, 8), ("d", 16384, 16384, 1), ("z", 128, 128, 8192)]:
+    gemv_cases = [("s", 32, 32, 1_000_000), ("s", 64, 64, 200_000), ("d", 256, 256, 8192), ("d", 1024, 1024, 512),
+                  ("s", 8192, 8192, 8), ("d", 16384, 16384, 1), ("z", 128, 128, 8192)]
+    ew_cases = [("s", 32, 32, 1_000_000, True), ("d", 1024, 1024, 128, True), ("d", 1000, 1000, 128, False),
+                ("s", 32, 32, 500_000, False)]
+    if args.aux_gemv:  # one small gemv case only: what a profiler captures
+        dt, m, n, batch = args.aux_gemv.split(",")
+        gemv_cases, ew_cases = [(dt, int(m), int(n), int(batch))], []
+    for dt, m, n, batch in gemv_cases:
         t = tdt[dt]
         A = bl.fill(torch.empty(batch, n, m, dtype=t, device="cuda"), 42, 0)
         row = {"dtype": dt, "m": m, "n": n, "batch": batch, "ops": {}}
@@ -671,8 +677,7 @@ def run_aux(args):
             row["ops"][name] = {"ms": round(ms, 4), "hbm_gbs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak, 3)}
         out["gemv"].append(row)
         del A
-    for dt, rows, cols, batch, packed in [("s", 32, 32, 1_000_000, True), ("d", 1024, 1024, 128, True),
-                                          ("d", 1000, 1000, 128, False), ("s", 32, 32, 500_000, False)]:
+    for dt, rows, cols, batch, packed in ew_cases:
         t = tdt[dt]
         ld = rows if packed else rows + 8
         def mk(i):
@@ -708,6 +713,7 @@ def main():
     ap.add_argument("--kernel", default="auto", help="forced kernel for --case")
     ap.add_argument("--hetero", action="store_true", help="time heterogeneous batches on the reference's pattern (1 GPU)")
     ap.add_argument("--aux", action="store_true", help="time gemv and the elementwise helpers against HBM bandwidth (1 GPU)")
+    ap.add_argument("--aux-gemv", default="", help="with --aux: only this gemv case, DTYPE,M,N,BATCH (e.g. s,32,32,100000)")
     ap.add_argument("--level3", action="store_true", help="time symm/hemm/trmm/syrk/herk beside gemm (1 GPU)")
     ap.add_argument("--splitk", action="store_true", help="--case through blb200_gemm_splitk with planned scratch")
     args = ap.parse_args()
