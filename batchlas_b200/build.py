@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libbatchlas_b200.so")
-SOURCES = ["dispatch.cu", "gemm_generic.cu", "gemm_small.cu", "gemm_tiled.cu", "gemm_dmma.cu", "gemm_sgemm128.cu", "gemm_splitk.cu", "level3.cu", "gemv.cu", "gemv_ring.cu", "elementwise.cu", "arena.cu", "fill.cu",
+SOURCES = ["dispatch.cu", "gemm_generic.cu", "gemm_small.cu", "gemm_tiled.cu", "gemm_tiled_s.cu", "gemm_tiled_d.cu", "gemm_tiled_c.cu", "gemm_tiled_z.cu", "gemm_dmma.cu", "gemm_sgemm128.cu", "gemm_splitk.cu", "level3.cu", "gemv.cu", "gemv_ring.cu", "elementwise.cu", "arena.cu", "fill.cu",
            "host_pipeline.cu", "status.cu", "peak.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
@@ -74,7 +74,7 @@ def build(force: bool = False) -> str:
 
 def _build_objects_and_link(force: bool) -> None:
     os.makedirs(OBJ, exist_ok=True)
-    with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as ex:
+    with concurrent.futures.ThreadPoolExecutor(max_workers=min(os.cpu_count() or 8, len(SOURCES))) as ex:
         objs = list(ex.map(lambda s: _compile(s, force, OBJ), SOURCES))
     if force or not os.path.exists(LIB) or any(os.path.getmtime(o) > os.path.getmtime(LIB) for o in objs):
         subprocess.check_call([_nvcc(), "-shared", "-o", LIB, *objs, "-cudart", "static", "-lpthread", "-ldl"])
