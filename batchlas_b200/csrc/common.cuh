@@ -210,6 +210,8 @@ int launch_splitk_reduce(const GemmParams& orig, int dtype, const void* partials
 
 bool small32_supported(const GemmParams& p, int dtype);
 bool small64_supported(const GemmParams& p, int dtype);
+bool small_ring_supported(const GemmParams& p, int dtype);
+int launch_small_ring(const GemmParams& p, int dtype, cudaStream_t stream);
 bool tiled_supported(const GemmParams& p, int dtype);
 bool dmma_supported(const GemmParams& p, int dtype);
 bool sgemm128_supported(const GemmParams& p, int dtype);

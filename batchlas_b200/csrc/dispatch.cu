@@ -237,6 +237,7 @@ static int dispatch_untraced(const blb200_gemm_desc* d, const StructureHints* hi
   }
   if (small32_supported(p, d->dtype)) return launch_small32(p, d->dtype, stream);
   if (small64_supported(p, d->dtype)) return launch_small64(p, d->dtype, stream);
+  if (small_ring_supported(p, d->dtype)) return launch_small_ring(p, d->dtype, stream);
   return launch_tile_kernel(p, d->dtype, stream);
 }
 

@@ -4,6 +4,7 @@
 namespace blb200 {
 int small_device_status(int* out);
 int gemv_ring_device_status(int* out);
+int small_ring_device_status(int* out);
 }
 
 // Synchronises the current device, then writes the first non-zero status word to *out
@@ -18,6 +19,10 @@ extern "C" int blb200_device_status(int* out) {
   if (rc != 0) return rc;
   if (word == 0) {
     rc = blb200::gemv_ring_device_status(&word);
+    if (rc != 0) return rc;
+  }
+  if (word == 0) {
+    rc = blb200::small_ring_device_status(&word);
     if (rc != 0) return rc;
   }
   *out = word;

@@ -163,6 +163,38 @@ def test_64x64_tiles_of_the_tiled_kernel(bl, dt):
                 assert_parity(p, A, B, C0, C, what=f"tiled {dt} {oa}{ob} {m}x{n}x{k}")
 
 
+@pytest.mark.parametrize("dt", DTYPE_NAMES)
+def test_small_packed_matrices_of_every_type_through_the_ring(bl, dt):
+    """Large batches of packed matrices up to 32 x 32 (complex<double>: 8 x 8), any k up to 64: the
+    general whole-matrix-per-warp ring kernel, every op pair, beta on and off, ragged shapes whose
+    operands are still multiples of 16 bytes."""
+    code = oracle.DTYPES[dt]
+    ops = ["N", "T"] if dt in "sd" else ["N", "T", "C"]
+    shapes = [(8, 8, 8), (8, 4, 64), (5, 8, 16)]
+    if dt != "z":
+        shapes += [(16, 16, 16), (12, 20, 28), (16, 4, 64), (32, 32, 16), (24, 24, 24), (32, 20, 36)]
+    if dt in "dc":
+        shapes += [(32, 32, 32)]
+    for oa in ops:
+        for ob in ops:
+            for (m, n, k) in shapes:
+                for alpha, beta in [(1.5, -0.5), (2.0, 0.0)]:
+                    batch = 1300
+                    p = oracle.make_problem(dt, oa, ob, m, n, k, batch, alpha=scalar_for(code, alpha),
+                                            beta=scalar_for(code, beta))
+                    A, B, C0 = make_inputs(p)
+                    if beta == 0.0:
+                        C0[:] = np.nan
+                    C, kern = run_device(bl, p, A, B, C0)
+                    assert kern == "small_ring", (kern, dt, oa, ob, m, n, k)
+                    Cz = np.zeros_like(C0) if beta == 0.0 else C0  # beta == 0: the NaNs must not be read
+                    bad, worst = oracle.check(p, A, B, Cz, C, [0, 1, 2, 147, 148, 149, 700, 1297, 1298, 1299])
+                    assert bad == 0, f"small_ring {dt} {oa}{ob} {m}x{n}x{k} beta={beta}: worst ratio {worst:.3g}"
+                    assert not np.isnan(C[: p.alloc_len("c")].view(np.float32 if dt in "sc" else np.float64)).any()
+                    assert oracle.untouched_outside_window(p, C0, C)
+    assert bl.device_status() == 0
+
+
 def test_large_float_tiles_with_packed_fma(bl):
     """sgemm128 (A not transposed, B either way): aligned and ragged shapes, beta on and off; the
     float shapes the reference tunes by hand (256^3 aligned, 200 x 130 x 70 ragged with alpha = 2,
