@@ -114,9 +114,13 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
       bp[c] = Bs + (B_KMAJOR ? col * k : col);
     }
     const int a_step = A_KMAJOR ? 1 : m, b_step = B_KMAJOR ? 1 : n;
-    int kk = k0, a_off = k0 * a_step, b_off = k0 * b_step;
+    // the k index of step t is computed from t alone (no value carried from step to step), so the
+    // loads of the following steps can be issued while this step's multiply-adds are still running
 #pragma unroll 4
     for (int t = 0; t < k; ++t) {
+      int kk = k0 + t;
+      kk -= kk >= k ? k : 0;
+      const int a_off = kk * a_step, b_off = kk * b_step;
       T av[RB], bv[CB];
 #pragma unroll
       for (int r = 0; r < RB; ++r) av[r] = maybe_conj(ap[r][a_off], conj_a);
@@ -126,9 +130,6 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
       for (int r = 0; r < RB; ++r)
 #pragma unroll
         for (int c = 0; c < CB; ++c) Scalar<T>::fma(acc[r][c], av[r], bv[c]);
-      a_off += a_step;
-      b_off += b_step;
-      if (++kk == k) kk = a_off = b_off = 0;
     }
 
     // The result is assembled in the slot (over the old C, or over A when there is none: every lane
