@@ -465,11 +465,14 @@ def run_ours(args, rank, local_rank, world):
                     launch()
                 torch.cuda.synchronize()
                 one = time_launches(torch, launch, 1)
-                reps = int(max(3, min(2000, 400.0 / max(one, 1e-3))))
+                # about 60 ms of back-to-back launches after a short idle: a kernel timed alone.  Held
+                # for 150 ms or more, the FP32 64^3 case reaches the 1000 W cap and the SM clock falls
+                # from 1965 to about 1710 MHz; its throughput falls in the same proportion.
+                reps = int(max(3, min(1000, 60.0 / max(one, 1e-3))))
                 barrier()
                 smp = ClockSampler(local_rank)
                 smp.start()
-                time.sleep(0.15)
+                time.sleep(0.4)
                 tw0 = time.time()
                 ms = max_over_ranks(time_launches(torch, launch, reps))
                 tw1 = time.time()
