@@ -17,6 +17,10 @@
 // most 27 KiB, a batch large enough to keep a ring per SM busy.  Ring discipline as in the other ring kernels: the slot
 // count is a multiple of the consumer count, slot s always belongs to consumer s % CW, and every wait
 // is bounded (on expiry the waiter records a code in the device status word and returns).
+#include <stdlib.h>
+
+#include <type_traits>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -34,8 +38,19 @@ __device__ __forceinline__ T maybe_conj(T v, bool conj) {
   return v;
 }
 
+__device__ __forceinline__ void dmma884(double& c0, double& c1, double a, double b) {
+  asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+               : "+d"(c0), "+d"(c1)
+               : "d"(a), "d"(b));
+}
+
 // RB x CB: outputs per lane (4 x 8 covers 32 x 32; 2 x 4 covers 16 x 16 with a quarter of the registers).
-template <typename T, int CW, bool A_KMAJOR, bool B_KMAJOR, bool HAS_C, int RB, int CB>
+// DMMA (double only; m, n multiples of 8, k a multiple of 4): the product runs on the FP64 tensor
+// pipe instead.  RB x CB then counts 8 x 8 output tiles per warp; lane (g = lane >> 2, q = lane & 3)
+// feeds A(8rb + g, k0 + q) and B(k0 + q, 8cb + g) and receives C(8rb + g, 8cb + 2q), C(.., 8cb + 2q + 1):
+// two fragment doubles per lane for sixteen tile products per k-step of 4, where the scalar loop
+// reads twelve per 32 multiply-adds and is bound by the latency of those reads.
+template <typename T, int CW, bool A_KMAJOR, bool B_KMAJOR, bool HAS_C, int RB, int CB, bool DMMA = false>
 __global__ void __launch_bounds__(32 * (1 + CW), 1)
     gemm_small_ring_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C, int m, int n, int k,
                            long long sa, long long sb, long long sc, int batch, T alpha, T beta, bool conj_a, bool conj_b,
@@ -92,6 +107,66 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
     const T* Bs = reinterpret_cast<const T*>(smem + (size_t)s * slot_bytes + a_bytes);
     const T* Cs = reinterpret_cast<const T*>(smem + (size_t)s * slot_bytes + a_bytes + b_bytes);
 
+    if constexpr (DMMA) {
+      const int g = lane >> 2, q = lane & 3;
+      const int mt = m >> 3, nt = n >> 3;
+      double d0[RB][CB], d1[RB][CB];
+#pragma unroll
+      for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+        for (int cb = 0; cb < CB; ++cb) d0[rb][cb] = d1[rb][cb] = 0.0;
+      // tiles past the edge repeat the last valid one (read, multiplied nowhere, never stored)
+      const double* ap[RB];
+      const double* bp[CB];
+#pragma unroll
+      for (int rb = 0; rb < RB; ++rb) {
+        const int row = 8 * min(rb, mt - 1) + g;
+        ap[rb] = As + (A_KMAJOR ? row * k + q : q * m + row);
+      }
+#pragma unroll
+      for (int cb = 0; cb < CB; ++cb) {
+        const int col = 8 * min(cb, nt - 1) + g;
+        bp[cb] = Bs + (B_KMAJOR ? col * k + q : q * n + col);
+      }
+      const int a_step = A_KMAJOR ? 4 : 4 * m, b_step = B_KMAJOR ? 4 : 4 * n;
+#pragma unroll 2
+      for (int k0 = 0; k0 < k; k0 += 4) {
+        double av[RB], bv[CB];
+#pragma unroll
+        for (int rb = 0; rb < RB; ++rb) av[rb] = ap[rb][(k0 >> 2) * a_step];
+#pragma unroll
+        for (int cb = 0; cb < CB; ++cb) bv[cb] = bp[cb][(k0 >> 2) * b_step];
+#pragma unroll
+        for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+          for (int cb = 0; cb < CB; ++cb)
+            if (rb < mt && cb < nt) dmma884(d0[rb][cb], d1[rb][cb], av[rb], bv[cb]);
+      }
+      __syncwarp();
+      double* Os = const_cast<double*>(HAS_C ? Cs : As);
+#pragma unroll
+      for (int cb = 0; cb < CB; ++cb)
+#pragma unroll
+        for (int rb = 0; rb < RB; ++rb)
+          if (rb < mt && cb < nt) {
+            const int idx = (8 * cb + 2 * q) * m + 8 * rb + g;
+            double o0 = alpha * d0[rb][cb], o1 = alpha * d1[rb][cb];
+            if (HAS_C) {
+              o0 = fma(beta, Os[idx], o0);
+              o1 = fma(beta, Os[idx + m], o1);
+            }
+            Os[idx] = o0;
+            Os[idx + m] = o1;
+          }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        bulk_s2g(C + item * sc, Os, c_bytes);
+        bulk_commit();
+        bulk_wait_read<0>();
+        mbar_arrive(&empty_bar[s]);
+      }
+    } else {
     T acc[RB][CB];
 #pragma unroll
     for (int r = 0; r < RB; ++r)
@@ -159,6 +234,7 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
       bulk_wait_read<0>();
       mbar_arrive(&empty_bar[s]);
     }
+    }  // scalar path
     s += CW;
     if (s >= stages) {
       s -= stages;
@@ -170,11 +246,11 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
 
 inline bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
 
-template <typename T, int CW, bool AK, bool BK, bool HC, int RB, int CB>
+template <typename T, int CW, bool AK, bool BK, bool HC, int RB, int CB, bool DMMA = false>
 int launch_one(const GemmParams& p, int stages, int slot_bytes, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
   const size_t smem = (size_t)stages * slot_bytes + (size_t)stages * 2 * sizeof(uint64_t);
-  auto kern = gemm_small_ring_kernel<T, CW, AK, BK, HC, RB, CB>;
+  auto kern = gemm_small_ring_kernel<T, CW, AK, BK, HC, RB, CB, DMMA>;
   static thread_local int configured_for = -1;
   int cur = 0;
   cudaGetDevice(&cur);
@@ -196,8 +272,18 @@ int launch_cw(const GemmParams& p, int stages, int slot_bytes, bool hc, cudaStre
   const bool ak = p.op_a != BLB200_N;  // op T / H stores A as k x m: k runs fastest
   const bool bk = p.op_b == BLB200_N;  // op N stores B as k x n: k runs fastest
   const bool quarter = p.m <= 16 && p.n <= 16;
+  static const bool dmma_on = [] { const char* v = getenv("BLB200_SMALL_RING_DMMA"); return !(v && *v == '0'); }();
+  const bool dmma = std::is_same<T, double>::value && dmma_on && p.m % 8 == 0 && p.n % 8 == 0 && p.k % 4 == 0;
 #define BLB_CASE(a, b)                                                                                     \
   if (ak == a && bk == b) {                                                                                \
+    if constexpr (std::is_same<T, double>::value) {                                                        \
+      if (dmma && quarter)                                                                                 \
+        return hc ? launch_one<T, CW, a, b, true, 2, 2, true>(p, stages, slot_bytes, stream)               \
+                  : launch_one<T, CW, a, b, false, 2, 2, true>(p, stages, slot_bytes, stream);             \
+      if (dmma)                                                                                            \
+        return hc ? launch_one<T, CW, a, b, true, 4, 4, true>(p, stages, slot_bytes, stream)               \
+                  : launch_one<T, CW, a, b, false, 4, 4, true>(p, stages, slot_bytes, stream);             \
+    }                                                                                                      \
     if (quarter)                                                                                           \
       return hc ? launch_one<T, CW, a, b, true, 2, 4>(p, stages, slot_bytes, stream)                       \
                 : launch_one<T, CW, a, b, false, 2, 4>(p, stages, slot_bytes, stream);                     \
@@ -220,6 +306,15 @@ int launch_typed(const GemmParams& p, cudaStream_t stream) {
   const int slot_bytes = slot_elems * (int)sizeof(T);
   const size_t budget = device_info().smem_optin > 8192 ? device_info().smem_optin - 4096 : 0;
   const int fit = (int)(budget / (size_t)slot_bytes);
+  if constexpr (std::is_same<T, double>::value) {
+    // Tensor-pipe path with 4 x 4 tiles per warp (about 135 registers): 8 warps with two or more slots
+    // each where 16 slots fit (16 warps would cap a thread at 96 registers and spill: 24^3 ran at 2.4
+    // instead of 3.5 TB/s); bigger items stay on four warps with two or three slots each, which
+    // measured faster than eight warps with one (32^3: 4.0 against 3.9, beta = 0: 3.9 against 2.8 TB/s).
+    static const int dmma_cw = [] { const char* v = getenv("BLB200_SMALL_RING_DMMA_CW"); return v && *v ? atoi(v) : 8; }();
+    const bool tiles4 = (p.m > 16 || p.n > 16) && p.m % 8 == 0 && p.n % 8 == 0 && p.k % 4 == 0;
+    if (tiles4 && dmma_cw == 8 && fit >= 16) return launch_cw<T, 8>(p, (fit >= 32 ? 32 : fit) / 8 * 8, slot_bytes, hc, stream);
+  }
   // 16 warps with two slots each when that fits, else with one
   if (fit >= 32) return launch_cw<T, 16>(p, 32, slot_bytes, hc, stream);
   if (fit >= 16) return launch_cw<T, 16>(p, 16, slot_bytes, hc, stream);
