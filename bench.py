@@ -526,7 +526,14 @@ def run_case(args):
 
     import batchlas_b200 as bl
     name, _, op = args.case.partition(":")
-    c = configs()[name]
+    import re
+    shape = re.fullmatch(r"([sdcz])(\d+)x(\d+)x(\d+)", name)
+    if shape:  # an arbitrary packed shape, e.g. d32x32x32:TN: uniform inputs, alpha 1.5, beta from --beta
+        c = dict(dtype=shape.group(1), ops=[("N", "N")], m=int(shape.group(2)), n=int(shape.group(3)),
+                 k=int(shape.group(4)), batch=100_000, alpha=1.5, beta=args.beta, pad=0,
+                 dist_ab=("uniform", 1.0), dist_c=("uniform", 1.0))
+    else:
+        c = configs()[name]
     ops = [tuple(op)] if op else c["ops"]
     batch = args.batch or c["batch"]
     torch.cuda.set_device(0)
@@ -711,8 +718,9 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the C1/C3/C4/C5 figures")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--case", default="", help="profiling mode: CONFIG[:OP], e.g. C2:NT or C3:TN (1 GPU)")
+    ap.add_argument("--case", default="", help="profiling mode: CONFIG[:OP], e.g. C2:NT or C3:TN, or a packed shape such as d32x32x32:NN (1 GPU)")
     ap.add_argument("--batch", type=int, default=0, help="batch override for --case")
+    ap.add_argument("--beta", type=float, default=-0.5, help="beta of a --case given as a shape (DTYPE MxNxK, e.g. d32x32x32:TN)")
     ap.add_argument("--kernel", default="auto", help="forced kernel for --case")
     ap.add_argument("--hetero", action="store_true", help="time heterogeneous batches on the reference's pattern (1 GPU)")
     ap.add_argument("--aux", action="store_true", help="time gemv and the elementwise helpers against HBM bandwidth (1 GPU)")
