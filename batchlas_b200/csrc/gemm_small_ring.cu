@@ -50,11 +50,17 @@ __device__ __forceinline__ void dmma884(double& c0, double& c1, double a, double
 // feeds A(8rb + g, k0 + q) and B(k0 + q, 8cb + g) and receives C(8rb + g, 8cb + 2q), C(.., 8cb + 2q + 1):
 // two fragment doubles per lane for sixteen tile products per k-step of 4, where the scalar loop
 // reads twelve per 32 multiply-adds and is bound by the latency of those reads.
-template <typename T, int CW, bool A_KMAJOR, bool B_KMAJOR, bool HAS_C, int RB, int CB, bool DMMA = false>
+// PAIR (DMMA only): two consumer warps share every item, warp half h taking the column tiles
+// CB/2 * h ... (one warp alone issues DMMAs at about half the pipe's rate, and eight warps with a
+// slot each leave nothing in flight while they work).  Each half assembles and stores its own
+// columns of C — the slot then always has a C area, so nothing is written over A while the other
+// half still reads it — and a slot is handed back by two arrivals.
+template <typename T, int CW, bool A_KMAJOR, bool B_KMAJOR, bool HAS_C, int RB, int CB, bool DMMA = false,
+          bool PAIR = false>
 __global__ void __launch_bounds__(32 * (1 + CW), 1)
     gemm_small_ring_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C, int m, int n, int k,
                            long long sa, long long sb, long long sc, int batch, T alpha, T beta, bool conj_a, bool conj_b,
-                           int stages, int slot_bytes) {
+                           int stages, int slot_bytes, int self_feed) {
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)stages * slot_bytes);
   uint64_t* empty_bar = full_bar + stages;
@@ -65,7 +71,7 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
+      mbar_init(&empty_bar[s], PAIR ? 2 : 1);
     }
     mbar_fence_init();
   }
@@ -74,7 +80,21 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
   // Items of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...; the j-th one uses slot j % stages.
   const int my_items = (batch > (int)blockIdx.x) ? (batch - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
+  // self_feed (not with PAIR): no producer warp.  Lane 0 of the warp that owns a slot issues the
+  // copies of the item that uses the slot next, as soon as the bulk store has read the slot: the
+  // refill starts without a hand-over through an "empty" barrier that another warp has to notice.
+  auto issue = [&](int slot, int jj) {
+    unsigned char* st = smem + (size_t)slot * slot_bytes;
+    const long long it = (long long)blockIdx.x + (long long)jj * gridDim.x;
+    mbar_arrive_expect_tx(&full_bar[slot], a_bytes + b_bytes + (HAS_C ? c_bytes : 0u));
+    bulk_g2s(st, A + it * sa, a_bytes, &full_bar[slot]);
+    bulk_g2s(st + a_bytes, B + it * sb, b_bytes, &full_bar[slot]);
+    if (HAS_C) bulk_g2s(st + a_bytes + b_bytes, C + it * sc, c_bytes, &full_bar[slot]);
+  };
+  const bool feed = !PAIR && self_feed != 0;
+
   if (warp == 0) {
+    if (feed) return;
     if (lane < stages) {  // lane == slot
       unsigned char* st = smem + (size_t)lane * slot_bytes;
       uint32_t round = 0;
@@ -98,9 +118,13 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
   int k0 = (A_KMAJOR && B_KMAJOR) ? ti + 8 * tj : (A_KMAJOR ? ti : (B_KMAJOR ? tj : 0));
   k0 = k0 % k;
 
-  int s = cw;
+  constexpr int OWNERS = PAIR ? CW / 2 : CW;  // warps (or warp pairs) that own slots
+  const int owner = PAIR ? (cw >> 1) : cw;
+  if (feed && lane == 0)
+    for (int slot = cw; slot < stages && slot < my_items; slot += CW) issue(slot, slot);
+  int s = owner;
   uint32_t round = 0;
-  for (int j = cw; j < my_items; j += CW) {
+  for (int j = owner; j < my_items; j += OWNERS) {
     const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
     if (!mbar_wait(&full_bar[s], round & 1u, kSmallRingWaitFull)) return;
     const T* As = reinterpret_cast<const T*>(smem + (size_t)s * slot_bytes);
@@ -108,48 +132,50 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
     const T* Cs = reinterpret_cast<const T*>(smem + (size_t)s * slot_bytes + a_bytes + b_bytes);
 
     if constexpr (DMMA) {
+      constexpr int CBW = PAIR ? CB / 2 : CB;    // column tiles of this warp
+      const int cb0 = PAIR ? CBW * (cw & 1) : 0;  // first one
       const int g = lane >> 2, q = lane & 3;
       const int mt = m >> 3, nt = n >> 3;
-      double d0[RB][CB], d1[RB][CB];
+      double d0[RB][CBW], d1[RB][CBW];
 #pragma unroll
       for (int rb = 0; rb < RB; ++rb)
 #pragma unroll
-        for (int cb = 0; cb < CB; ++cb) d0[rb][cb] = d1[rb][cb] = 0.0;
+        for (int cb = 0; cb < CBW; ++cb) d0[rb][cb] = d1[rb][cb] = 0.0;
       // tiles past the edge repeat the last valid one (read, multiplied nowhere, never stored)
       const double* ap[RB];
-      const double* bp[CB];
+      const double* bp[CBW];
 #pragma unroll
       for (int rb = 0; rb < RB; ++rb) {
         const int row = 8 * min(rb, mt - 1) + g;
         ap[rb] = As + (A_KMAJOR ? row * k + q : q * m + row);
       }
 #pragma unroll
-      for (int cb = 0; cb < CB; ++cb) {
-        const int col = 8 * min(cb, nt - 1) + g;
+      for (int cb = 0; cb < CBW; ++cb) {
+        const int col = 8 * min(cb0 + cb, nt - 1) + g;
         bp[cb] = Bs + (B_KMAJOR ? col * k + q : q * n + col);
       }
       const int a_step = A_KMAJOR ? 4 : 4 * m, b_step = B_KMAJOR ? 4 : 4 * n;
 #pragma unroll 2
       for (int k0 = 0; k0 < k; k0 += 4) {
-        double av[RB], bv[CB];
+        double av[RB], bv[CBW];
 #pragma unroll
         for (int rb = 0; rb < RB; ++rb) av[rb] = ap[rb][(k0 >> 2) * a_step];
 #pragma unroll
-        for (int cb = 0; cb < CB; ++cb) bv[cb] = bp[cb][(k0 >> 2) * b_step];
+        for (int cb = 0; cb < CBW; ++cb) bv[cb] = bp[cb][(k0 >> 2) * b_step];
 #pragma unroll
         for (int rb = 0; rb < RB; ++rb)
 #pragma unroll
-          for (int cb = 0; cb < CB; ++cb)
-            if (rb < mt && cb < nt) dmma884(d0[rb][cb], d1[rb][cb], av[rb], bv[cb]);
+          for (int cb = 0; cb < CBW; ++cb)
+            if (rb < mt && cb0 + cb < nt) dmma884(d0[rb][cb], d1[rb][cb], av[rb], bv[cb]);
       }
       __syncwarp();
-      double* Os = const_cast<double*>(HAS_C ? Cs : As);
+      double* Os = const_cast<double*>((HAS_C || PAIR) ? Cs : As);
 #pragma unroll
-      for (int cb = 0; cb < CB; ++cb)
+      for (int cb = 0; cb < CBW; ++cb)
 #pragma unroll
         for (int rb = 0; rb < RB; ++rb)
-          if (rb < mt && cb < nt) {
-            const int idx = (8 * cb + 2 * q) * m + 8 * rb + g;
+          if (rb < mt && cb0 + cb < nt) {
+            const int idx = (8 * (cb0 + cb) + 2 * q) * m + 8 * rb + g;
             double o0 = alpha * d0[rb][cb], o1 = alpha * d1[rb][cb];
             if (HAS_C) {
               o0 = fma(beta, Os[idx], o0);
@@ -161,10 +187,16 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
       fence_async_smem();
       __syncwarp();
       if (lane == 0) {
-        bulk_s2g(C + item * sc, Os, c_bytes);
-        bulk_commit();
-        bulk_wait_read<0>();
-        mbar_arrive(&empty_bar[s]);
+        // this warp's columns are one contiguous run of C
+        const int c_first = 8 * cb0, c_last = min(n, 8 * (cb0 + CBW));
+        if (c_last > c_first) {
+          bulk_s2g(C + item * sc + (long long)c_first * m, Os + c_first * m,
+                   (uint32_t)((c_last - c_first) * m * (int)sizeof(double)));
+          bulk_commit();
+          bulk_wait_read<0>();
+        }
+        if (!feed) mbar_arrive(&empty_bar[s]);
+        else if (j + stages < my_items) issue(s, j + stages);
       }
     } else {
     T acc[RB][CB];
@@ -232,10 +264,11 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
       bulk_s2g(C + item * sc, Os, c_bytes);
       bulk_commit();
       bulk_wait_read<0>();
-      mbar_arrive(&empty_bar[s]);
+      if (!feed) mbar_arrive(&empty_bar[s]);
+      else if (j + stages < my_items) issue(s, j + stages);
     }
     }  // scalar path
-    s += CW;
+    s += OWNERS;
     if (s >= stages) {
       s -= stages;
       ++round;
@@ -246,11 +279,16 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
 
 inline bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
 
-template <typename T, int CW, bool AK, bool BK, bool HC, int RB, int CB, bool DMMA = false>
+bool dmma_enabled() {
+  static const bool on = [] { const char* v = getenv("BLB200_SMALL_RING_DMMA"); return !(v && *v == '0'); }();
+  return on;
+}
+
+template <typename T, int CW, bool AK, bool BK, bool HC, int RB, int CB, bool DMMA = false, bool PAIR = false>
 int launch_one(const GemmParams& p, int stages, int slot_bytes, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
   const size_t smem = (size_t)stages * slot_bytes + (size_t)stages * 2 * sizeof(uint64_t);
-  auto kern = gemm_small_ring_kernel<T, CW, AK, BK, HC, RB, CB, DMMA>;
+  auto kern = gemm_small_ring_kernel<T, CW, AK, BK, HC, RB, CB, DMMA, PAIR>;
   static thread_local int configured_for = -1;
   int cur = 0;
   cudaGetDevice(&cur);
@@ -260,10 +298,11 @@ int launch_one(const GemmParams& p, int stages, int slot_bytes, cudaStream_t str
     configured_for = cur;
   }
   const int grid = p.batch < dev.sm_count ? p.batch : dev.sm_count;
+  static const int self_feed = [] { const char* v = getenv("BLB200_SMALL_RING_SELF_FEED"); return v && *v ? atoi(v) : 1; }();
   kern<<<grid, 32 * (1 + CW), smem, stream>>>((const T*)p.a, (const T*)p.b, (T*)p.c, p.m, p.n, p.k, p.sa, p.sb, p.sc,
                                             p.batch, Scalar<T>::make(p.alpha[0], p.alpha[1]),
                                             Scalar<T>::make(p.beta[0], p.beta[1]), p.op_a == BLB200_H,
-                                            p.op_b == BLB200_H, stages, slot_bytes);
+                                            p.op_b == BLB200_H, stages, slot_bytes, self_feed);
   return (int)cudaGetLastError();
 }
 
@@ -272,8 +311,7 @@ int launch_cw(const GemmParams& p, int stages, int slot_bytes, bool hc, cudaStre
   const bool ak = p.op_a != BLB200_N;  // op T / H stores A as k x m: k runs fastest
   const bool bk = p.op_b == BLB200_N;  // op N stores B as k x n: k runs fastest
   const bool quarter = p.m <= 16 && p.n <= 16;
-  static const bool dmma_on = [] { const char* v = getenv("BLB200_SMALL_RING_DMMA"); return !(v && *v == '0'); }();
-  const bool dmma = std::is_same<T, double>::value && dmma_on && p.m % 8 == 0 && p.n % 8 == 0 && p.k % 4 == 0;
+  const bool dmma = std::is_same<T, double>::value && dmma_enabled() && p.m % 8 == 0 && p.n % 8 == 0 && p.k % 4 == 0;
 #define BLB_CASE(a, b)                                                                                     \
   if (ak == a && bk == b) {                                                                                \
     if constexpr (std::is_same<T, double>::value) {                                                        \
@@ -297,6 +335,18 @@ int launch_cw(const GemmParams& p, int stages, int slot_bytes, bool hc, cudaStre
   return BLB200_E_INTERNAL;
 }
 
+// double, 4 x 4 tiles, four warp pairs
+int launch_dmma_pairs(const GemmParams& p, int stages, int slot_bytes, bool hc, cudaStream_t stream) {
+  const bool ak = p.op_a != BLB200_N, bk = p.op_b == BLB200_N;
+#define BLB_CASE(a, b)                                                                                      \
+  if (ak == a && bk == b)                                                                                   \
+    return hc ? launch_one<double, 8, a, b, true, 4, 4, true, true>(p, stages, slot_bytes, stream)          \
+              : launch_one<double, 8, a, b, false, 4, 4, true, true>(p, stages, slot_bytes, stream);
+  BLB_CASE(false, false) BLB_CASE(false, true) BLB_CASE(true, false) BLB_CASE(true, true)
+#undef BLB_CASE
+  return BLB200_E_INTERNAL;
+}
+
 template <typename T>
 int launch_typed(const GemmParams& p, cudaStream_t stream) {
   const bool hc = !(p.beta[0] == 0.0 && p.beta[1] == 0.0);
@@ -313,6 +363,14 @@ int launch_typed(const GemmParams& p, cudaStream_t stream) {
     // measured faster than eight warps with one (32^3: 4.0 against 3.9, beta = 0: 3.9 against 2.8 TB/s).
     static const int dmma_cw = [] { const char* v = getenv("BLB200_SMALL_RING_DMMA_CW"); return v && *v ? atoi(v) : 8; }();
     const bool tiles4 = (p.m > 16 || p.n > 16) && p.m % 8 == 0 && p.n % 8 == 0 && p.k % 4 == 0;
+    // warp pairs on slots that always carry a C area
+    // (measured slower than one warp per item: 32^3 3.8 against 4.0 TB/s; kept as an opt-in)
+    static const bool pairs_on = [] { const char* v = getenv("BLB200_SMALL_RING_DMMA_PAIRS"); return v && *v == '1'; }();
+    if (tiles4 && pairs_on && dmma_enabled()) {
+      const int slot_pair = (p.m * p.k + p.k * p.n + p.m * p.n) * (int)sizeof(T);
+      const int fit_pair = (int)(budget / (size_t)slot_pair);
+      if (fit_pair >= 8) return launch_dmma_pairs(p, (fit_pair >= 32 ? 32 : fit_pair) / 4 * 4, slot_pair, hc, stream);
+    }
     if (tiles4 && dmma_cw == 8 && fit >= 16) return launch_cw<T, 8>(p, (fit >= 32 ? 32 : fit) / 8 * 8, slot_bytes, hc, stream);
   }
   // 16 warps with two slots each when that fits, else with one
