@@ -127,7 +127,7 @@ template <int CW, bool A_KMAJOR, bool B_KMAJOR, bool HAS_C, bool TRANS_OUT = fal
 __global__ void __launch_bounds__(32 * (1 + CW), 1)
     gemm_small32_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
                         long long sa, long long sb, long long sc, int batch, float alpha, float beta,
-                        int stages) {
+                        int stages, int self_feed) {
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int kStageBytes = (HAS_C ? 3 : 2) * kMatBytes32;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)stages * kStageBytes);
@@ -146,17 +146,28 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
   // Items of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...; the j-th one uses stage j % stages.
   const int my_items = (batch > (int)blockIdx.x) ? (batch - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
+  // self_feed: no producer warp.  Lane 0 of the warp that owns a stage issues the copies of the
+  // item that uses the stage next as soon as the warp has read its fragments: the refill starts
+  // without a hand-over through an "empty" barrier that the producer's lane has to notice (the
+  // producer's lanes wait in one diverged warp, and a lane that sits in a blocking barrier wait
+  // holds the others up).
+  auto issue = [&](int stage, int jj) {
+    unsigned char* st = smem + (size_t)stage * kStageBytes;
+    const long long it = (long long)blockIdx.x + (long long)jj * gridDim.x;
+    mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+    bulk_g2s(st, A + it * sa, kMatBytes32, &full_bar[stage]);
+    bulk_g2s(st + kMatBytes32, B + it * sb, kMatBytes32, &full_bar[stage]);
+    if (HAS_C) bulk_g2s(st + 2 * kMatBytes32, C + it * sc, kMatBytes32, &full_bar[stage]);
+  };
+  const bool feed = self_feed != 0;
+
   if (warp == 0) {
+    if (feed) return;
     if (lane < stages) {  // lane == stage
-      unsigned char* st = smem + (size_t)lane * kStageBytes;
       uint32_t round = 0;
       for (int j = lane; j < my_items; j += stages, ++round) {
         if (!mbar_wait(&empty_bar[lane], (round & 1u) ^ 1u, kWaitEmpty)) return;
-        const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
-        mbar_arrive_expect_tx(&full_bar[lane], kStageBytes);
-        bulk_g2s(st, A + item * sa, kMatBytes32, &full_bar[lane]);
-        bulk_g2s(st + kMatBytes32, B + item * sb, kMatBytes32, &full_bar[lane]);
-        if (HAS_C) bulk_g2s(st + 2 * kMatBytes32, C + item * sc, kMatBytes32, &full_bar[lane]);
+        issue(lane, j);
       }
     }
     return;
@@ -164,6 +175,8 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
 
   const int cw = warp - 1;
   const int ti = lane & 7, tj = lane >> 3;
+  if (feed && lane == 0)
+    for (int stage = cw; stage < stages && stage < my_items; stage += CW) issue(stage, stage);
   int s = cw;          // stage of this warp's current item: (cw + CW*i) % stages
   uint32_t round = 0;  // how many times this warp has been through stage `s` before
   for (int j = cw; j < my_items; j += CW) {
@@ -187,7 +200,14 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
         prior[c] = TRANS_OUT ? Cs4[(4 * ti + (c >> 1)) * 8 + 2 * tj + (c & 1)] : Cs4[(8 * tj + c) * 8 + ti];
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(&empty_bar[s]);  // the slot may be refilled while we store
+    if (lane == 0) {  // the slot is refilled while we store
+      if (!feed) {
+        mbar_arrive(&empty_bar[s]);
+      } else if (j + stages < my_items) {
+        fence_async_smem();
+        issue(s, j + stages);
+      }
+    }
 
     const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
     float4* Cg4 = reinterpret_cast<float4*>(C + item * sc);
@@ -257,8 +277,9 @@ int launch32(const GemmParams& p, cudaStream_t stream) {
     configured_for = cur;
   }
   const int grid = p.batch < dev.sm_count ? p.batch : dev.sm_count;
+  static const int self_feed = env_int("BLB200_SMALL32_SELF_FEED", 1);  // 0: producer warp + empty barriers
   kern<<<grid, 32 * (1 + CW), smem, stream>>>((const float*)p.a, (const float*)p.b, (float*)p.c, p.sa, p.sb,
-                                           p.sc, p.batch, (float)p.alpha[0], (float)p.beta[0], stages);
+                                           p.sc, p.batch, (float)p.alpha[0], (float)p.beta[0], stages, self_feed);
   return (int)cudaGetLastError();
 }
 
