@@ -4,7 +4,8 @@
 // the producer: each of its lanes owns one ring slot and, independently of the other lanes, waits
 // for that slot's "empty" mbarrier and issues the slot's TMA copies (a single thread doing this
 // for every slot is latency-bound at about 4 KiB per 250 ns per SM, well under HBM speed).  The
-// other warps are consumers.  Every slot is consumed by the same warp (or warp pair) in every
+// other warps are consumers.  (small32 by default runs without the producer: the consumer warp
+// that owns a stage refills it itself, see `self_feed` in its kernel.)  Every slot is consumed by the same warp (or warp pair) in every
 // round — a consumer therefore never waits for round r of a slot before round r-1 has completed,
 // which is what makes the one-bit mbarrier phase parity sufficient.
 //
