@@ -13,9 +13,9 @@ LIB_PATH = os.path.join(_HERE, "libbatchlas_b200.so")
 
 S, D, C, Z = 0, 1, 2, 3
 OP_N, OP_T, OP_H = 0, 1, 2
-K_AUTO, K_GENERIC, K_SMALL32, K_SMALL64, K_TILED, K_DMMA, K_SGEMM128 = 0, 1, 2, 3, 4, 5, 6
+K_AUTO, K_GENERIC, K_SMALL32, K_SMALL64, K_TILED, K_DMMA, K_SGEMM128, K_SMALL_RING = 0, 1, 2, 3, 4, 5, 6, 7
 KERNEL_IDS = {"auto": K_AUTO, "generic": K_GENERIC, "small32": K_SMALL32, "small64": K_SMALL64,
-              "tiled": K_TILED, "dmma": K_DMMA, "sgemm128": K_SGEMM128}
+              "tiled": K_TILED, "dmma": K_DMMA, "sgemm128": K_SGEMM128, "small_ring": K_SMALL_RING}
 
 E_NULL, E_SHAPE, E_DTYPE, E_UNSUPPORTED, E_NO_DEVICE, E_TOO_LARGE, E_INTERNAL = -1, -2, -3, -4, -5, -6, -7
 
@@ -91,6 +91,8 @@ SIGNATURES = {
     "blb200_version": (ctypes.c_char_p, []),
     "blb200_trace_flush": (ctypes.c_int, []),
     "blb200_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
+    "blb200_device_status_reset": (ctypes.c_int, []),
+    "blb200_selftest_wait_expiry": (ctypes.c_int, [ctypes.c_uint32, ctypes.c_void_p]),
     "blb200_arena_create": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p)]),
     "blb200_arena_destroy": (ctypes.c_int, [ctypes.c_void_p]),
     "blb200_arena_acquire": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(Lease)]),

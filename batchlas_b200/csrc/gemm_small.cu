@@ -1,13 +1,15 @@
 // Whole-matrix-per-warp kernels for packed small float matrices: the HBM-bound end of the family.
 //
-// Shared structure.  A persistent grid of one CTA per SM walks the batch round-robin.  Warp 0 is
-// the producer: each of its lanes owns one ring slot and, independently of the other lanes, waits
-// for that slot's "empty" mbarrier and issues the slot's TMA copies (a single thread doing this
-// for every slot is latency-bound at about 4 KiB per 250 ns per SM, well under HBM speed).  The
-// other warps are consumers.  (small32 by default runs without the producer: the consumer warp
-// that owns a stage refills it itself, see `self_feed` in its kernel.)  Every slot is consumed by the same warp (or warp pair) in every
-// round — a consumer therefore never waits for round r of a slot before round r-1 has completed,
-// which is what makes the one-bit mbarrier phase parity sufficient.
+// Shared structure.  A persistent grid of one CTA per SM walks the batch round-robin through a ring
+// of shared-memory slots filled by TMA copies that complete on one "full" mbarrier per slot.  There
+// is no producer warp and no "empty" barrier: a slot belongs to one warp (small32) or one warp pair
+// (small64) for the whole launch, and the owner itself issues the copies of the item that uses the
+// slot next, the moment it has read the slot.  (One thread issuing every copy of an SM is latency
+// bound at about 4 KiB per 250 ns, well under HBM speed; a producer warp with one lane per slot
+// removes that cap but its lanes wait in one diverged warp, and a lane parked in a blocking barrier
+// wait delays the other slots' refills.)  Because a slot always has the same owner, a consumer
+// never waits for round r of a slot before round r-1 has completed, which is what makes the one-bit
+// mbarrier phase parity sufficient.
 //
 // small32: m = n = k = 32, ld = 32 on all three operands, 16-byte aligned bases, strides multiples
 // of 4 elements (BatchLAS gates its own vector fast paths the same way:
@@ -22,10 +24,10 @@
 // the lanes of one request fall into different 16-byte bank groups; the sum over k is the same
 // set of products in a different order.
 //
-// small64: m = n = k = 64, ld = 64, same alignment rules.  Two consumer warps share one matrix
+// small64: m = n = k = 64, ld = 64, same alignment rules.  Two warps share one matrix
 // (warp half hw owns columns 32hw..32hw+31, each lane an 8 x 8 block: 16 fragment floats per 64
 // FMAs, so the FP32 pipe rather than shared memory sets the pace).  The ring holds half-K slots of
-// 16 KiB (A half + B half); each of the 4 pairs owns 3 slots.  An M-major / N-major half is one
+// 16 KiB (A half + B half); each of the 4 pairs owns 3 slots (6 pairs: 2 slots).  An M-major / N-major half is one
 // contiguous 8 KiB run (untiled bulk copy).  A K-major half is 64 rows of 128 bytes, 256 bytes
 // apart in memory: it is fetched by one tiled TMA copy (cp.async.bulk.tensor.3d, box 32 x 64 x 1)
 // with the 128-byte swizzle, which XORs the 16-byte chunk index with (row & 7); with rows (or
@@ -42,7 +44,7 @@
 namespace blb200 {
 namespace {
 
-enum WaitCode { kWaitFull = 101, kWaitEmpty = 102 };
+enum WaitCode { kWaitFull = 101 };
 
 inline bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
 
@@ -119,27 +121,26 @@ __device__ __forceinline__ void mma32(const float4* __restrict__ As4, const floa
   }
 }
 
-// Shared memory: `stages` x {A, B[, C]} of 4 KiB each, then full[stages], empty[stages] barriers.
-// `stages` is a multiple of the consumer warp count CW and at most 32 (one producer lane per stage).
+// Shared memory: `stages` x {A, B[, C]} of 4 KiB each, then full[stages] barriers.
+// `stages` is a multiple of the warp count CW; stage s belongs to warp s % CW for the whole launch.
+// There is no producer warp: lane 0 of the warp that owns a stage issues the copies of the item
+// that uses the stage next as soon as the warp has read its fragments, so a refill never waits for
+// a hand-over that another warp has to notice.
 // TRANS_OUT: the lane's 4 x 8 block is a block of C^T (used for op pair TT, which is computed as
 // C^T = B_stored * A_stored with the operands swapped by the launcher, i.e. through the NN fragment
 // path); the epilogue then writes row 8tj..8tj+7 of column 4ti+r as two float4.
 template <int CW, bool A_KMAJOR, bool B_KMAJOR, bool HAS_C, bool TRANS_OUT = false>
-__global__ void __launch_bounds__(32 * (1 + CW), 1)
+__global__ void __launch_bounds__(32 * CW, 1)
     gemm_small32_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
                         long long sa, long long sb, long long sc, int batch, float alpha, float beta,
-                        int stages, int self_feed) {
+                        int stages) {
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int kStageBytes = (HAS_C ? 3 : 2) * kMatBytes32;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)stages * kStageBytes);
-  uint64_t* empty_bar = full_bar + stages;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
-    }
+    for (int s = 0; s < stages; ++s) mbar_init(&full_bar[s], 1);
     mbar_fence_init();
   }
   __syncthreads();
@@ -147,11 +148,6 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
   // Items of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...; the j-th one uses stage j % stages.
   const int my_items = (batch > (int)blockIdx.x) ? (batch - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
-  // self_feed: no producer warp.  Lane 0 of the warp that owns a stage issues the copies of the
-  // item that uses the stage next as soon as the warp has read its fragments: the refill starts
-  // without a hand-over through an "empty" barrier that the producer's lane has to notice (the
-  // producer's lanes wait in one diverged warp, and a lane that sits in a blocking barrier wait
-  // holds the others up).
   auto issue = [&](int stage, int jj) {
     unsigned char* st = smem + (size_t)stage * kStageBytes;
     const long long it = (long long)blockIdx.x + (long long)jj * gridDim.x;
@@ -160,23 +156,10 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
     bulk_g2s(st + kMatBytes32, B + it * sb, kMatBytes32, &full_bar[stage]);
     if (HAS_C) bulk_g2s(st + 2 * kMatBytes32, C + it * sc, kMatBytes32, &full_bar[stage]);
   };
-  const bool feed = self_feed != 0;
 
-  if (warp == 0) {
-    if (feed) return;
-    if (lane < stages) {  // lane == stage
-      uint32_t round = 0;
-      for (int j = lane; j < my_items; j += stages, ++round) {
-        if (!mbar_wait(&empty_bar[lane], (round & 1u) ^ 1u, kWaitEmpty)) return;
-        issue(lane, j);
-      }
-    }
-    return;
-  }
-
-  const int cw = warp - 1;
+  const int cw = warp;
   const int ti = lane & 7, tj = lane >> 3;
-  if (feed && lane == 0)
+  if (lane == 0)
     for (int stage = cw; stage < stages && stage < my_items; stage += CW) issue(stage, stage);
   int s = cw;          // stage of this warp's current item: (cw + CW*i) % stages
   uint32_t round = 0;  // how many times this warp has been through stage `s` before
@@ -201,13 +184,9 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
         prior[c] = TRANS_OUT ? Cs4[(4 * ti + (c >> 1)) * 8 + 2 * tj + (c & 1)] : Cs4[(8 * tj + c) * 8 + ti];
     }
     __syncwarp();
-    if (lane == 0) {  // the slot is refilled while we store
-      if (!feed) {
-        mbar_arrive(&empty_bar[s]);
-      } else if (j + stages < my_items) {
-        fence_async_smem();
-        issue(s, j + stages);
-      }
+    if (lane == 0 && j + stages < my_items) {  // the stage is refilled while we store
+      fence_async_smem();
+      issue(s, j + stages);
     }
 
     const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
@@ -260,27 +239,21 @@ template <int CW, bool AK, bool BK, bool HC, bool TRANS_OUT = false>
 int launch32(const GemmParams& p, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
   constexpr int kStageBytes = (HC ? 3 : 2) * kMatBytes32;
-  const size_t budget = dev.smem_optin > 8192 ? dev.smem_optin - 4096 : 0;
-  static const int want = env_int("BLB200_SMALL32_STAGES", 16);  // tuning knob; rounded to a legal value
-  int stages = (int)(budget / ((size_t)kStageBytes * CW)) * CW;
-  if (stages > 32) stages = 32 / CW * CW;
-  if (want >= CW && want < stages) stages = want / CW * CW;
-  if (stages < CW) return BLB200_E_UNSUPPORTED;
-  const size_t smem = (size_t)stages * kStageBytes + (size_t)stages * 2 * sizeof(uint64_t);
+  constexpr int stages = CW;  // one stage per warp: 16 x 12 KiB in flight per SM
+  const size_t smem = (size_t)stages * kStageBytes + (size_t)stages * sizeof(uint64_t);
+  if (dev.smem_optin < smem) return BLB200_E_UNSUPPORTED;
   auto kern = gemm_small32_kernel<CW, AK, BK, HC, TRANS_OUT>;
   static thread_local int configured_for = -1;  // per (instantiation, thread): device last configured
   int cur = 0;
   cudaGetDevice(&cur);
   if (configured_for != cur) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)(budget < smem ? smem : budget));
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured_for = cur;
   }
   const int grid = p.batch < dev.sm_count ? p.batch : dev.sm_count;
-  static const int self_feed = env_int("BLB200_SMALL32_SELF_FEED", 1);  // 0: producer warp + empty barriers
-  kern<<<grid, 32 * (1 + CW), smem, stream>>>((const float*)p.a, (const float*)p.b, (float*)p.c, p.sa, p.sb,
-                                           p.sc, p.batch, (float)p.alpha[0], (float)p.beta[0], stages, self_feed);
+  kern<<<grid, 32 * CW, smem, stream>>>((const float*)p.a, (const float*)p.b, (float*)p.c, p.sa, p.sb, p.sc, p.batch,
+                                     (float)p.alpha[0], (float)p.beta[0], stages);
   return (int)cudaGetLastError();
 }
 
@@ -434,10 +407,21 @@ __device__ __forceinline__ void tma_load_3d(void* dst_smem, const CUtensorMap* m
       : "memory");
 }
 
-// Pair p's q-th half-item lives in slot p*3 + q % 3 (round q / 3); half-item q is half q & 1 of
-// the pair's (q >> 1)-th item.  Producer lane l < 12 owns slot l.
+// Release-acquire counter bump in shared memory: whoever reads an odd old value knows that the
+// other warp of its pair has finished reading the slot as well.
+__device__ __forceinline__ uint32_t smem_add_acq_rel(uint32_t* p, uint32_t v) {
+  uint32_t old;
+  asm volatile("atom.acq_rel.cta.shared.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(smem_u32(p)), "r"(v) : "memory");
+  return old;
+}
+
+// Pair p's q-th half-item lives in slot p * SPP + q % SPP (round q / SPP; SPP = slots per pair);
+// half-item q is half q & 1 of the pair's (q >> 1)-th item.  There is no producer warp: the two
+// warps of a pair count themselves off a slot, and the one that leaves it last issues the copies of
+// the half-item that uses the slot next — the refill starts the moment the slot is free, with no
+// hand-over that a third warp has to notice.
 template <int PAIRS, bool A_KMAJOR, bool B_KMAJOR, bool HAS_C>
-__global__ void __launch_bounds__(32 * (1 + 2 * PAIRS), 1)
+__global__ void __launch_bounds__(64 * PAIRS, 1)
     gemm_small64_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
                         long long sa, long long sb, long long sc, int batch, float alpha, float beta,
                         const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b) {
@@ -447,13 +431,13 @@ __global__ void __launch_bounds__(32 * (1 + 2 * PAIRS), 1)
   // the 128-byte swizzle is a function of the shared-memory address: slots must be 1024-byte aligned
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)kSlots64 * kSlotBytes64);
-  uint64_t* empty_bar = full_bar + kSlots64;
+  uint32_t* left = reinterpret_cast<uint32_t*>(full_bar + kSlots64);  // per slot: warps that have left it, ever
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSlots64; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 2);  // one arrival per warp of the pair
+      left[s] = 0u;
     }
     mbar_fence_init();
   }
@@ -462,37 +446,34 @@ __global__ void __launch_bounds__(32 * (1 + 2 * PAIRS), 1)
   const int my_items = (batch > (int)blockIdx.x) ? (batch - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
   // Programmatic dependent launch: let the next kernel in the stream place its CTAs on SMs as this
-  // grid drains (its barrier set-up then overlaps our tail), and do not touch global memory until
-  // every earlier grid in the stream has finished.  Only the producer lanes need the second half:
-  // consumers see memory only through data those lanes fetched afterwards.
+  // grid drains (its barrier set-up then overlaps our tail); no thread touches global memory
+  // (operand copies, the old C, the C stores) before every earlier grid in the stream has finished.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  if (warp == 0) {
-    if (lane < kSlots64) {
-      asm volatile("griddepcontrol.wait;" ::: "memory");
-      const int pair = lane / kSlotsPerPair64, i = lane % kSlotsPerPair64;
-      // items of this pair: pair, pair + 4, ...
-      const int pair_items = (my_items > pair) ? (my_items - 1 - pair) / kPairs64 + 1 : 0;
-      unsigned char* st = smem + (size_t)lane * kSlotBytes64;
-      uint32_t round = 0;
-      for (int q = i; q < 2 * pair_items; q += kSlotsPerPair64, ++round) {
-        if (!mbar_wait(&empty_bar[lane], (round & 1u) ^ 1u, kWaitEmpty)) return;
-        const int j = pair + (q >> 1) * kPairs64, half = q & 1;
-        const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
-        mbar_arrive_expect_tx(&full_bar[lane], kSlotBytes64);
-        if (A_KMAJOR) tma_load_3d(st, &map_a, 32 * half, 0, (int)item, &full_bar[lane]);
-        else bulk_g2s(st, A + item * sa + half * (kMatElems64 / 2), kHalfBytes64, &full_bar[lane]);
-        if (B_KMAJOR) tma_load_3d(st + kHalfBytes64, &map_b, 32 * half, 0, (int)item, &full_bar[lane]);
-        else bulk_g2s(st + kHalfBytes64, B + item * sb + half * (kMatElems64 / 2), kHalfBytes64, &full_bar[lane]);
-      }
-    }
-    return;
-  }
-
-  const int pair = (warp - 1) >> 1, hw = (warp - 1) & 1;
+  const int pair = warp >> 1, hw = warp & 1;
   const int ti = lane & 7, tj = lane >> 3;
-  int slot_i = 0;      // q % 3
-  uint32_t round = 0;  // q / 3
+  // items of this pair: pair, pair + PAIRS, ...
+  const int pair_items = (my_items > pair) ? (my_items - 1 - pair) / kPairs64 + 1 : 0;
+  const int pair_halves = 2 * pair_items;
+
+  auto issue = [&](int q, int slot_of_pair) {
+    const int s = pair * kSlotsPerPair64 + slot_of_pair;
+    unsigned char* st = smem + (size_t)s * kSlotBytes64;
+    const int j = pair + (q >> 1) * kPairs64, half = q & 1;
+    const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
+    mbar_arrive_expect_tx(&full_bar[s], kSlotBytes64);
+    if (A_KMAJOR) tma_load_3d(st, &map_a, 32 * half, 0, (int)item, &full_bar[s]);
+    else bulk_g2s(st, A + item * sa + half * (kMatElems64 / 2), kHalfBytes64, &full_bar[s]);
+    if (B_KMAJOR) tma_load_3d(st + kHalfBytes64, &map_b, 32 * half, 0, (int)item, &full_bar[s]);
+    else bulk_g2s(st + kHalfBytes64, B + item * sb + half * (kMatElems64 / 2), kHalfBytes64, &full_bar[s]);
+  };
+  if (hw == 0 && lane == 0)
+    for (int q = 0; q < kSlotsPerPair64 && q < pair_halves; ++q) issue(q, q);
+
+  int slot_i = 0;      // q % SPP
+  uint32_t round = 0;  // q / SPP
+  int q = 0;
   for (int j = pair; j < my_items; j += kPairs64) {
     constexpr PackMode PM = pack_mode<A_KMAJOR, B_KMAJOR>();
     float acc[8][8];
@@ -504,13 +485,19 @@ __global__ void __launch_bounds__(32 * (1 + 2 * PAIRS), 1)
 #pragma unroll
     for (int i = 0; i < 32; ++i) accp[i] = 0ull;
 #pragma unroll 1
-    for (int half = 0; half < 2; ++half) {
+    for (int half = 0; half < 2; ++half, ++q) {
       const int s = pair * kSlotsPerPair64 + slot_i;
       if (!mbar_wait(&full_bar[s], round & 1u, kWaitFull)) return;
       const unsigned char* st = smem + (size_t)s * kSlotBytes64;
       mma64_half<A_KMAJOR, B_KMAJOR>(st, st + kHalfBytes64, ti, tj, hw, acc, accp);
       __syncwarp();
-      if (lane == 0) mbar_arrive(&empty_bar[s]);
+      if (lane == 0) {
+        const uint32_t before = smem_add_acq_rel(&left[s], 1u);
+        if ((before & 1u) && q + kSlotsPerPair64 < pair_halves) {  // the pair's other warp left earlier
+          fence_async_smem();
+          issue(q + kSlotsPerPair64, slot_i);
+        }
+      }
       if (++slot_i == kSlotsPerPair64) {
         slot_i = 0;
         ++round;
@@ -603,20 +590,54 @@ int make_kmajor_map64(CUtensorMap* map, const float* base, long long stride_elem
   return r == CUDA_SUCCESS ? BLB200_OK : BLB200_E_INTERNAL;
 }
 
+// Tensor maps are pure functions of (base, item stride, batch): a small per-thread cache saves the
+// driver call on repeated launches over the same operand (a solver loop, a benchmark).
+struct MapCache64 {
+  struct Entry {
+    const void* base = nullptr;
+    long long stride = 0;
+    int batch = 0;
+    bool valid = false;
+    alignas(64) CUtensorMap map;
+  };
+  static constexpr int kEntries = 8;
+  Entry e[kEntries];
+  int next = 0;
+  int get(CUtensorMap* out, const float* base, long long stride, int batch) {
+    for (int i = 0; i < kEntries; ++i)
+      if (e[i].valid && e[i].base == base && e[i].stride == stride && e[i].batch == batch) {
+        memcpy(out, &e[i].map, sizeof(CUtensorMap));
+        return BLB200_OK;
+      }
+    Entry& slot = e[next];
+    next = (next + 1) % kEntries;
+    slot.valid = false;
+    const int rc = make_kmajor_map64(&slot.map, base, stride, batch);
+    if (rc != BLB200_OK) return rc;
+    slot.base = base;
+    slot.stride = stride;
+    slot.batch = batch;
+    slot.valid = true;
+    memcpy(out, &slot.map, sizeof(CUtensorMap));
+    return BLB200_OK;
+  }
+};
+
 template <int PAIRS, bool AK, bool BK, bool HC>
 int launch64(const GemmParams& p, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
-  const size_t smem = (size_t)kSlots64 * kSlotBytes64 + (size_t)kSlots64 * 2 * sizeof(uint64_t) + 1024;
+  const size_t smem = (size_t)kSlots64 * kSlotBytes64 + (size_t)kSlots64 * (sizeof(uint64_t) + sizeof(uint32_t)) + 1024;
   if (dev.smem_optin < smem) return BLB200_E_UNSUPPORTED;
   alignas(64) CUtensorMap map_a, map_b;
   memset(&map_a, 0, sizeof(map_a));
   memset(&map_b, 0, sizeof(map_b));
+  static thread_local MapCache64 maps;
   if (AK) {
-    int rc = make_kmajor_map64(&map_a, (const float*)p.a, p.batch > 1 ? p.sa : kMatElems64, p.batch);
+    int rc = maps.get(&map_a, (const float*)p.a, p.batch > 1 ? p.sa : kMatElems64, p.batch);
     if (rc != BLB200_OK) return rc;
   }
   if (BK) {
-    int rc = make_kmajor_map64(&map_b, (const float*)p.b, p.batch > 1 ? p.sb : kMatElems64, p.batch);
+    int rc = maps.get(&map_b, (const float*)p.b, p.batch > 1 ? p.sb : kMatElems64, p.batch);
     if (rc != BLB200_OK) return rc;
   }
   auto kern = gemm_small64_kernel<PAIRS, AK, BK, HC>;
@@ -629,17 +650,16 @@ int launch64(const GemmParams& p, cudaStream_t stream) {
     configured_for = cur;
   }
   const int grid = p.batch < dev.sm_count ? p.batch : dev.sm_count;
-  static const int use_pdl = env_int("BLB200_PDL", 1);  // 0 switches programmatic dependent launch off
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3(32 * (1 + 2 * PAIRS));
+  cfg.blockDim = dim3(64 * PAIRS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = use_pdl ? 1 : 0;
+  cfg.numAttrs = 1;
   return (int)cudaLaunchKernelEx(&cfg, kern, (const float*)p.a, (const float*)p.b, (float*)p.c, (long long)p.sa,
                                  (long long)p.sb, (long long)p.sc, p.batch, (float)p.alpha[0], (float)p.beta[0], map_a,
                                  map_b);
@@ -662,7 +682,6 @@ int launch_small32(const GemmParams& p, int dtype, cudaStream_t stream) {
   const bool ak = p.op_a != BLB200_N;  // op T stores A as k x m: k runs fastest
   const bool bk = p.op_b == BLB200_N;  // op N stores B as k x n: k runs fastest
   const bool hc = (float)p.beta[0] != 0.f;
-  static const int cw = env_int("BLB200_SMALL32_WARPS", 16);  // tuning knob: 8, 12 or 16 consumer warps
   int rc;
   if (ak && !bk) {
     // TT: C^T = B_stored * A_stored.  B (n x k, column-major) plays the M-major left operand, A (k x m)
@@ -670,18 +689,12 @@ int launch_small32(const GemmParams& p, int dtype, cudaStream_t stream) {
     GemmParams q = p;
     q.a = p.b; q.b = p.a;
     q.sa = p.sb; q.sb = p.sa;
-    if (cw == 8) rc = hc ? launch32<8, false, true, true, true>(q, stream) : launch32<8, false, true, false, true>(q, stream);
-    else if (cw == 12) rc = hc ? launch32<12, false, true, true, true>(q, stream) : launch32<12, false, true, false, true>(q, stream);
-    else rc = hc ? launch32<16, false, true, true, true>(q, stream) : launch32<16, false, true, false, true>(q, stream);
+    rc = hc ? launch32<16, false, true, true, true>(q, stream) : launch32<16, false, true, false, true>(q, stream);
     if (rc == BLB200_OK) note_launch("small32");
     return rc;
   }
-#define BLB_CASE(a, b)                                                                            \
-  if (ak == a && bk == b) {                                                                       \
-    if (cw == 16) rc = hc ? launch32<16, a, b, true>(p, stream) : launch32<16, a, b, false>(p, stream); \
-    else if (cw == 12) rc = hc ? launch32<12, a, b, true>(p, stream) : launch32<12, a, b, false>(p, stream); \
-    else rc = hc ? launch32<8, a, b, true>(p, stream) : launch32<8, a, b, false>(p, stream);      \
-  } else
+#define BLB_CASE(a, b) \
+  if (ak == a && bk == b) rc = hc ? launch32<16, a, b, true>(p, stream) : launch32<16, a, b, false>(p, stream); else
   BLB_CASE(false, false) BLB_CASE(false, true) BLB_CASE(true, false) BLB_CASE(true, true) { rc = BLB200_E_INTERNAL; }
 #undef BLB_CASE
   if (rc == BLB200_OK) note_launch("small32");
@@ -719,5 +732,6 @@ int launch_small64(const GemmParams& p, int dtype, cudaStream_t stream) {
 }
 
 int small_device_status(int* out) { return read_device_status_word(out); }
+int small_device_status_clear() { return clear_device_status_word(); }
 
 }  // namespace blb200

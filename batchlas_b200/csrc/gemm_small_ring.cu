@@ -1,10 +1,13 @@
 // Whole-matrix-per-warp gemm for large batches of small packed matrices of ANY of the four element
 // types and any shape up to 32 x 32 (k up to 64): the general sibling of the float-only 32^3 / 64^3
 // kernels.  Such problems are HBM-bound (a 32 x 32 x 32 double item moves 32 KiB for 64 Kflop), so the
-// whole design is about streaming: one producer warp keeps a shared-memory ring full with untiled TMA
-// bulk copies of whole A, B (and C when beta != 0) items — one producer lane per slot, full / empty
-// mbarriers — and each consumer warp multiplies one item out of its slot.  Nothing but long
-// sequential reads and the C stores reaches HBM.
+// whole design is about streaming: a shared-memory ring is kept full with untiled TMA bulk copies
+// of whole A, B (and C when beta != 0) items, one "full" mbarrier per slot, and each warp multiplies
+// one item out of its slot.  A slot belongs to one warp for the whole launch; lane 0 of that warp
+// issues the copies of the item that uses the slot next as soon as the bulk store of the result has
+// read the slot (no producer warp, no "empty" barrier: a producer lane parked in a blocking barrier
+// wait held up its warp's other lanes and every refill started late — double 32^3 4.0 -> 6.4 TB/s,
+// float 16^3 2.6 -> 5.3).  Nothing but long sequential reads and the C stores reaches HBM.
 //
 // A lane owns rows ti + 8r and columns tj + 4c (ti = lane & 7, tj = lane >> 3; up to 4 x 8 outputs), so
 // that an M-major A or an N-major B is read by consecutive lanes at consecutive addresses.  A K-major
@@ -15,7 +18,7 @@
 // Preconditions (small_ring_supported): packed operands (ld == stored rows), item sizes multiples of
 // 16 bytes, item starts on 16-byte boundaries, m, n <= 32 (complex<double>: 16), k <= 64, one slot at
 // most 27 KiB, a batch large enough to keep a ring per SM busy.  Ring discipline as in the other ring kernels: the slot
-// count is a multiple of the consumer count, slot s always belongs to consumer s % CW, and every wait
+// count is a multiple of the warp count, slot s always belongs to warp s % CW, and every wait
 // is bounded (on expiry the waiter records a code in the device status word and returns).
 #include <stdlib.h>
 
@@ -27,7 +30,7 @@
 namespace blb200 {
 namespace {
 
-enum WaitCode { kSmallRingWaitFull = 301, kSmallRingWaitEmpty = 302 };
+enum WaitCode { kSmallRingWaitFull = 301 };
 constexpr int kMaxMN = 32, kMaxK = 64, kMaxSlotBytes = 27648;
 
 template <typename T>
@@ -50,29 +53,19 @@ __device__ __forceinline__ void dmma884(double& c0, double& c1, double a, double
 // feeds A(8rb + g, k0 + q) and B(k0 + q, 8cb + g) and receives C(8rb + g, 8cb + 2q), C(.., 8cb + 2q + 1):
 // two fragment doubles per lane for sixteen tile products per k-step of 4, where the scalar loop
 // reads twelve per 32 multiply-adds and is bound by the latency of those reads.
-// PAIR (DMMA only): two consumer warps share every item, warp half h taking the column tiles
-// CB/2 * h ... (one warp alone issues DMMAs at about half the pipe's rate, and eight warps with a
-// slot each leave nothing in flight while they work).  Each half assembles and stores its own
-// columns of C — the slot then always has a C area, so nothing is written over A while the other
-// half still reads it — and a slot is handed back by two arrivals.
-template <typename T, int CW, bool A_KMAJOR, bool B_KMAJOR, bool HAS_C, int RB, int CB, bool DMMA = false,
-          bool PAIR = false>
-__global__ void __launch_bounds__(32 * (1 + CW), 1)
+template <typename T, int CW, bool A_KMAJOR, bool B_KMAJOR, bool HAS_C, int RB, int CB, bool DMMA = false>
+__global__ void __launch_bounds__(32 * CW, 1)
     gemm_small_ring_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C, int m, int n, int k,
                            long long sa, long long sb, long long sc, int batch, T alpha, T beta, bool conj_a, bool conj_b,
-                           int stages, int slot_bytes, int self_feed) {
+                           int stages, int slot_bytes) {
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)stages * slot_bytes);
-  uint64_t* empty_bar = full_bar + stages;
   const uint32_t a_bytes = (uint32_t)(m * k * (int)sizeof(T)), b_bytes = (uint32_t)(k * n * (int)sizeof(T)),
                  c_bytes = (uint32_t)(m * n * (int)sizeof(T));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], PAIR ? 2 : 1);
-    }
+    for (int s = 0; s < stages; ++s) mbar_init(&full_bar[s], 1);
     mbar_fence_init();
   }
   __syncthreads();
@@ -80,9 +73,6 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
   // Items of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...; the j-th one uses slot j % stages.
   const int my_items = (batch > (int)blockIdx.x) ? (batch - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
-  // self_feed (not with PAIR): no producer warp.  Lane 0 of the warp that owns a slot issues the
-  // copies of the item that uses the slot next, as soon as the bulk store has read the slot: the
-  // refill starts without a hand-over through an "empty" barrier that another warp has to notice.
   auto issue = [&](int slot, int jj) {
     unsigned char* st = smem + (size_t)slot * slot_bytes;
     const long long it = (long long)blockIdx.x + (long long)jj * gridDim.x;
@@ -91,26 +81,7 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
     bulk_g2s(st + a_bytes, B + it * sb, b_bytes, &full_bar[slot]);
     if (HAS_C) bulk_g2s(st + a_bytes + b_bytes, C + it * sc, c_bytes, &full_bar[slot]);
   };
-  const bool feed = !PAIR && self_feed != 0;
-
-  if (warp == 0) {
-    if (feed) return;
-    if (lane < stages) {  // lane == slot
-      unsigned char* st = smem + (size_t)lane * slot_bytes;
-      uint32_t round = 0;
-      for (int j = lane; j < my_items; j += stages, ++round) {
-        if (!mbar_wait(&empty_bar[lane], (round & 1u) ^ 1u, kSmallRingWaitEmpty)) return;
-        const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
-        mbar_arrive_expect_tx(&full_bar[lane], a_bytes + b_bytes + (HAS_C ? c_bytes : 0u));
-        bulk_g2s(st, A + item * sa, a_bytes, &full_bar[lane]);
-        bulk_g2s(st + a_bytes, B + item * sb, b_bytes, &full_bar[lane]);
-        if (HAS_C) bulk_g2s(st + a_bytes + b_bytes, C + item * sc, c_bytes, &full_bar[lane]);
-      }
-    }
-    return;
-  }
-
-  const int cw = warp - 1;
+  const int cw = warp;
   const int ti = lane & 7, tj = lane >> 3;
   const int rmax = (m - ti + 7) >> 3;  // rows ti + 8r < m
   const int cmax = (n - tj + 3) >> 2;  // columns tj + 4c < n
@@ -118,13 +89,11 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
   int k0 = (A_KMAJOR && B_KMAJOR) ? ti + 8 * tj : (A_KMAJOR ? ti : (B_KMAJOR ? tj : 0));
   k0 = k0 % k;
 
-  constexpr int OWNERS = PAIR ? CW / 2 : CW;  // warps (or warp pairs) that own slots
-  const int owner = PAIR ? (cw >> 1) : cw;
-  if (feed && lane == 0)
+  if (lane == 0)
     for (int slot = cw; slot < stages && slot < my_items; slot += CW) issue(slot, slot);
-  int s = owner;
+  int s = cw;
   uint32_t round = 0;
-  for (int j = owner; j < my_items; j += OWNERS) {
+  for (int j = cw; j < my_items; j += CW) {
     const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
     if (!mbar_wait(&full_bar[s], round & 1u, kSmallRingWaitFull)) return;
     const T* As = reinterpret_cast<const T*>(smem + (size_t)s * slot_bytes);
@@ -132,8 +101,7 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
     const T* Cs = reinterpret_cast<const T*>(smem + (size_t)s * slot_bytes + a_bytes + b_bytes);
 
     if constexpr (DMMA) {
-      constexpr int CBW = PAIR ? CB / 2 : CB;    // column tiles of this warp
-      const int cb0 = PAIR ? CBW * (cw & 1) : 0;  // first one
+      constexpr int CBW = CB, cb0 = 0;  // column tiles of this warp, first one
       const int g = lane >> 2, q = lane & 3;
       const int mt = m >> 3, nt = n >> 3;
       double d0[RB][CBW], d1[RB][CBW];
@@ -169,7 +137,7 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
             if (rb < mt && cb0 + cb < nt) dmma884(d0[rb][cb], d1[rb][cb], av[rb], bv[cb]);
       }
       __syncwarp();
-      double* Os = const_cast<double*>((HAS_C || PAIR) ? Cs : As);
+      double* Os = const_cast<double*>(HAS_C ? Cs : As);
 #pragma unroll
       for (int cb = 0; cb < CBW; ++cb)
 #pragma unroll
@@ -195,8 +163,7 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
           bulk_commit();
           bulk_wait_read<0>();
         }
-        if (!feed) mbar_arrive(&empty_bar[s]);
-        else if (j + stages < my_items) issue(s, j + stages);
+        if (j + stages < my_items) issue(s, j + stages);
       }
     } else {
     T acc[RB][CB];
@@ -264,11 +231,10 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
       bulk_s2g(C + item * sc, Os, c_bytes);
       bulk_commit();
       bulk_wait_read<0>();
-      if (!feed) mbar_arrive(&empty_bar[s]);
-      else if (j + stages < my_items) issue(s, j + stages);
+      if (j + stages < my_items) issue(s, j + stages);
     }
     }  // scalar path
-    s += OWNERS;
+    s += CW;
     if (s >= stages) {
       s -= stages;
       ++round;
@@ -279,16 +245,11 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
 
 inline bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
 
-bool dmma_enabled() {
-  static const bool on = [] { const char* v = getenv("BLB200_SMALL_RING_DMMA"); return !(v && *v == '0'); }();
-  return on;
-}
-
-template <typename T, int CW, bool AK, bool BK, bool HC, int RB, int CB, bool DMMA = false, bool PAIR = false>
+template <typename T, int CW, bool AK, bool BK, bool HC, int RB, int CB, bool DMMA = false>
 int launch_one(const GemmParams& p, int stages, int slot_bytes, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
-  const size_t smem = (size_t)stages * slot_bytes + (size_t)stages * 2 * sizeof(uint64_t);
-  auto kern = gemm_small_ring_kernel<T, CW, AK, BK, HC, RB, CB, DMMA, PAIR>;
+  const size_t smem = (size_t)stages * slot_bytes + (size_t)stages * sizeof(uint64_t);
+  auto kern = gemm_small_ring_kernel<T, CW, AK, BK, HC, RB, CB, DMMA>;
   static thread_local int configured_for = -1;
   int cur = 0;
   cudaGetDevice(&cur);
@@ -298,11 +259,10 @@ int launch_one(const GemmParams& p, int stages, int slot_bytes, cudaStream_t str
     configured_for = cur;
   }
   const int grid = p.batch < dev.sm_count ? p.batch : dev.sm_count;
-  static const int self_feed = [] { const char* v = getenv("BLB200_SMALL_RING_SELF_FEED"); return v && *v ? atoi(v) : 1; }();
-  kern<<<grid, 32 * (1 + CW), smem, stream>>>((const T*)p.a, (const T*)p.b, (T*)p.c, p.m, p.n, p.k, p.sa, p.sb, p.sc,
+  kern<<<grid, 32 * CW, smem, stream>>>((const T*)p.a, (const T*)p.b, (T*)p.c, p.m, p.n, p.k, p.sa, p.sb, p.sc,
                                             p.batch, Scalar<T>::make(p.alpha[0], p.alpha[1]),
                                             Scalar<T>::make(p.beta[0], p.beta[1]), p.op_a == BLB200_H,
-                                            p.op_b == BLB200_H, stages, slot_bytes, self_feed);
+                                            p.op_b == BLB200_H, stages, slot_bytes);
   return (int)cudaGetLastError();
 }
 
@@ -311,7 +271,7 @@ int launch_cw(const GemmParams& p, int stages, int slot_bytes, bool hc, cudaStre
   const bool ak = p.op_a != BLB200_N;  // op T / H stores A as k x m: k runs fastest
   const bool bk = p.op_b == BLB200_N;  // op N stores B as k x n: k runs fastest
   const bool quarter = p.m <= 16 && p.n <= 16;
-  const bool dmma = std::is_same<T, double>::value && dmma_enabled() && p.m % 8 == 0 && p.n % 8 == 0 && p.k % 4 == 0;
+  const bool dmma = std::is_same<T, double>::value && p.m % 8 == 0 && p.n % 8 == 0 && p.k % 4 == 0;
 #define BLB_CASE(a, b)                                                                                     \
   if (ak == a && bk == b) {                                                                                \
     if constexpr (std::is_same<T, double>::value) {                                                        \
@@ -335,18 +295,6 @@ int launch_cw(const GemmParams& p, int stages, int slot_bytes, bool hc, cudaStre
   return BLB200_E_INTERNAL;
 }
 
-// double, 4 x 4 tiles, four warp pairs
-int launch_dmma_pairs(const GemmParams& p, int stages, int slot_bytes, bool hc, cudaStream_t stream) {
-  const bool ak = p.op_a != BLB200_N, bk = p.op_b == BLB200_N;
-#define BLB_CASE(a, b)                                                                                      \
-  if (ak == a && bk == b)                                                                                   \
-    return hc ? launch_one<double, 8, a, b, true, 4, 4, true, true>(p, stages, slot_bytes, stream)          \
-              : launch_one<double, 8, a, b, false, 4, 4, true, true>(p, stages, slot_bytes, stream);
-  BLB_CASE(false, false) BLB_CASE(false, true) BLB_CASE(true, false) BLB_CASE(true, true)
-#undef BLB_CASE
-  return BLB200_E_INTERNAL;
-}
-
 template <typename T>
 int launch_typed(const GemmParams& p, cudaStream_t stream) {
   const bool hc = !(p.beta[0] == 0.0 && p.beta[1] == 0.0);
@@ -361,17 +309,8 @@ int launch_typed(const GemmParams& p, cudaStream_t stream) {
     // each where 16 slots fit (16 warps would cap a thread at 96 registers and spill: 24^3 ran at 2.4
     // instead of 3.5 TB/s); bigger items stay on four warps with two or three slots each, which
     // measured faster than eight warps with one (32^3: 4.0 against 3.9, beta = 0: 3.9 against 2.8 TB/s).
-    static const int dmma_cw = [] { const char* v = getenv("BLB200_SMALL_RING_DMMA_CW"); return v && *v ? atoi(v) : 8; }();
     const bool tiles4 = (p.m > 16 || p.n > 16) && p.m % 8 == 0 && p.n % 8 == 0 && p.k % 4 == 0;
-    // warp pairs on slots that always carry a C area
-    // (measured slower than one warp per item: 32^3 3.8 against 4.0 TB/s; kept as an opt-in)
-    static const bool pairs_on = [] { const char* v = getenv("BLB200_SMALL_RING_DMMA_PAIRS"); return v && *v == '1'; }();
-    if (tiles4 && pairs_on && dmma_enabled()) {
-      const int slot_pair = (p.m * p.k + p.k * p.n + p.m * p.n) * (int)sizeof(T);
-      const int fit_pair = (int)(budget / (size_t)slot_pair);
-      if (fit_pair >= 8) return launch_dmma_pairs(p, (fit_pair >= 32 ? 32 : fit_pair) / 4 * 4, slot_pair, hc, stream);
-    }
-    if (tiles4 && dmma_cw == 8 && fit >= 16) return launch_cw<T, 8>(p, (fit >= 32 ? 32 : fit) / 8 * 8, slot_bytes, hc, stream);
+    if (tiles4 && fit >= 16) return launch_cw<T, 8>(p, (fit >= 32 ? 32 : fit) / 8 * 8, slot_bytes, hc, stream);
   }
   // 16 warps with two slots each when that fits, else with one
   if (fit >= 32) return launch_cw<T, 16>(p, 32, slot_bytes, hc, stream);
@@ -384,6 +323,7 @@ int launch_typed(const GemmParams& p, cudaStream_t stream) {
 }  // namespace
 
 int small_ring_device_status(int* out) { return read_device_status_word(out); }
+int small_ring_device_status_clear() { return clear_device_status_word(); }
 
 bool small_ring_supported(const GemmParams& p, int dtype) {
   const long long es = dtype == BLB200_S ? 4 : (dtype == BLB200_Z ? 16 : 8);

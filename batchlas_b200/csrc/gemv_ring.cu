@@ -283,6 +283,7 @@ int launch_typed(const void* a, const void* x, void* y, int m, int n, int batch,
 }  // namespace
 
 int gemv_ring_device_status(int* out) { return read_device_status_word(out); }
+int gemv_ring_device_status_clear() { return clear_device_status_word(); }
 
 bool gemv_ring_supported(int dtype, const void* a, const void* x, const void* y, int m, int n, int batch, long long lda,
                          long long sa, long long incx, long long sx, long long incy, long long sy, bool trans,

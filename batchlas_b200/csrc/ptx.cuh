@@ -14,6 +14,10 @@ static __device__ int g_device_status = 0;
 static inline int read_device_status_word(int* out) {
   return (int)cudaMemcpyFromSymbol(out, g_device_status, sizeof(int), 0, cudaMemcpyDeviceToHost);
 }
+static inline int clear_device_status_word() {
+  const int zero = 0;
+  return (int)cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int), 0, cudaMemcpyHostToDevice);
+}
 
 constexpr uint32_t kSpinLimit = 1u << 22;  // polls; each poll may itself block for a short HW-defined time
 
@@ -50,14 +54,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return done != 0;
 }
 
-// Returns false (after recording `code`) when the phase did not complete within the limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+// Returns false (after recording `code`) when the phase did not complete within `limit` polls.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, int code, uint32_t limit) {
+  for (uint32_t spin = 0; spin < limit; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if (spin > 64) __nanosleep(64);
   }
   atomicCAS(&g_device_status, 0, code);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
+  return mbar_wait_limit(bar, parity, code, kSpinLimit);
 }
 
 // global -> shared bulk copy of `bytes` (multiple of 16; both addresses 16-byte aligned),

@@ -1,21 +1,37 @@
 #!/usr/bin/env python
 """Benchmark of the batched-GEMM hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extra]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|cublas] [--no-extra]
 
 Headline workload (``config.workload`` = "C2"): tiny-matrix SGEMM, float32, M=N=K=32, packed
-column-major (ld 32, batch stride 1024), alpha=1.5, beta=-0.5, A/B/C ~ U[-1,1], batch 1,000,000
-per GPU, ops NT and TN.  One *step* = one NT call plus one TN call over the whole per-GPU batch
-(2 kernel launches).  Inputs are 12.3 GB per GPU, far larger than the 126 MB L2, so no explicit
-L2 flush is needed between iterations.  Multi-GPU: the batch dimension is sharded contiguously,
-one process per GPU, no collective on the data path ("weak": per-GPU batch fixed).
+column-major (ld 32, batch stride 1024), alpha=1.5, beta=-0.5, A/B/C ~ U[-1,1], batch 1,000,000,
+ops NT and TN.  One *step* = one NT call plus one TN call over the whole batch (2 kernel launches
+per GPU).  Inputs are 12.3 GB, far larger than the 126 MB L2, so no explicit L2 flush is needed
+between iterations.  Multi-GPU: the 1,000,000 items are sharded contiguously over the ranks, one
+process per GPU, no collective on the data path ("strong": the total batch is fixed, 125,000 items
+per GPU at 8 GPUs).
 
 Reported on one JSON line: ``value`` (GFLOP/s, inputs resident in HBM, CUDA-event timed, max over
 ranks), ``e2e`` (same metric through the host-buffer C-ABI entry with H2D/D2H inside the timed
 region), ``roofline`` (algorithmic bytes / measured launch time against the measured HBM copy
 bandwidth), ``cpu_baseline`` (the CPU oracle — a port of the reference's serial CBLAS loop — on a
-bounded sample), ``clocks``, ``gpu_launches`` and, unless --no-extra, ``configs``: device-timed
-figures for the other four benchmark configurations (C1, C3, C4, C5), batch-sharded over the ranks.
+bounded sample), ``clocks``, ``gpu_launches``, ``sustained`` (the same steps repeated for 2 s or
+more, with the SM clock the power cap allows) and, unless --no-extra, ``strong`` and ``configs``:
+device-timed figures for the other four benchmark configurations (C1, C3, C4, C5), batch-sharded
+over the ranks, each with a burst figure, a sustained figure, the cuBLAS figure on the same
+buffers and, with more than one GPU, the speed-up over rank 0 running the whole batch alone.
+
+Timing patterns.  The headline times exactly K steps inside one event pair (C drifts under
+beta = -0.5 but stays bounded; timing does not depend on the values).  The per-configuration
+figures follow the reference's harness (BatchLAS include/util/bench_structured.hh:118-150): when
+beta != 0, C is restored from the generator before every launch, outside the timed interval; every
+launch then has its own event pair and only those intervals are summed.  With beta == 0 the
+launches run back to back inside one event pair.
+
+cuBLAS leg: ``cublas{S,D,C,Z}gemmStridedBatched`` through ctypes on the libcublas that ships with
+torch, default math mode (FP32 / FP64 arithmetic, no TF32) — what the reference's CUDA backend
+executes on this GPU (BatchLAS src/backends/cublas.cc:125-147).  It is a yardstick inside this file
+only; the library never links or calls cuBLAS.
 """
 from __future__ import annotations
 
@@ -33,10 +49,10 @@ sys.path.insert(0, ROOT)
 METRIC = "batched GEMM GFLOP/s (device-timed)"
 NOMINAL_HBM_GBS = 8000.0          # the roofline definition of the task statement uses 8 TB/s
 FALLBACK_HBM_GBS = 6650.0         # earlier measurement on this pool, used when no peaks file exists
-# dram__bytes_read.sum + dram__bytes_write.sum per item of the dominant kernel, from the ncu
-# capture summarised under profiles/; traffic grows in proportion to the batch, so it is scaled to
-# the full launch by the item count.
-NCU_TRAFFIC_BYTES_PER_ITEM = 16071.5  # profiles/small32_C2_sgemm32.md: 100 000-item capture, mean of NT and TN
+# dram__bytes_read.sum + dram__bytes_write.sum per item of the dominant kernel, from the committed
+# ncu summary of a 100 000-item capture (mean of NT and TN); traffic grows in proportion to the
+# batch, so it is scaled to the full launch by the item count.
+NCU_TRAFFIC_BYTES_PER_ITEM = 16071.5
 
 
 def measured_peaks():
@@ -279,6 +295,128 @@ def time_launches(torch, launch, reps):
     return s.elapsed_time(e) / reps  # ms per rep
 
 
+def time_restored(torch, launch, restore, reps):
+    """ms per launch with C restored before every launch, outside the timed intervals: one event
+    pair per launch, only those intervals are summed."""
+    pairs = []
+    for _ in range(reps):
+        restore()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        launch()
+        e.record()
+        pairs.append((s, e))
+    torch.cuda.synchronize()
+    return sum(s.elapsed_time(e) for s, e in pairs) / reps
+
+
+def time_op(torch, launch, restore, reps):
+    return time_restored(torch, launch, restore, reps) if restore else time_launches(torch, launch, reps)
+
+
+def sustained_run(torch, launch, restore, one_ms, local_rank, seconds=2.0):
+    """The same launch repeated for `seconds` or more of device time; returns ms per launch and the
+    clocks sampled meanwhile (median SM MHz under load, throttle reasons)."""
+    reps = int(max(3, min(20000, seconds * 1e3 / max(one_ms, 1e-3))))
+    smp = ClockSampler(local_rank)
+    smp.start()
+    time.sleep(0.15)
+    t0 = time.time()
+    ms = time_op(torch, launch, restore, reps)
+    t1 = time.time()
+    smp.stop()
+    clk = smp.summary(t0 + 0.3, t1)  # skip the ramp: the clock under a held load is what is wanted
+    return ms, reps, clk
+
+
+# ---- cuBLAS yardstick (bench only) --------------------------------------------------------------------
+class Cublas:
+    """cublas{S,D,C,Z}gemmStridedBatched on the caller's device buffers and stream: the call the
+    reference's CUDA backend ends in (BatchLAS src/backends/cublas.cc:125-147).  Default math mode:
+    FP32 / FP64 arithmetic, no TF32."""
+
+    def __init__(self, torch):
+        import ctypes
+        import glob
+        self.ct = ctypes
+        self.torch = torch
+        cands = []
+        try:
+            import nvidia.cublas.lib as nl
+            cands += glob.glob(os.path.join(os.path.dirname(nl.__file__), "libcublas.so*"))
+        except Exception:
+            pass
+        cands += ["libcublas.so.12", "libcublas.so"]
+        self.lib = None
+        for c in cands:
+            try:
+                self.lib = ctypes.CDLL(c)
+                break
+            except OSError:
+                continue
+        if self.lib is None:
+            raise RuntimeError("libcublas not found")
+        self.handle = ctypes.c_void_p()
+        self.lib.cublasCreate_v2.argtypes = [ctypes.POINTER(ctypes.c_void_p)]
+        if self.lib.cublasCreate_v2(ctypes.byref(self.handle)) != 0:
+            raise RuntimeError("cublasCreate failed")
+        self.lib.cublasSetStream_v2.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        vp, i, ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        self.fns = {}
+        for letter, name in (("s", "cublasSgemmStridedBatched"), ("d", "cublasDgemmStridedBatched"),
+                             ("c", "cublasCgemmStridedBatched"), ("z", "cublasZgemmStridedBatched")):
+            fn = getattr(self.lib, name)
+            fn.argtypes = [vp, i, i, i, i, i, vp, vp, i, ll, vp, i, ll, vp, vp, i, ll, i]
+            fn.restype = i
+            self.fns[letter] = fn
+        ver = ctypes.c_int(0)
+        self.lib.cublasGetVersion_v2.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]
+        self.lib.cublasGetVersion_v2(self.handle, ctypes.byref(ver))
+        self.version = ver.value
+
+    def launcher(self, c, op, tensors, meta, batch):
+        ct = self.ct
+        letter = c["dtype"]
+        real = {"s": ct.c_float, "d": ct.c_double, "c": ct.c_float, "z": ct.c_double}[letter]
+        al, be = complex(c["alpha"]), complex(c["beta"])
+        alpha = (real * 2)(al.real, al.imag)
+        beta = (real * 2)(be.real, be.imag)
+        opc = {"N": 0, "T": 1, "C": 2}
+        fn = self.fns[letter]
+        args = (opc[op[0]], opc[op[1]], c["m"], c["n"], c["k"], ct.cast(alpha, ct.c_void_p),
+                tensors["a"].data_ptr(), meta["a"][0], meta["a"][1], tensors["b"].data_ptr(), meta["b"][0], meta["b"][1],
+                ct.cast(beta, ct.c_void_p), tensors["c"].data_ptr(), meta["c"][0], meta["c"][1], batch)
+        handle, lib, torch = self.handle, self.lib, self.torch
+
+        def launch(_keep=(alpha, beta)):
+            lib.cublasSetStream_v2(handle, torch.cuda.current_stream().cuda_stream)
+            rc = fn(handle, *args)
+            if rc != 0:
+                raise RuntimeError(f"cuBLAS status {rc}")
+        return launch
+
+
+def checksum_all_items(torch, c, op, tensors, meta, batch, launch, restore):
+    """Full-size parity property: restore C, run `launch` once, and hold EVERY item to the summed
+    entrywise bound through the checksum identity (tests/_props.py).  Returns the worst ratio."""
+    from tests import _props
+    restore()
+    torch.cuda.synchronize()
+    oa, ob = op
+    ar, ac = (c["m"], c["k"]) if oa == "N" else (c["k"], c["m"])
+    br, bc = (c["k"], c["n"]) if ob == "N" else (c["n"], c["k"])
+    tA = _props.strided_view(torch, tensors["a"], ar, ac, meta["a"][0], meta["a"][1], batch)
+    tB = _props.strided_view(torch, tensors["b"], br, bc, meta["b"][0], meta["b"][1], batch)
+    tC = _props.strided_view(torch, tensors["c"], c["m"], c["n"], meta["c"][0], meta["c"][1], batch)
+    before = _props.sums_before(torch, tC)
+    launch()
+    torch.cuda.synchronize()
+    bad, worst = _props.checksum_check(torch, tA, tB, tC, oa, ob, c["alpha"], c["beta"], c["k"], c["dtype"], before)
+    if bad:
+        raise SystemExit(f"PARITY FAILURE (checksum) {op}: {bad} of {batch} items beyond the bound (worst {worst:.3g})")
+    return worst
+
+
 # ---- the two arms ------------------------------------------------------------------------------------
 def run_reference_arm(args, rank):
     if rank != 0:
@@ -292,7 +430,7 @@ def run_reference_arm(args, rank):
     value = sorted(vals)[len(vals) // 2]
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "GFLOP/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "C2", "note": "reference CPU path (port of the serial CBLAS batch "
                        "loop of netlib_lapack.cc:108-171, BLAS threading at its default) on a bounded sub-batch "
                        "per step; cpu_baseline.batch_parallel_gflops is the same loop split over all host cores"},
@@ -300,6 +438,103 @@ def run_reference_arm(args, rank):
             "e2e": {"value": value, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0, "wall_s": time.perf_counter() - t0}
     print(json.dumps(line), flush=True)
+
+
+def restore_fn(bl, torch, c, tensors, meta, first_item):
+    """Device-side restore of C from the generator (None when beta == 0: C is never read)."""
+    if c["beta"] == 0:
+        return None
+    dist, scale = c["dist_c"]
+    sc = meta["c"][1]
+
+    def restore():
+        bl.fill(tensors["c"], 42, 3, dist, scale, first_index=first_item * sc)
+    return restore
+
+
+def measure_config_op(bl, torch, c, op, tens, mt, nb, b0, local_rank, barrier, max_over_ranks, world, cublas,
+                      do_sustained=True, kernel="auto"):
+    """Burst, sustained and cuBLAS figures for one op pair of one configuration on this rank's shard."""
+    d = desc_for(bl, c, op, tens, mt, nb, kernel=kernel)
+    launch = (lambda d=d: bl.gemm_strided_batched(d))
+    restore = restore_fn(bl, torch, c, tens, mt, b0)
+    for _ in range(3):
+        launch()
+    torch.cuda.synchronize()
+    one = time_launches(torch, launch, 1)
+    # about 60 ms of launches after a short idle: a kernel timed alone.  Held for 150 ms or more, the
+    # FP32 64^3 case reaches the 1000 W cap and the SM clock falls from 1965 to about 1710 MHz.
+    reps = int(max(3, min(1000, 60.0 / max(one, 1e-3))))
+    barrier()
+    smp = ClockSampler(local_rank)
+    smp.start()
+    time.sleep(0.4)
+    tw0 = time.time()
+    ms = max_over_ranks(time_op(torch, launch, restore, reps))
+    tw1 = time.time()
+    smp.stop()
+    clk = smp.summary(tw0, tw1)
+    kern = bl.last_kernel_name()
+    w = verify_sample(bl, torch, c, op, tens, mt, nb, b0, n_check=2)
+    full_restore = restore or (lambda: None)
+    wsum = checksum_all_items(torch, c, op, tens, mt, nb, launch, full_restore)
+    total_flops = flops_per_item(c) * c["batch"]
+    tfl = total_flops / (ms * 1e-3) / 1e12
+    ai = flops_per_item(c) / algorithmic_bytes_per_item(c)
+    roof = min(PIPE_PEAK_TFLOPS[c["dtype"]] * world, ai * NOMINAL_HBM_GBS * 1e9 / 1e12 * world)
+    out = {"gflops": tfl * 1e3, "ms": ms, "kernel": kern, "frac_of_roofline": tfl / roof,
+           "worst_error_ratio": w, "checksum_all_items_worst_ratio": wsum, "reps": reps,
+           "timing": "C restored before each launch, per-launch events" if restore else "back-to-back, one event pair",
+           "sm_mhz": clk["sm_mhz"], "clock_reasons": clk["reasons"],
+           "hbm_gbs": algorithmic_bytes_per_item(c) * c["batch"] / (ms * 1e-3) / 1e9}
+    if do_sustained:
+        time.sleep(0.3)
+        barrier()
+        sms, sreps, sclk = sustained_run(torch, launch, restore, ms, local_rank)
+        sms = max_over_ranks(sms)
+        stfl = total_flops / (sms * 1e-3) / 1e12
+        out["sustained"] = {"gflops": stfl * 1e3, "ms": sms, "launches": sreps, "seconds": sms * sreps * 1e-3,
+                            "frac_of_roofline": stfl / roof, "sm_mhz": sclk["sm_mhz"], "clock_reasons": sclk["reasons"],
+                            "gflops_per_mhz": (stfl * 1e3 / sclk["sm_mhz"]) if sclk["sm_mhz"] else None}
+    if cublas is not None:
+        try:
+            cl = cublas.launcher(c, op, tens, mt, nb)
+            for _ in range(3):
+                cl()
+            torch.cuda.synchronize()
+            cw = checksum_all_items(torch, c, op, tens, mt, nb, cl, full_restore)  # the yardstick computes the same thing
+            time.sleep(0.3)
+            barrier()
+            cms = max_over_ranks(time_op(torch, cl, restore, reps))
+            out["cublas_gflops"] = total_flops / (cms * 1e-3) / 1e9
+            out["cublas_ms"] = cms
+            out["vs_cublas"] = cms / ms
+            out["cublas_checksum_worst_ratio"] = cw
+        except Exception as exc:  # the yardstick must never take the benchmark down
+            out["cublas_error"] = str(exc)[:200]
+    return out
+
+
+def bind_to_gpu_numa_node(torch, local_rank):
+    """Best effort: run this process on the cores of the NUMA node its GPU hangs off, so that host
+    staging buffers allocated afterwards land in that node's memory.  Returns what was done."""
+    try:
+        pr = torch.cuda.get_device_properties(local_rank)
+        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read().strip())
+        if node < 0:
+            return {"pci": bdf, "numa_node": node, "bound": False}
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return {"pci": bdf, "numa_node": node, "bound": False, "why": "no allowed core on that node"}
+        os.sched_setaffinity(0, allowed)
+        return {"pci": bdf, "numa_node": node, "bound": True, "cores": len(allowed)}
+    except Exception as exc:
+        return {"bound": False, "why": str(exc)[:120]}
 
 
 def run_ours(args, rank, local_rank, world):
@@ -341,10 +576,16 @@ def run_ours(args, rank, local_rank, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    cublas = None
+    if not args.no_cublas:
+        try:
+            cublas = Cublas(torch)
+        except Exception:
+            cublas = None
+
     cfgs = configs()
     c2 = cfgs["C2"]
-    batch = c2["batch"]                      # per GPU (weak scaling)
-    first_item = rank * batch
+    first_item, batch = shard_range(c2["batch"], rank, world)   # strong scaling: the 10^6 items are shared out
     tensors, meta = alloc_config(bl, torch, c2, batch, first_item, device)
     descs = [desc_for(bl, c2, op, tensors, meta, batch) for op in c2["ops"]]
 
@@ -364,7 +605,6 @@ def run_ours(args, rank, local_rank, world):
     kernel_name = bl.last_kernel_name()
     launches0 = bl.launch_count()
     barrier()
-    t_wall0 = time.time()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     for _ in range(args.steps):
@@ -379,17 +619,48 @@ def run_ours(args, rank, local_rank, world):
     clocks = sampler.summary(t_load0, t_wall1)
     clocks["window"] = "warm-up + timed steps"
     ms_per_step = ms_total / args.steps
-    flops_step = flops_per_item(c2) * batch * len(c2["ops"]) * world
+    flops_step = flops_per_item(c2) * c2["batch"] * len(c2["ops"])
     value = flops_step / (ms_per_step * 1e-3) / 1e9
 
     per_op_ms = {}
     for (oa, ob), d in zip(c2["ops"], descs):
         per_op_ms[oa + ob] = max_over_ranks(time_launches(torch, lambda d=d: bl.gemm_strided_batched(d), max(3, args.steps)))
 
-    # parity spot-check on the exact buffers that were timed (restores C first)
-    worst = max(verify_sample(bl, torch, c2, op, tensors, meta, batch, first_item) for op in c2["ops"])
+    # the same steps held for two seconds or more: what the 1000 W cap allows
+    time.sleep(0.3)
+    barrier()
+    s_ms, s_reps, s_clk = sustained_run(torch, step, None, ms_per_step, local_rank)
+    s_ms = max_over_ranks(s_ms)
+    sustained = {"value": flops_step / (s_ms * 1e-3) / 1e9, "unit": "GFLOP/s", "ms_per_step": s_ms, "steps": s_reps,
+                 "seconds": s_ms * s_reps * 1e-3, "sm_mhz": s_clk["sm_mhz"], "clock_reasons": s_clk["reasons"],
+                 "hbm_gbs": algorithmic_bytes_per_item(c2) * batch * len(c2["ops"]) / (s_ms * 1e-3) / 1e9,
+                 "gflops_per_mhz": (flops_step / (s_ms * 1e-3) / 1e9 / s_clk["sm_mhz"]) if s_clk["sm_mhz"] else None}
 
-    # roofline of the dominant kernel: one launch = one op over the per-GPU batch
+    # parity on the exact buffers that were timed (restores C first): sampled items against the
+    # long-double arbiter, and every item through the checksum identity
+    worst = max(verify_sample(bl, torch, c2, op, tensors, meta, batch, first_item) for op in c2["ops"])
+    c2_restore = restore_fn(bl, torch, c2, tensors, meta, first_item)
+    worst_sum = max(checksum_all_items(torch, c2, op, tensors, meta, batch,
+                                       (lambda d=d: bl.gemm_strided_batched(d)), c2_restore)
+                    for op, d in zip(c2["ops"], descs))
+
+    cublas_c2 = None
+    if cublas is not None:
+        try:
+            cms = {}
+            for op in c2["ops"]:
+                cl = cublas.launcher(c2, op, tensors, meta, batch)
+                for _ in range(2):
+                    cl()
+                torch.cuda.synchronize()
+                cms[op[0] + op[1]] = max_over_ranks(time_launches(torch, cl, max(3, min(args.steps, 5))))
+            cublas_c2 = {"ms_by_op": cms, "gflops": flops_step / (sum(cms.values()) * 1e-3) / 1e9,
+                         "vs_cublas": sum(cms.values()) / ms_per_step, "version": cublas.version,
+                         "call": "cublasSgemmStridedBatched, default math (no TF32), same device buffers"}
+        except Exception as exc:
+            cublas_c2 = {"error": str(exc)[:200]}
+
+    # roofline of the dominant kernel: one launch = one op over this GPU's share of the batch
     peak, peak_kind = measured_peaks()
     bytes_launch = algorithmic_bytes_per_item(c2) * batch
     launch_ms = ms_per_step / len(c2["ops"])
@@ -405,6 +676,7 @@ def run_ours(args, rank, local_rank, world):
     e2e = None
     if not args.no_e2e:
         import psutil
+        numa = bind_to_gpu_numa_node(torch, local_rank) if args.numa_bind else {"bound": False, "why": "not requested"}
         es = 4
         need = 3 * batch * 1024 * es
         avail = psutil.virtual_memory().available / max(world, 1)
@@ -434,19 +706,33 @@ def run_ours(args, rank, local_rank, world):
             e2e_step()
         torch.cuda.synchronize()
         dt_e2e = max_over_ranks(time.perf_counter() - t0)
-        e2e_flops = flops_per_item(c2) * e2e_batch * len(c2["ops"]) * world * e2e_steps
+        all_items = e2e_batch
+        if world > 1:
+            t = torch.tensor([float(e2e_batch)], dtype=torch.float64, device=device)
+            dist.all_reduce(t)
+            all_items = int(t.item())
+        e2e_flops = flops_per_item(c2) * all_items * len(c2["ops"]) * e2e_steps
+        # the ceiling of this box for the same bytes: plain pinned copies, all ranks at once
+        barrier()
+        t0 = time.perf_counter()
+        for src in (hA, hB, hC):
+            tensors["a"][: e2e_batch * 1024].copy_(src, non_blocking=True)
+        torch.cuda.synchronize()
+        dt_copy = max_over_ranks(time.perf_counter() - t0)
         e2e = {"value": e2e_flops / dt_e2e / 1e9, "unit": "GFLOP/s",
-               "h2d_bytes_per_step": 3 * e2e_batch * 4096 * len(c2["ops"]),
-               "d2h_bytes_per_step": e2e_batch * 4096 * len(c2["ops"]), "steps": e2e_steps,
+               "h2d_bytes_per_step": 3 * all_items * 4096 * len(c2["ops"]),
+               "d2h_bytes_per_step": all_items * 4096 * len(c2["ops"]), "steps": e2e_steps,
                "batch_per_gpu": e2e_batch, "api": "blb200_gemm_strided_batched_host (pinned host A,B,C; chunked "
-               "H2D -> kernel -> D2H on 3 streams)", "ms_per_step": dt_e2e / e2e_steps * 1e3}
+               "H2D -> kernel -> D2H on 3 streams)", "ms_per_step": dt_e2e / e2e_steps * 1e3,
+               "h2d_gbs_in_step": 3 * all_items * 4096 * len(c2["ops"]) * e2e_steps / dt_e2e / 1e9,
+               "h2d_gbs_plain_copies_all_ranks": 3 * all_items * 4096 / dt_copy / 1e9, "numa": numa}
         del hA, hB, hC
 
     del tensors
     torch.cuda.empty_cache()
 
     # ---- the other configurations, device-timed, batch sharded over the ranks (strong) ------------
-    extra = {}
+    extra, strong = {}, {}
     pipe_peaks = None
     if not args.no_extra:
         pipe_peaks = {"fp32_tflops_measured": bl.measure_pipe_peak("s"), "fp64_tflops_measured": bl.measure_pipe_peak("d"),
@@ -459,38 +745,40 @@ def run_ours(args, rank, local_rank, world):
             tens, mt = alloc_config(bl, torch, c, nb, b0, device)
             per_op = {}
             for op in c["ops"]:
-                d = desc_for(bl, c, op, tens, mt, nb)
-                launch = (lambda d=d: bl.gemm_strided_batched(d))
-                for _ in range(3):
-                    launch()
-                torch.cuda.synchronize()
-                one = time_launches(torch, launch, 1)
-                # about 60 ms of back-to-back launches after a short idle: a kernel timed alone.  Held
-                # for 150 ms or more, the FP32 64^3 case reaches the 1000 W cap and the SM clock falls
-                # from 1965 to about 1710 MHz; its throughput falls in the same proportion.
-                reps = int(max(3, min(1000, 60.0 / max(one, 1e-3))))
-                barrier()
-                smp = ClockSampler(local_rank)
-                smp.start()
-                time.sleep(0.4)
-                tw0 = time.time()
-                ms = max_over_ranks(time_launches(torch, launch, reps))
-                tw1 = time.time()
-                smp.stop()
-                clk = smp.summary(tw0, tw1)
-                kern = bl.last_kernel_name()
-                w = verify_sample(bl, torch, c, op, tens, mt, nb, b0, n_check=2)
-                total_flops = flops_per_item(c) * c["batch"]
-                tfl = total_flops / (ms * 1e-3) / 1e12
-                ai = flops_per_item(c) / algorithmic_bytes_per_item(c)
-                roof = min(PIPE_PEAK_TFLOPS[c["dtype"]] * world, ai * NOMINAL_HBM_GBS * 1e9 / 1e12 * world)
-                per_op[op[0] + op[1]] = {"gflops": tfl * 1e3, "ms": ms, "kernel": kern,
-                                         "frac_of_roofline": tfl / roof, "worst_error_ratio": w, "reps": reps,
-                                         "sm_mhz": clk["sm_mhz"], "clock_reasons": clk["reasons"],
-                                         "hbm_gbs": algorithmic_bytes_per_item(c) * c["batch"] / (ms * 1e-3) / 1e9}
+                per_op[op[0] + op[1]] = measure_config_op(bl, torch, c, op, tens, mt, nb, b0, local_rank, barrier,
+                                                         max_over_ranks, world, cublas, do_sustained=not args.no_sustained)
             extra[name] = per_op
             del tens
             torch.cuda.empty_cache()
+            if world > 1:
+                # strong scaling inside this run: rank 0 alone runs the whole batch on its GPU while the
+                # others wait; speed-up = that time / the sharded time measured above
+                alone = {}
+                if rank == 0:
+                    tens, mt = alloc_config(bl, torch, c, c["batch"], 0, device)
+                    for op in c["ops"]:
+                        d = desc_for(bl, c, op, tens, mt, c["batch"])
+                        launch = (lambda d=d: bl.gemm_strided_batched(d))
+                        restore = restore_fn(bl, torch, c, tens, mt, 0)
+                        for _ in range(3):
+                            launch()
+                        torch.cuda.synchronize()
+                        one = time_launches(torch, launch, 1)
+                        time.sleep(0.4)
+                        alone[op[0] + op[1]] = time_op(torch, launch, restore, int(max(3, min(1000, 60.0 / max(one, 1e-3)))))
+                    del tens
+                    torch.cuda.empty_cache()
+                barrier()
+                for opn, r in per_op.items():
+                    a_ms = alone.get(opn)
+                    strong[f"{name}:{opn}"] = {"ms_1gpu_whole_batch": a_ms, "ms_sharded": r["ms"],
+                                               "speedup": (a_ms / r["ms"]) if a_ms else None, "gflops": r["gflops"]}
+            else:
+                for opn, r in per_op.items():
+                    strong[f"{name}:{opn}"] = {"ms_sharded": r["ms"], "gflops": r["gflops"],
+                                               "frac_of_roofline": r["frac_of_roofline"],
+                                               "sustained_frac": r.get("sustained", {}).get("frac_of_roofline"),
+                                               "vs_cublas": r.get("vs_cublas")}
 
     status = bl.device_status()
     if status != 0:
@@ -499,21 +787,24 @@ def run_ours(args, rank, local_rank, world):
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": {"workload": "C2", "shape": "SGEMM 32x32x32, ops NT+TN per step, alpha=1.5 beta=-0.5, "
-                           "packed column-major (ld 32, stride 1024)", "batch_per_gpu": batch,
-                           "global_batch": batch * world, "sharding": f"contiguous batch ranges x{world}, no collective",
-                           "l2": "inputs (12.3 GB per GPU) exceed the 126 MB L2; no flush needed",
+                           "packed column-major (ld 32, stride 1024)", "global_batch": c2["batch"],
+                           "batch_per_gpu": batch, "sharding": f"contiguous batch ranges x{world}, no collective",
+                           "l2": f"inputs ({3 * batch * 4096 / 1e9:.1f} GB per GPU) exceed the 126 MB L2; no flush needed",
                            "seed": 42},
                 "roofline": roofline, "e2e": e2e, "gpu_launches": int(launches) * world, "clocks": clocks,
-                "parity_worst_error_ratio": worst}
+                "sustained": sustained, "parity_worst_error_ratio": worst,
+                "parity_checksum_all_items_worst_ratio": worst_sum, "cublas": cublas_c2}
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline("C2")
         if extra:
-            line["configs"] = extra
+            line["strong"] = strong     # compact, ahead of the long per-configuration block
             line["pipe_peaks"] = pipe_peaks
             line["configs_note"] = ("device-timed, whole BASELINE batch sharded contiguously over the ranks; "
-                                    "frac_of_roofline = achieved / min(nominal pipe peak, AI x 8 TB/s)")
+                                    "frac_of_roofline = achieved / min(nominal pipe peak, AI x 8 TB/s); beta != 0: C "
+                                    "restored before each launch outside the timed intervals")
+            line["configs"] = extra
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -542,6 +833,8 @@ def run_case(args):
     for o in ops:
         d = desc_for(bl, c, o, tens, mt, batch, kernel=args.kernel)
         launch = lambda: bl.gemm_strided_batched(d)
+        if args.impl == "cublas":  # the yardstick on the same buffers
+            launch = Cublas(torch).launcher(c, o, tens, mt, batch)
         if args.splitk:
             import ctypes
             from batchlas_b200 import _lib
@@ -554,8 +847,10 @@ def run_case(args):
         for _ in range(args.warmup):
             launch()
         torch.cuda.synchronize()
-        ms = time_launches(torch, launch, args.steps)
+        ms = time_op(torch, launch, restore_fn(bl, torch, c, tens, mt, 0), args.steps)
         w = verify_sample(bl, torch, c, o, tens, mt, batch, 0, n_check=2)
+        if args.impl == "cublas":
+            out["impl"] = "cublas"
         out["ops"][o[0] + o[1]] = {"ms": ms, "kernel": bl.last_kernel_name(), "worst_error_ratio": w,
                                    "gflops": flops_per_item(c) * batch / (ms * 1e-3) / 1e9,
                                    "hbm_gbs": algorithmic_bytes_per_item(c) * batch / (ms * 1e-3) / 1e9}
@@ -714,10 +1009,13 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "cublas"])
     ap.add_argument("--no-extra", action="store_true", help="skip the C1/C3/C4/C5 figures")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-cublas", action="store_true", help="skip the cuBLAS yardstick legs")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the 2 s sustained figures of the configurations")
+    ap.add_argument("--numa-bind", action="store_true", help="bind each rank to its GPU's NUMA node before pinning host buffers")
     ap.add_argument("--case", default="", help="profiling mode: CONFIG[:OP], e.g. C2:NT or C3:TN, or a packed shape such as d32x32x32:NN (1 GPU)")
     ap.add_argument("--batch", type=int, default=0, help="batch override for --case")
     ap.add_argument("--beta", type=float, default=-0.5, help="beta of a --case given as a shape (DTYPE MxNxK, e.g. d32x32x32:TN)")
@@ -734,6 +1032,9 @@ def main():
     if args.impl == "reference":
         run_reference_arm(args, rank)
         return
+    if args.impl == "cublas" and not args.case:
+        raise SystemExit("--impl cublas times one configuration: give --case CONFIG[:OP] (the full run reports "
+                         "cublas_gflops beside every figure already)")
     if args.case:
         run_case(args)
         return

@@ -51,8 +51,10 @@ enum {
   BLB200_K_SMALL64 = 3, /* whole 64x64x64 float matrices per warp pair, TMA ring (tiled+bulk)   */
   BLB200_K_TILED = 4,   /* register-blocked FFMA/DFMA smem tiles fed by 16-byte async copies    */
   BLB200_K_DMMA = 5,    /* FP64 tensor-core (mma.sync m8n8k4) tiles, double and complex<double> */
-  BLB200_K_SGEMM128 = 6 /* float, A not transposed: 128x128x32 tiles, 8x8 blocks, packed FP32 FMA */
+  BLB200_K_SGEMM128 = 6, /* float, A not transposed: 128x128x32 tiles, 8x8 blocks, packed FP32 FMA */
+  BLB200_K_SMALL_RING = 7 /* any dtype, packed items up to 32x32 (k <= 64): whole items per warp, TMA ring */
 };
+/* Split-K has no kernel id: it needs scratch, which only its own entry points below receive. */
 
 /*
  * One strided-batched GEMM:  C_b <- alpha * op_a(A_b) * op_b(B_b) + beta * C_b,  b in [0,batch).
@@ -134,7 +136,11 @@ int blb200_gemm_splitk(const blb200_gemm_desc* desc, int32_t splits, void* works
  *   - All calls share the one array, and it keeps whatever the previous call left in it.  The
  *     kernels overwrite every partial element they later read, so no clearing is needed; but two
  *     calls that can overlap on the GPU (different streams, different host threads) race on the
- *     array.  Keep calls to this entry point ordered on one stream per device. */
+ *     array.  Keep calls to this entry point ordered on one stream per device.
+ *   - When the plan says that splitting does not help (fewer than 2 splits), the call runs the
+ *     ordinary launch, which needs no scratch at all.
+ *   - The looked-up address is remembered per device ordinal for the life of the process; it does
+ *     not survive a cudaDeviceReset (do not reset a device between calls to this entry point). */
 size_t blb200_gemm_splitk_static_capacity(void);
 int blb200_gemm_splitk_static(const blb200_gemm_desc* desc, int32_t splits, void* cuda_stream);
 
@@ -162,8 +168,21 @@ const char* blb200_version(void);
  * mirrors BatchLAS src/util/kernel-trace.hh:46-215.  No-op when tracing is off. */
 int blb200_trace_flush(void);
 /* Synchronises the current device and reports whether any kernel of this library ever gave up
- * on one of its bounded waits: *out = 0 when none did, else a small code naming the wait. */
+ * on one of its bounded waits: *out = 0 when none did, else a small code naming the wait
+ * (1xx: 32^3 / 64^3 float rings, 2xx: gemv ring, 3xx: small-matrix ring, BLB200_WAIT_SELFTEST: the
+ * self-test below).  Failure detection in the sense of BatchLAS's queue error handling
+ * (src/util/queue-impl.cc wait_and_throw): the host learns of a lost copy instead of hanging. */
 int blb200_device_status(int* out);
+/* Synchronises the current device and clears the status words, so that a later
+ * blb200_device_status reports only what happened after this call. */
+int blb200_device_status_reset(void);
+/* Self-test of the failure path: launches one warp that waits, with the library's own bounded
+ * wait and a limit of `max_polls` polls (1 .. 65536, i.e. at most a few milliseconds), on a barrier
+ * that nothing ever completes.  The wait gives up, the kernel returns normally, and
+ * blb200_device_status then reports BLB200_WAIT_SELFTEST.  Nothing faults and no copy is in flight;
+ * the device stays usable.  Asynchronous. */
+enum { BLB200_WAIT_SELFTEST = 901 };
+int blb200_selftest_wait_expiry(uint32_t max_polls, void* cuda_stream);
 
 /* Diagnostic: measured FMA issue rate of the current device in TFLOP/s (2 flops per FMA) for
  * dtype BLB200_S (FFMA) or BLB200_D (DFMA) — the pipe peak that compute-bound shapes are judged

@@ -65,6 +65,14 @@ def test_static_scratch_split_k_matches_caller_scratch_split_k(lib):
         assert bad == 0, (dt, oa, ob, worst)
         assert oracle.untouched_outside_window(p, C0, got)
 
+    # "allocates nothing": with every kernel already loaded by the calls above, one more call leaves
+    # the device's free memory exactly where it was
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    bl._lib.check(L.blb200_gemm_splitk_static(_desc(bl, p, dA, dB, dC_static), splits, stream))
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+
     # a plan that does not fit the fixed array is refused, nothing is launched
     big = bl.make_desc(dA.data_ptr(), dB.data_ptr(), dC_ref.data_ptr(), 1, 0, 0, 512, 512, 1 << 20, 1, 512, 1 << 20, 512,
                        0, 0, 0)
