@@ -13,9 +13,9 @@ LIB_PATH = os.path.join(_HERE, "libbatchlas_b200.so")
 
 S, D, C, Z = 0, 1, 2, 3
 OP_N, OP_T, OP_H = 0, 1, 2
-K_AUTO, K_GENERIC, K_SMALL32, K_SMALL64, K_TILED, K_DMMA, K_SGEMM128, K_SMALL_RING = 0, 1, 2, 3, 4, 5, 6, 7
+K_AUTO, K_GENERIC, K_SMALL32, K_SMALL64, K_TILED, K_DMMA, K_SGEMM128, K_SMALL_RING, K_DMMA_TMA = 0, 1, 2, 3, 4, 5, 6, 7, 8
 KERNEL_IDS = {"auto": K_AUTO, "generic": K_GENERIC, "small32": K_SMALL32, "small64": K_SMALL64,
-              "tiled": K_TILED, "dmma": K_DMMA, "sgemm128": K_SGEMM128, "small_ring": K_SMALL_RING}
+              "tiled": K_TILED, "dmma": K_DMMA, "sgemm128": K_SGEMM128, "small_ring": K_SMALL_RING, "dmma_tma": K_DMMA_TMA}
 
 E_NULL, E_SHAPE, E_DTYPE, E_UNSUPPORTED, E_NO_DEVICE, E_TOO_LARGE, E_INTERNAL = -1, -2, -3, -4, -5, -6, -7
 
@@ -85,6 +85,11 @@ SIGNATURES = {
     "blb200_axpby": (ctypes.c_int, [ctypes.POINTER(EwiseDesc), ctypes.POINTER(ctypes.c_double),
                                     ctypes.POINTER(ctypes.c_double), ctypes.c_void_p]),
     "blb200_gemm_strided_batched_host": (ctypes.c_int, [ctypes.POINTER(GemmDesc), ctypes.c_int, ctypes.c_int32]),
+    "blb200_gemm_strided_batched_host_multi": (ctypes.c_int, [ctypes.POINTER(GemmDesc), ctypes.POINTER(ctypes.c_int32),
+                                                              ctypes.c_int32, ctypes.c_int32]),
+    "blb200_shard_range": (None, [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(ctypes.c_int64),
+                                  ctypes.POINTER(ctypes.c_int64)]),
+    "blb200_host_staging_trim": (ctypes.c_int, [ctypes.c_int]),
     "blb200_last_kernel_name": (ctypes.c_char_p, []),
     "blb200_launch_count": (ctypes.c_uint64, []),
     "blb200_status_string": (ctypes.c_char_p, [ctypes.c_int]),

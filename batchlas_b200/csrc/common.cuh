@@ -48,6 +48,18 @@ __device__ __forceinline__ int item_dim(const int* dims, long long item, int cap
   return v < 0 ? 0 : (v < cap ? v : cap);
 }
 
+// True when every operand's base, leading dimension and batch stride are multiples of `bytes`
+// (es = element bytes): 16 selects the 16-byte copy policy of the tile kernels, es the
+// element-granular one (how BatchLAS switches its own load policy inside one kernel,
+// src/sycl/gemm/load_policies.hh:18-34).
+inline bool operands_aligned_to(const GemmParams& p, long long es, long long bytes) {
+  auto ok = [&](const void* base, long long ld, long long stride) {
+    return reinterpret_cast<uintptr_t>(base) % (uintptr_t)bytes == 0 && (ld * es) % bytes == 0 && (stride * es) % bytes == 0;
+  };
+  return ok(p.a, p.lda, p.sa) && ok(p.b, p.ldb, p.sb) && ok(p.c, p.ldc, p.sc);
+}
+inline long long dtype_bytes(int dtype) { return dtype == BLB200_S ? 4 : (dtype == BLB200_Z ? 16 : 8); }
+
 struct StructureHints {
   int tri_a, tri_b, out_tri, out_herm;
 };
@@ -205,6 +217,7 @@ int launch_small64(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_tiled(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_dmma(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_sgemm128(const GemmParams& p, int dtype, cudaStream_t stream);
+int launch_dmma_tma(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_splitk_reduce(const GemmParams& orig, int dtype, const void* partials, int splits, long long part_ld,
                          long long part_stride, cudaStream_t stream);
 
@@ -214,6 +227,7 @@ bool small_ring_supported(const GemmParams& p, int dtype);
 int launch_small_ring(const GemmParams& p, int dtype, cudaStream_t stream);
 bool tiled_supported(const GemmParams& p, int dtype);
 bool dmma_supported(const GemmParams& p, int dtype);
+bool dmma_tma_supported(const GemmParams& p, int dtype);
 bool sgemm128_supported(const GemmParams& p, int dtype);
 bool sgemm128_preferred(const GemmParams& p);  // against the tiled kernel, by padded work
 

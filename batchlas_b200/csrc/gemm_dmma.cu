@@ -7,19 +7,25 @@
 // bandwidth (about 78 % of it busy for 61 % of the FP64 pipe), the DMMA kernel is not.  DMMA
 // multiplies and accumulates in full binary64, so results stay within the same bound.
 //
-// Layout.  Operands stay in their stored orientation; rows of a stage are pitched 32 bytes past
-// their natural length so that the 16 lanes of a half-warp request (4 fragment rows x 4 k) fall
-// into 16 different 8-byte bank pairs:
-//   M-major A (op N):   stage rows are k, BM doubles each;    fragment (m = g, k = t) at [k][m]
-//   K-major A (op T/C): stage rows are m, BK doubles each;    fragment at [m][k]
+// Layout.  Operands stay in their stored orientation, laid out so that the 16 lanes of a half-warp
+// request (4 fragment rows x 4 k) fall into 16 different 8-byte bank pairs:
+//   M-major A (op N):   stage rows are k, BM doubles each, pitched 32 bytes past their length;
+//                       fragment (m = g, k = t) at [k][m]
+//   K-major A (op T/C): stage rows are m, BK doubles each.  Real double: rows of exactly 128 bytes
+//                       whose four 32-byte groups (4 k each) are stored at group index
+//                       (k / 4) ^ (row & 3) — no padding, so a stage is 8 KiB and four CTAs fit an
+//                       SM for every op pair (with padded rows TN needed 61 KiB per CTA and only
+//                       three fitted).  Complex: rows pitched 64 bytes past their length.
 //   (g = lane >> 2, t = lane & 3; B likewise with n in place of m.)
 // A warp owns a 32 x 32 block of C as 4 x 4 DMMA tiles (16 accumulator pairs); a CTA of 4 warps
 // owns 64 x 64, four CTAs share an SM.  Complex operands keep (re, im) interleaved, one 16-byte fragment load per lane,
 // and each complex tile product is four real DMMAs; conjugation flips the sign of the imaginary
 // fragment in registers.
 //
-// Preconditions are those of the tiled kernel (16-byte aligned bases, ld and stride multiples of
-// 16 bytes); edges are zero-filled on load and predicated on store.
+// Preconditions are those of the tiled kernel: element-aligned operands.  16-byte aligned bases, ld
+// and stride take 16-byte copies (AL = true); a double operand that is only 8-byte aligned (a slice
+// with an odd offset, ld = 257) is copied element by element into the same stage layout
+// (AL = false).  Edges are zero-filled on load and predicated on store.
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -35,10 +41,10 @@ __device__ __forceinline__ void dmma(double& c0, double& c1, double a, double b)
 // Bytes added to every stage row.  A request must spread its fragment rows over all banks: 4 rows
 // of 32 bytes (double, half-warp of 64-bit loads; complex M-major, quarter-warp of 4 k-rows x 2
 // elements) want a 32-byte shift per row, 2 rows of 64 bytes (complex K-major) a 64-byte shift.
-__host__ __device__ constexpr int pad_for(int es, bool kmajor) { return (es == 16 && kmajor) ? 64 : 32; }
+__host__ __device__ constexpr int pad_for(int es, bool kmajor) { return kmajor ? (es == 16 ? 64 : 0) : 32; }
 
 // Asynchronous copy of one operand tile into a pitched stage.  ES = element bytes (8 or 16).
-template <int ES, int BMN, int BK, int THREADS, bool KMAJOR>
+template <int ES, int BMN, int BK, int THREADS, bool KMAJOR, bool AL = true>
 __device__ __forceinline__ void load_tile_pitched(unsigned char* smem, const unsigned char* __restrict__ base,
                                                   long long ld, int MN0, int MN, int k0, int K, int tid) {
   constexpr int V = 16 / ES;  // elements per 16-byte chunk
@@ -51,7 +57,13 @@ __device__ __forceinline__ void load_tile_pitched(unsigned char* smem, const uns
       int valid = (gk < K) ? (MN - gm) : 0;
       valid = valid < 0 ? 0 : (valid > V ? V : valid);
       const unsigned char* src = valid ? base + ((long long)gk * ld + gm) * ES : base;
-      cp_async16(smem + (size_t)kk * PITCH + (size_t)mc * 16, src, valid * ES);
+      unsigned char* dst = smem + (size_t)kk * PITCH + (size_t)mc * 16;
+      if constexpr (AL) {
+        cp_async16(dst, src, valid * ES);
+      } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) cp_async_elem<ES>(dst + e * ES, e < valid ? src + e * ES : src, e < valid ? ES : 0);
+      }
     }
   } else {
     constexpr int CH_PER_ROW = BK / V, CHUNKS = BMN * CH_PER_ROW, PITCH = BK * ES + pad_for(ES, true);
@@ -62,7 +74,14 @@ __device__ __forceinline__ void load_tile_pitched(unsigned char* smem, const uns
       int valid = (gmn < MN) ? (K - gk) : 0;
       valid = valid < 0 ? 0 : (valid > V ? V : valid);
       const unsigned char* src = valid ? base + ((long long)gmn * ld + gk) * ES : base;
-      cp_async16(smem + (size_t)r * PITCH + (size_t)kc * 16, src, valid * ES);
+      // real double: 32-byte group kc / 2 of row r lives at group (kc / 2) ^ (r & 3)
+      unsigned char* dst = smem + (size_t)r * PITCH + (ES == 8 ? (size_t)((((kc >> 1) ^ (r & 3)) << 5) + ((kc & 1) << 4)) : (size_t)kc * 16);
+      if constexpr (AL) {
+        cp_async16(dst, src, valid * ES);
+      } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) cp_async_elem<ES>(dst + e * ES, e < valid ? src + e * ES : src, e < valid ? ES : 0);
+      }
     }
   }
 }
@@ -78,7 +97,7 @@ constexpr int kStagesD = 3, kStagesZ = 3;  // copy-ring depth; 4 gains ~1 % on N
 // HINTS = false is the plain gemm; HINTS = true reads the structure hints of GemmParams (a separate
 // instantiation, so that the plain kernel's code and register allocation stay what they were).
 // WM x WN warps of 32 x 32 each; 16 / (WM * WN) CTAs per SM.
-template <int OPA, int OPB, bool HINTS, int WM, int WN>
+template <int OPA, int OPB, bool HINTS, int WM, int WN, bool AL = true>
 __global__ void __launch_bounds__(32 * WM * WN, 16 / (WM * WN)) gemm_dmma_d_kernel(GemmParams p, int tiles_m, int tiles_n) {
   constexpr int BM = 32 * WM, BN = 32 * WN, BK = 16, STAGES = kStagesD, THREADS = 32 * WM * WN;
   constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
@@ -127,8 +146,8 @@ __global__ void __launch_bounds__(32 * WM * WN, 16 / (WM * WN)) gemm_dmma_d_kern
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
     if (s < KT) {
-      load_tile_pitched<8, BM, BK, THREADS, AK>(As + (size_t)s * A_STAGE, A, p.lda, m0, p.m, s * BK, p.k, tid);
-      load_tile_pitched<8, BN, BK, THREADS, BKM>(Bs + (size_t)s * B_STAGE, B, p.ldb, n0, p.n, s * BK, p.k, tid);
+      load_tile_pitched<8, BM, BK, THREADS, AK, AL>(As + (size_t)s * A_STAGE, A, p.lda, m0, p.m, s * BK, p.k, tid);
+      load_tile_pitched<8, BN, BK, THREADS, BKM, AL>(Bs + (size_t)s * B_STAGE, B, p.ldb, n0, p.n, s * BK, p.k, tid);
     }
     cp_async_commit();
   }
@@ -138,8 +157,9 @@ __global__ void __launch_bounds__(32 * WM * WN, 16 / (WM * WN)) gemm_dmma_d_kern
   const int b_off = BKM ? (wn * 32 + g) * B_PITCH + t * 8 : t * B_PITCH + (wn * 32 + g) * 8;
   constexpr int A_MB = AK ? 8 * A_PITCH : 64;       // next 8 rows of m
   constexpr int B_NB = BKM ? 8 * B_PITCH : 64;      // next 8 columns of n
-  constexpr int A_K4 = AK ? 32 : 4 * A_PITCH;       // next 4 k
-  constexpr int B_K4 = BKM ? 32 : 4 * B_PITCH;
+  constexpr int A_K4 = AK ? 0 : 4 * A_PITCH;        // next 4 k (K-major: the swizzled group below)
+  constexpr int B_K4 = BKM ? 0 : 4 * B_PITCH;
+  const int ksw = (g & 3) << 5;                      // K-major rows: 4-k group q is stored at q ^ (row & 3)
 
   for (int kt = 0; kt < KT; ++kt) {
     cp_async_wait<STAGES - 2>();
@@ -148,8 +168,8 @@ __global__ void __launch_bounds__(32 * WM * WN, 16 / (WM * WN)) gemm_dmma_d_kern
       const int nxt = kt + STAGES - 1;
       if (nxt < KT) {
         const int s = nxt % STAGES;
-        load_tile_pitched<8, BM, BK, THREADS, AK>(As + (size_t)s * A_STAGE, A, p.lda, m0, p.m, nxt * BK, p.k, tid);
-        load_tile_pitched<8, BN, BK, THREADS, BKM>(Bs + (size_t)s * B_STAGE, B, p.ldb, n0, p.n, nxt * BK, p.k, tid);
+        load_tile_pitched<8, BM, BK, THREADS, AK, AL>(As + (size_t)s * A_STAGE, A, p.lda, m0, p.m, nxt * BK, p.k, tid);
+        load_tile_pitched<8, BN, BK, THREADS, BKM, AL>(Bs + (size_t)s * B_STAGE, B, p.ldb, n0, p.n, nxt * BK, p.k, tid);
       }
       cp_async_commit();
     }
@@ -158,10 +178,11 @@ __global__ void __launch_bounds__(32 * WM * WN, 16 / (WM * WN)) gemm_dmma_d_kern
 #pragma unroll
     for (int k4 = 0; k4 < BK / 4; ++k4) {
       double af[4], bf[4];
+      const int kgrp = ksw ^ (k4 << 5);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) af[i] = *reinterpret_cast<const double*>(as + k4 * A_K4 + i * A_MB);
+      for (int i = 0; i < 4; ++i) af[i] = *reinterpret_cast<const double*>(as + k4 * A_K4 + (AK ? kgrp : 0) + i * A_MB);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) bf[j] = *reinterpret_cast<const double*>(bs + k4 * B_K4 + j * B_NB);
+      for (int j = 0; j < 4; ++j) bf[j] = *reinterpret_cast<const double*>(bs + k4 * B_K4 + (BKM ? kgrp : 0) + j * B_NB);
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -345,7 +366,12 @@ int launch_d_tile(const GemmParams& p, cudaStream_t stream) {
   constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
   constexpr size_t smem =
       kStagesD * (size_t)(pitched_stage_bytes<8, 32 * WM, 16, AK>() + pitched_stage_bytes<8, 32 * WN, 16, BKM>());
-  static thread_local int configured_for = -1, configured_for_hints = -1;
+  static thread_local int configured_for = -1, configured_for_hints = -1, configured_for_elem = -1;
+  if (!operands_aligned_to(p, 8, 16)) {  // element-granular copies (plain gemm only: tiled_supported saw to that)
+    if (has_hints(p) || p.splits > 1) return BLB200_E_UNSUPPORTED;
+    return launch_kernel(gemm_dmma_d_kernel<OPA, OPB, false, WM, WN, false>, smem, p, 32 * WM, 32 * WN, stream,
+                         &configured_for_elem, 32 * WM * WN);
+  }
   if (has_hints(p))
     return launch_kernel(gemm_dmma_d_kernel<OPA, OPB, true, WM, WN>, smem, p, 32 * WM, 32 * WN, stream,
                          &configured_for_hints, 32 * WM * WN);

@@ -1,0 +1,318 @@
+// FP64 tensor-core tiles for real double, fed by TMA: the plain strided-batched DGEMM of the mid and
+// large shapes (256^3, 1024^3).  Same CTA shape as the cp.async DMMA kernel — 64 x 64 output, four
+// warps of 32 x 32 as 4 x 4 mma.sync m8n8k4 tiles, four CTAs per SM — but the operand tiles arrive by
+// cp.async.bulk.tensor from 3-D tensor maps (rows x columns x batch item) over the caller's own
+// column-major storage, complete on one mbarrier per stage, and are laid out by the 128-byte
+// swizzle.  What that removes from the 128 threads of a CTA: every per-thread copy instruction with
+// its address and edge arithmetic (edges are zero-filled by the tensor map's bounds), the
+// cp.async group bookkeeping, and the row padding of the stages (a stage is 16 KiB for every op
+// pair).  One thread issues two to eight box copies per k-tile.
+//
+// Stage layout (BK = 16 doubles = 128 bytes, the widest row the 128-byte swizzle allows):
+//   K-major operand (A under op T, B under op N): one box of 16 k x 64 rows; stage row r holds the
+//     16 k of matrix row r, its 16-byte chunks XORed with (r & 7).
+//   M-major operand (A under op N, B under op T): four boxes of 16 rows x 16 k, 2 KiB each; box row
+//     kk holds 16 consecutive matrix rows at k = kk, chunks XORed with (kk & 7).
+// The DMMA fragment of lane (g = lane >> 2, t = lane & 3) is element (row g, k t) of an 8 x 4 tile.
+// With all stage rows exactly 128 bytes apart, a half-warp request (4 g x 4 t) is conflict-free only
+// if the XOR spreads it over all eight chunks, which fixes which matrix rows the eight g-lanes of a
+// tile must own.  Both assignments are permutations of the warp's 32 rows over (g, tile i):
+//   K-major:  row = 16 (i >> 1) + 8 (g >> 2) + 2 (g & 3) + (i & 1)        -> row & 7 = 2 (g & 3) + (i & 1)
+//   M-major:  row = 16 (i >> 1) + 8 ((g >> 1) & 1) + 4 (i & 1) + 2 (g >> 2) + (g & 1)
+// Every tile product still multiplies rows of op(A) with columns of op(B) over the same k, so the
+// result is the same sum in the same order as the other DMMA kernel; only which lane holds which
+// element of C differs, and the epilogue applies the same permutations.
+//
+// Preconditions (dmma_tma_supported): real double, no structure hints / per-item dims / split-K,
+// 16-byte aligned bases, even ld and batch strides (tensor-map strides are multiples of 16 bytes),
+// positive batch strides.  No load with cluster multicast is used; the maps cover this GPU's memory.
+#include <cuda.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace blb200 {
+namespace {
+
+enum WaitCode { kDmmaTmaWaitFull = 401 };
+
+constexpr int kBM = 64, kBN = 64, kBK = 16, kStages = 3, kThreads = 128;
+constexpr int kOperandBytes = 64 * kBK * 8;       // 8 KiB
+constexpr int kStageBytes = 2 * kOperandBytes;    // A tile + B tile
+
+__device__ __forceinline__ void dmma(double& c0, double& c1, double a, double b) {
+  asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+               : "+d"(c0), "+d"(c1)
+               : "d"(a), "d"(b));
+}
+
+__device__ __forceinline__ void tma_load_3d(void* dst_smem, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
+          "r"(smem_u32(dst_smem)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// Row of the warp's 32 owned by lane group g in tile i (see the file comment).
+__device__ __forceinline__ int perm_kmajor(int g, int i) { return 16 * (i >> 1) + 8 * (g >> 2) + 2 * (g & 3) + (i & 1); }
+__device__ __forceinline__ int perm_mmajor(int g, int i) {
+  return 16 * (i >> 1) + 8 * ((g >> 1) & 1) + 4 * (i & 1) + 2 * (g >> 2) + (g & 1);
+}
+
+// Byte offset, inside an operand tile, of this lane's fragment element for tile 0 and k-step 0 of
+// warp row-block w; fragment_offset() below moves it to tile i and k-step k4.
+template <bool KMAJOR>
+__device__ __forceinline__ int fragment_base(int w, int g, int t) {
+  if (KMAJOR) return (32 * w + 2 * (g & 3) + 8 * (g >> 2)) * 128 + ((((t >> 1) | ((g & 3) << 1))) << 4) + (t & 1) * 8;
+  const int c0 = (g >> 2) + 4 * ((g >> 1) & 1);
+  return 2 * w * 2048 + t * 128 + ((c0 ^ t) << 4) + (g & 1) * 8;
+}
+template <bool KMAJOR>
+__device__ __forceinline__ int fragment_offset(int base, int i, int k4) {
+  if (KMAJOR) return (base ^ ((i & 1) << 4) ^ (k4 << 5)) + (i & 1) * 128 + (i >> 1) * 2048;
+  return (base ^ ((i & 1) << 5) ^ ((k4 & 1) << 6)) + (i >> 1) * 2048 + k4 * 512;
+}
+
+template <int OPA, int OPB>
+__global__ void __launch_bounds__(kThreads, 4)
+    gemm_dmma_tma_d_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                           double* __restrict__ C, long long sc, long long ldc, int m, int n, int k, int tiles_m,
+                           int tiles_n, double alpha, double beta) {
+  constexpr bool AK = (OPA != BLB200_N);   // A stored k x m: k fastest
+  constexpr bool BKM = (OPB == BLB200_N);  // B stored k x n: k fastest
+  extern __shared__ unsigned char smem_raw[];
+  // the swizzle is a function of the shared-memory address: tiles must start on 1024-byte boundaries
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)kStages * kStageBytes);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int wm = warp & 1, wn = warp >> 1;
+
+  const long long tiles_per_item = (long long)tiles_m * tiles_n;
+  const long long tile = blockIdx.x;
+  const int item = (int)(tile / tiles_per_item);
+  const int rem = (int)(tile - (long long)item * tiles_per_item);
+  const int m0 = (rem % tiles_m) * kBM, n0 = (rem / tiles_m) * kBN;
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  const int KT = (k + kBK - 1) / kBK;
+  auto issue = [&](int s, int kt) {  // one thread: the copies of k-tile kt into stage s
+    unsigned char* st = smem + (size_t)s * kStageBytes;
+    const int k0 = kt * kBK;
+    mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
+    if (AK) {
+      tma_load_3d(st, &map_a, k0, m0, item, &full_bar[s]);
+    } else {
+#pragma unroll
+      for (int b = 0; b < 4; ++b) tma_load_3d(st + b * 2048, &map_a, m0 + 16 * b, k0, item, &full_bar[s]);
+    }
+    if (BKM) {
+      tma_load_3d(st + kOperandBytes, &map_b, k0, n0, item, &full_bar[s]);
+    } else {
+#pragma unroll
+      for (int b = 0; b < 4; ++b) tma_load_3d(st + kOperandBytes + b * 2048, &map_b, n0 + 16 * b, k0, item, &full_bar[s]);
+    }
+  };
+  if (tid == 0)
+    for (int s = 0; s < kStages - 1 && s < KT; ++s) issue(s, s);
+
+  double acc[4][4][2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = 0.0;
+
+  const int a_base = fragment_base<AK>(wm, g, t);
+  const int b_base = fragment_base<BKM>(wn, g, t);
+
+  int issued = KT < kStages - 1 ? KT : kStages - 1;  // k-tiles whose copies have been issued (thread 0's view)
+  int kt = 0;
+  bool lost = false;
+  for (; kt < KT; ++kt) {
+    const int s = kt % kStages;
+    const bool ok = mbar_wait(&full_bar[s], (uint32_t)(kt / kStages) & 1u, kDmmaTmaWaitFull);
+    // one barrier: every warp has left stage (kt - 1) % kStages, and all threads agree on `ok`
+    if (__syncthreads_or(!ok)) {
+      lost = true;
+      break;
+    }
+    if (tid == 0 && issued < KT) {
+      fence_async_smem();
+      issue(issued % kStages, issued);
+      ++issued;
+    }
+    const unsigned char* as = smem + (size_t)s * kStageBytes;
+    const unsigned char* bs = as + kOperandBytes;
+#pragma unroll
+    for (int k4 = 0; k4 < kBK / 4; ++k4) {
+      double af[4], bf[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) af[i] = *reinterpret_cast<const double*>(as + fragment_offset<AK>(a_base, i, k4));
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bf[j] = *reinterpret_cast<const double*>(bs + fragment_offset<BKM>(b_base, j, k4));
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dmma(acc[i][j][0], acc[i][j][1], af[i], bf[j]);
+    }
+  }
+  if (lost) {
+    // A copy never arrived (recorded in the status word).  Do not leave while later copies may still
+    // land in this CTA's shared memory: give each issued stage a short, bounded chance to complete.
+    if (tid == 0)
+      for (int q = kt + 1; q < issued; ++q)
+        mbar_wait_limit(&full_bar[q % kStages], (uint32_t)(q / kStages) & 1u, kDmmaTmaWaitFull, 1u << 12);
+    return;
+  }
+
+  const bool beta_zero = beta == 0.0;
+  C += (long long)item * sc;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int cl = BKM ? perm_kmajor(2 * t + e, j) : perm_mmajor(2 * t + e, j);
+      const int col = n0 + 32 * wn + cl;
+      if (col >= n) continue;
+      double* ccol = C + (long long)col * ldc;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = m0 + 32 * wm + (AK ? perm_kmajor(g, i) : perm_mmajor(g, i));
+        if (row >= m) continue;
+        double out = alpha * acc[i][j][e];
+        if (!beta_zero) out = fma(beta, ccol[row], out);
+        ccol[row] = out;
+      }
+    }
+}
+
+// cuTensorMapEncodeTiled, resolved from the driver at run time (no link-time libcuda dependency).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return (EncodeTiledFn)p;
+  }();
+  return fn;
+}
+
+// 3-D map over a column-major double operand: dims (rows, cols, items), strides (ld, item stride).
+// KMAJOR operands (the contraction index runs along the stored rows) are fetched as one 16 x 64 box,
+// the others as 16 x 16 boxes; both 128 bytes wide, 128-byte swizzle, zero fill past the edges.
+int make_operand_map(CUtensorMap* map, const void* base, int rows, int cols, long long ld, long long stride, int batch,
+                     bool kmajor) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return BLB200_E_INTERNAL;
+  const cuuint64_t dims[3] = {(cuuint64_t)rows, (cuuint64_t)cols, (cuuint64_t)(batch > 0 ? batch : 1)};
+  const long long item_stride = batch > 1 ? stride : ld * (long long)cols;
+  const cuuint64_t strides[2] = {(cuuint64_t)ld * 8, (cuuint64_t)item_stride * 8};
+  const cuuint32_t box[3] = {16, kmajor ? 64u : 16u, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? BLB200_OK : BLB200_E_INTERNAL;
+}
+
+// Tensor maps are pure functions of (base, shape, ld, stride, batch, box kind): a small per-thread
+// cache saves the driver call when the same operand is multiplied again.
+struct OperandMapCache {
+  struct Entry {
+    const void* base = nullptr;
+    int rows = 0, cols = 0, batch = 0;
+    long long ld = 0, stride = 0;
+    bool kmajor = false, valid = false;
+    alignas(64) CUtensorMap map;
+  };
+  static constexpr int kEntries = 16;
+  Entry e[kEntries];
+  int next = 0;
+  int get(CUtensorMap* out, const void* base, int rows, int cols, long long ld, long long stride, int batch, bool kmajor) {
+    for (int i = 0; i < kEntries; ++i) {
+      const Entry& c = e[i];
+      if (c.valid && c.base == base && c.rows == rows && c.cols == cols && c.ld == ld && c.stride == stride &&
+          c.batch == batch && c.kmajor == kmajor) {
+        memcpy(out, &c.map, sizeof(CUtensorMap));
+        return BLB200_OK;
+      }
+    }
+    Entry& slot = e[next];
+    next = (next + 1) % kEntries;
+    slot.valid = false;
+    const int rc = make_operand_map(&slot.map, base, rows, cols, ld, stride, batch, kmajor);
+    if (rc != BLB200_OK) return rc;
+    slot.base = base; slot.rows = rows; slot.cols = cols; slot.ld = ld; slot.stride = stride;
+    slot.batch = batch; slot.kmajor = kmajor; slot.valid = true;
+    memcpy(out, &slot.map, sizeof(CUtensorMap));
+    return BLB200_OK;
+  }
+};
+
+template <int OPA, int OPB>
+int launch_op(const GemmParams& p, cudaStream_t stream) {
+  constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
+  const size_t smem = (size_t)kStages * kStageBytes + kStages * sizeof(uint64_t) + 1024;
+  const int tiles_m = (p.m + kBM - 1) / kBM, tiles_n = (p.n + kBN - 1) / kBN;
+  const long long total = (long long)tiles_m * tiles_n * p.batch;
+  if (total > 0x7fffffffLL) return BLB200_E_UNSUPPORTED;
+  alignas(64) CUtensorMap map_a, map_b;
+  static thread_local OperandMapCache maps;
+  const int a_rows = AK ? p.k : p.m, a_cols = AK ? p.m : p.k;
+  const int b_rows = BKM ? p.k : p.n, b_cols = BKM ? p.n : p.k;
+  int rc = maps.get(&map_a, p.a, a_rows, a_cols, p.lda, p.sa, p.batch, AK);
+  if (rc != BLB200_OK) return rc;
+  rc = maps.get(&map_b, p.b, b_rows, b_cols, p.ldb, p.sb, p.batch, BKM);
+  if (rc != BLB200_OK) return rc;
+  auto kern = gemm_dmma_tma_d_kernel<OPA, OPB>;
+  static thread_local int configured_for = -1;
+  int cur = 0;
+  cudaGetDevice(&cur);
+  if (configured_for != cur) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured_for = cur;
+  }
+  kern<<<(unsigned)total, kThreads, smem, stream>>>(map_a, map_b, (double*)p.c, p.sc, p.ldc, p.m, p.n, p.k, tiles_m,
+                                                   tiles_n, p.alpha[0], p.beta[0]);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+int dmma_tma_device_status(int* out) { return read_device_status_word(out); }
+int dmma_tma_device_status_clear() { return clear_device_status_word(); }
+
+bool dmma_tma_supported(const GemmParams& p, int dtype) {
+  if (dtype != BLB200_D) return false;
+  if (p.k < 1 || (p.m <= 32 && p.n <= 32)) return false;
+  if (has_hints(p) || p.splits > 1) return false;
+  if (!operands_aligned_to(p, 8, 16)) return false;
+  if (p.batch > 1 && (p.sa <= 0 || p.sb <= 0)) return false;  // a broadcast operand has no tensor-map stride
+  return encode_tiled_fn() != nullptr;
+}
+
+int launch_dmma_tma(const GemmParams& p, int dtype, cudaStream_t stream) {
+  if (!dmma_tma_supported(p, dtype)) return BLB200_E_UNSUPPORTED;
+  int rc = BLB200_E_INTERNAL;
+#define BLB_OP(A_, B_) \
+  if (p.op_a == A_ && p.op_b == B_) rc = launch_op<A_, B_>(p, stream);
+  BLB_OP(0, 0) BLB_OP(0, 1) BLB_OP(1, 0) BLB_OP(1, 1)
+#undef BLB_OP
+  if (rc == BLB200_OK) note_launch("dmma_tma");
+  return rc;
+}
+
+}  // namespace blb200

@@ -250,6 +250,7 @@ int launch_one(const GemmParams& p, cudaStream_t stream) {
 bool sgemm128_supported(const GemmParams& p, int dtype) {
   if (dtype != BLB200_S || p.op_a != BLB200_N) return false;
   if (p.m < 64 || p.n < 64) return false;  // smaller outputs waste most of a 128 x 128 tile
+  if (!operands_aligned_to(p, 4, 16)) return false;  // 16-byte copies only; other operands take the tiled kernel
   return tiled_supported(p, dtype);
 }
 

@@ -27,7 +27,7 @@
 // small64: m = n = k = 64, ld = 64, same alignment rules.  Two warps share one matrix
 // (warp half hw owns columns 32hw..32hw+31, each lane an 8 x 8 block: 16 fragment floats per 64
 // FMAs, so the FP32 pipe rather than shared memory sets the pace).  The ring holds half-K slots of
-// 16 KiB (A half + B half); each of the 4 pairs owns 3 slots (6 pairs: 2 slots).  An M-major / N-major half is one
+// 16 KiB (A half + B half); each of the 6 pairs owns 2 slots.  An M-major / N-major half is one
 // contiguous 8 KiB run (untiled bulk copy).  A K-major half is 64 rows of 128 bytes, 256 bytes
 // apart in memory: it is fetched by one tiled TMA copy (cp.async.bulk.tensor.3d, box 32 x 64 x 1)
 // with the 128-byte swizzle, which XORs the 16-byte chunk index with (row & 7); with rows (or
@@ -47,11 +47,6 @@ namespace {
 enum WaitCode { kWaitFull = 101 };
 
 inline bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
-
-int env_int(const char* name, int dflt) {
-  const char* v = getenv(name);
-  return (v && *v) ? atoi(v) : dflt;
-}
 
 // =================================================================================================
 // small32
@@ -718,13 +713,11 @@ int launch_small64(const GemmParams& p, int dtype, cudaStream_t stream) {
   const bool ak = p.op_a != BLB200_N;
   const bool bk = p.op_b == BLB200_N;
   const bool hc = (float)p.beta[0] != 0.f;
-  static const int pairs = env_int("BLB200_SMALL64_PAIRS", 4);  // tuning knob: 4 or 6 warp pairs
+  // Six warp pairs (three warps per scheduler) with two slots each: 52.1 TFLOP/s on 10 000 items
+  // (NT 55.3) against 50.8 (51.9) for four pairs with three slots each.
   int rc;
-#define BLB_CASE(a, b)                                                                               \
-  if (ak == a && bk == b) {                                                                          \
-    if (pairs == 6) rc = hc ? launch64<6, a, b, true>(p, stream) : launch64<6, a, b, false>(p, stream); \
-    else rc = hc ? launch64<4, a, b, true>(p, stream) : launch64<4, a, b, false>(p, stream);         \
-  } else
+#define BLB_CASE(a, b) \
+  if (ak == a && bk == b) rc = hc ? launch64<6, a, b, true>(p, stream) : launch64<6, a, b, false>(p, stream); else
   BLB_CASE(false, false) BLB_CASE(false, true) BLB_CASE(true, false) BLB_CASE(true, true) { rc = BLB200_E_INTERNAL; }
 #undef BLB_CASE
   if (rc == BLB200_OK) note_launch("small64");

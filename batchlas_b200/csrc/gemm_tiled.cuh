@@ -11,8 +11,11 @@
 // V = 16 / sizeof(T).  A warp is 8 (m) x 4 (n) lanes, so an A request touches 128 contiguous bytes
 // and a B request 64, both conflict-free.  Conjugation is applied to fragments in registers.
 //
-// Preconditions (checked by tiled_supported, otherwise the generic kernel runs): 16-byte aligned
-// bases, and ld * sizeof(T) and stride * sizeof(T) multiples of 16.  m, n, k are arbitrary: edge
+// Two load policies, one kernel body (as BatchLAS switches policy inside its tiled kernel,
+// src/sycl/gemm/load_policies.hh:18-34): AL = true needs 16-byte aligned bases and ld * sizeof(T),
+// stride * sizeof(T) multiples of 16, and moves 16 bytes per copy; AL = false needs only element
+// alignment (a slice with an odd offset, ld = 258) and moves one element per copy into the same
+// shared-memory layout, with scalar C accesses in the epilogue.  m, n, k are arbitrary: edge
 // chunks are zero-filled through the copy's source-size operand and the epilogue is predicated.
 //
 // Algorithmic traffic per item: A and B once each, C written once and read once iff beta != 0;
@@ -58,7 +61,14 @@ __device__ __forceinline__ void unpack16(const uint4& raw, T (&out)[16 / sizeof(
 // Issue the async copies of one operand tile.
 //   MN0: first m (or n) index of the tile, MN: matrix extent along it, BMN: tile extent,
 //   k0: first k of the tile, K: extent along k, G: thread groups along this dimension.
-template <typename T, int BMN, int BK, int G, int THREADS, bool KMAJOR>
+template <int ES>
+__device__ __forceinline__ void copy_chunk_by_elements(unsigned char* dst, const unsigned char* src, int valid) {
+  constexpr int V = 16 / ES;
+#pragma unroll
+  for (int e = 0; e < V; ++e) cp_async_elem<ES>(dst + e * ES, e < valid ? src + e * ES : src, e < valid ? ES : 0);
+}
+
+template <typename T, int BMN, int BK, int G, int THREADS, bool KMAJOR, bool AL = true>
 __device__ __forceinline__ void load_tile(unsigned char* smem, const T* __restrict__ base, long long ld,
                                           int MN0, int MN, int k0, int K, int tid) {
   constexpr int V = 16 / (int)sizeof(T);
@@ -71,7 +81,9 @@ __device__ __forceinline__ void load_tile(unsigned char* smem, const T* __restri
       int valid = (gk < K) ? (MN - gm) : 0;
       valid = valid < 0 ? 0 : (valid > V ? V : valid);
       const T* src = valid ? base + (long long)gk * ld + gm : base;
-      cp_async16(smem + (size_t)kk * (BMN * sizeof(T)) + (size_t)mc * 16, src, valid * (int)sizeof(T));
+      unsigned char* dst = smem + (size_t)kk * (BMN * sizeof(T)) + (size_t)mc * 16;
+      if constexpr (AL) cp_async16(dst, src, valid * (int)sizeof(T));
+      else copy_chunk_by_elements<(int)sizeof(T)>(dst, (const unsigned char*)src, valid);
     }
   } else {
     constexpr int CH_PER_ROW = BK / V, CHUNKS = BMN * CH_PER_ROW, PITCH = BK * (int)sizeof(T) + 16;
@@ -85,7 +97,9 @@ __device__ __forceinline__ void load_tile(unsigned char* smem, const T* __restri
       const int v = r / (G * V), rem = r % (G * V), g = rem / V, e = rem % V;
       const int slot = (v * V + e) * G + g;
       const T* src = valid ? base + (long long)gmn * ld + gk : base;
-      cp_async16(smem + (size_t)slot * PITCH + (size_t)kc * 16, src, valid * (int)sizeof(T));
+      unsigned char* dst = smem + (size_t)slot * PITCH + (size_t)kc * 16;
+      if constexpr (AL) cp_async16(dst, src, valid * (int)sizeof(T));
+      else copy_chunk_by_elements<(int)sizeof(T)>(dst, (const unsigned char*)src, valid);
     }
   }
 }
@@ -124,7 +138,7 @@ __device__ __forceinline__ void read_frag(const unsigned char* smem, int g, int 
 
 // HINTS = false is the plain gemm; HINTS = true reads the structure hints of GemmParams (a separate
 // instantiation, so that the plain kernel's code and register allocation stay what they were).
-template <typename T, typename Cfg, int OPA, int OPB, int MIN_BLOCKS, bool HINTS>
+template <typename T, typename Cfg, int OPA, int OPB, int MIN_BLOCKS, bool HINTS, bool AL = true>
 __global__ void __launch_bounds__(Cfg::THREADS, MIN_BLOCKS)
     gemm_tiled_kernel(GemmParams p, int tiles_m, int tiles_n) {
   constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, TM = Cfg::TM, TN = Cfg::TN, V = Cfg::V;
@@ -177,8 +191,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, MIN_BLOCKS)
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
     if (s < KT) {
-      load_tile<T, BM, BK, GM, THREADS, AK>(As + (size_t)s * A_STAGE, A, p.lda, m0, p.m, s * BK, p.k, tid);
-      load_tile<T, BN, BK, GN, THREADS, BKM>(Bs + (size_t)s * B_STAGE, B, p.ldb, n0, p.n, s * BK, p.k, tid);
+      load_tile<T, BM, BK, GM, THREADS, AK, AL>(As + (size_t)s * A_STAGE, A, p.lda, m0, p.m, s * BK, p.k, tid);
+      load_tile<T, BN, BK, GN, THREADS, BKM, AL>(Bs + (size_t)s * B_STAGE, B, p.ldb, n0, p.n, s * BK, p.k, tid);
     }
     cp_async_commit();
   }
@@ -190,8 +204,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, MIN_BLOCKS)
       const int nxt = kt + STAGES - 1;
       if (nxt < KT) {
         const int s = nxt % STAGES;
-        load_tile<T, BM, BK, GM, THREADS, AK>(As + (size_t)s * A_STAGE, A, p.lda, m0, p.m, nxt * BK, p.k, tid);
-        load_tile<T, BN, BK, GN, THREADS, BKM>(Bs + (size_t)s * B_STAGE, B, p.ldb, n0, p.n, nxt * BK, p.k, tid);
+        load_tile<T, BM, BK, GM, THREADS, AK, AL>(As + (size_t)s * A_STAGE, A, p.lda, m0, p.m, nxt * BK, p.k, tid);
+        load_tile<T, BN, BK, GN, THREADS, BKM, AL>(Bs + (size_t)s * B_STAGE, B, p.ldb, n0, p.n, nxt * BK, p.k, tid);
       }
       cp_async_commit();
     }
@@ -238,7 +252,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, MIN_BLOCKS)
       const int row = m0 + v * (GM * V) + g * V;
       // with a triangular output the vector access is used only strictly inside the wanted triangle
       const bool whole = !HINTS || p.out_tri == 0 || (p.out_tri == 1 ? row > col : row + V - 1 < col);
-      if (row + V <= p.m && whole) {
+      if (AL && row + V <= p.m && whole) {
         union {
           uint4 u;
           T t[V];
@@ -271,14 +285,14 @@ __global__ void __launch_bounds__(Cfg::THREADS, MIN_BLOCKS)
   }
 }
 
-template <typename T, typename Cfg, int OPA, int OPB, int MIN_BLOCKS, bool HINTS>
+template <typename T, typename Cfg, int OPA, int OPB, int MIN_BLOCKS, bool HINTS, bool AL = true>
 int launch_cfg(const GemmParams& p, cudaStream_t stream) {
   constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
   constexpr size_t smem = (size_t)Cfg::STAGES * (stage_bytes<T>(Cfg::BM, Cfg::BK, AK) + stage_bytes<T>(Cfg::BN, Cfg::BK, BKM));
   const int tiles_m = (p.m + Cfg::BM - 1) / Cfg::BM, tiles_n = (p.n + Cfg::BN - 1) / Cfg::BN;
   const long long total = (long long)tiles_m * tiles_n * p.batch;
   if (total > 0x7fffffffLL) return BLB200_E_UNSUPPORTED;
-  auto kern = gemm_tiled_kernel<T, Cfg, OPA, OPB, MIN_BLOCKS, HINTS>;
+  auto kern = gemm_tiled_kernel<T, Cfg, OPA, OPB, MIN_BLOCKS, HINTS, AL>;
   static thread_local int configured_for = -1;
   int cur = 0;
   cudaGetDevice(&cur);
@@ -295,10 +309,18 @@ template <typename T, typename Cfg, int MIN_BLOCKS>
 int launch_ops(const GemmParams& p, cudaStream_t stream) {
   const int oa = p.op_a, ob = p.op_b;
   const bool hints = has_hints(p);
+  // element-granular copies for operands that are not 16-byte aligned (plain gemm only; sizeof(T)
+  // == 16 is always on the 16-byte policy)
+  const bool al = sizeof(T) == 16 || operands_aligned_to(p, (long long)sizeof(T), 16);
+  if (!al && (hints || p.splits > 1)) return BLB200_E_UNSUPPORTED;
 #define BLB_OP(A_, B_)                                                                    \
-  if (oa == A_ && ob == B_)                                                               \
+  if (oa == A_ && ob == B_) {                                                             \
+    if constexpr (sizeof(T) < 16) {                                                       \
+      if (!al) return launch_cfg<T, Cfg, A_, B_, MIN_BLOCKS, false, false>(p, stream);    \
+    }                                                                                     \
     return hints ? launch_cfg<T, Cfg, A_, B_, MIN_BLOCKS, true>(p, stream)                \
-                 : launch_cfg<T, Cfg, A_, B_, MIN_BLOCKS, false>(p, stream);
+                 : launch_cfg<T, Cfg, A_, B_, MIN_BLOCKS, false>(p, stream);              \
+  }
   BLB_OP(0, 0) BLB_OP(0, 1) BLB_OP(1, 0) BLB_OP(1, 1)
   if (Scalar<T>::is_complex) {
     BLB_OP(0, 2) BLB_OP(1, 2) BLB_OP(2, 0) BLB_OP(2, 1) BLB_OP(2, 2)

@@ -104,6 +104,15 @@ __device__ __forceinline__ void cp_async16(void* dst_smem, const void* src_gmem,
                "r"(src_bytes)
                : "memory");
 }
+// BYTES-sized (4, 8 or 16) async copy for operands that are only element-aligned; src_bytes = 0
+// zero-fills.  Both addresses must be BYTES-aligned.
+template <int BYTES>
+__device__ __forceinline__ void cp_async_elem(void* dst_smem, const void* src_gmem, uint32_t src_bytes) {
+  static_assert(BYTES == 4 || BYTES == 8 || BYTES == 16, "cp.async copies 4, 8 or 16 bytes");
+  asm volatile("cp.async.ca.shared.global [%0], [%1], %2, %3;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem), "n"(BYTES),
+               "r"(src_bytes)
+               : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {

@@ -123,6 +123,23 @@ def gemm_host(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, alpha=1.0, beta
     return C
 
 
+def gemm_host_multi(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, alpha=1.0, beta=0.0,
+                    transA: Transpose = Transpose.NoTrans, transB: Transpose = Transpose.NoTrans,
+                    devices=None, chunk_items: int = 0) -> torch.Tensor:
+    """gemm_host over several GPUs of the box in one call: contiguous batch ranges, one host thread
+    and one copy/compute pipeline per GPU, each writing its own slice of C.  `devices` defaults to
+    every visible GPU.  Synchronous; returns C."""
+    import ctypes
+    if A.is_cuda or B.is_cuda or C.is_cuda:
+        raise RuntimeError("gemm_host_multi takes host tensors")
+    if devices is None:
+        devices = list(range(torch.cuda.device_count()))
+    desc = _desc_from_tensors(A, B, C, alpha, beta, transA, transB, "auto")
+    arr = (ctypes.c_int32 * len(devices))(*devices)
+    check(load().blb200_gemm_strided_batched_host_multi(desc, arr, len(devices), chunk_items))
+    return C
+
+
 def fill(t: torch.Tensor, seed: int, tensor_id: int, dist: str = "uniform", scale: float = 1.0,
          first_index: int = 0) -> torch.Tensor:
     """Fill contiguous CUDA tensor `t` from the library's counter-based generator."""

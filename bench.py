@@ -827,9 +827,11 @@ def run_case(args):
         c = configs()[name]
     ops = [tuple(op)] if op else c["ops"]
     batch = args.batch or c["batch"]
+    if args.ld_extra:  # e.g. 1: leading dimensions that are not multiples of 16 bytes (element-granular copies)
+        c = dict(c, pad=c["pad"] + args.ld_extra)
     torch.cuda.set_device(0)
     tens, mt = alloc_config(bl, torch, c, batch, 0, torch.device("cuda", 0))
-    out = {"case": name, "batch": batch, "ops": {}}
+    out = {"case": name, "batch": batch, "ld_extra": args.ld_extra, "ops": {}}
     for o in ops:
         d = desc_for(bl, c, o, tens, mt, batch, kernel=args.kernel)
         launch = lambda: bl.gemm_strided_batched(d)
@@ -1020,6 +1022,7 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="batch override for --case")
     ap.add_argument("--beta", type=float, default=-0.5, help="beta of a --case given as a shape (DTYPE MxNxK, e.g. d32x32x32:TN)")
     ap.add_argument("--kernel", default="auto", help="forced kernel for --case")
+    ap.add_argument("--ld-extra", type=int, default=0, help="extra elements on every leading dimension of a --case")
     ap.add_argument("--hetero", action="store_true", help="time heterogeneous batches on the reference's pattern (1 GPU)")
     ap.add_argument("--aux", action="store_true", help="time gemv and the elementwise helpers against HBM bandwidth (1 GPU)")
     ap.add_argument("--aux-gemv", default="", help="with --aux: only this gemv case, DTYPE,M,N,BATCH (e.g. s,32,32,100000)")

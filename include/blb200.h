@@ -52,7 +52,8 @@ enum {
   BLB200_K_TILED = 4,   /* register-blocked FFMA/DFMA smem tiles fed by 16-byte async copies    */
   BLB200_K_DMMA = 5,    /* FP64 tensor-core (mma.sync m8n8k4) tiles, double and complex<double> */
   BLB200_K_SGEMM128 = 6, /* float, A not transposed: 128x128x32 tiles, 8x8 blocks, packed FP32 FMA */
-  BLB200_K_SMALL_RING = 7 /* any dtype, packed items up to 32x32 (k <= 64): whole items per warp, TMA ring */
+  BLB200_K_SMALL_RING = 7, /* any dtype, packed items up to 32x32 (k <= 64): whole items per warp, TMA ring */
+  BLB200_K_DMMA_TMA = 8 /* double: the DMMA tiles fed by tensor-map TMA copies (128-byte swizzle) instead of cp.async */
 };
 /* Split-K has no kernel id: it needs scratch, which only its own entry points below receive. */
 
@@ -146,13 +147,31 @@ int blb200_gemm_splitk_static(const blb200_gemm_desc* desc, int32_t splits, void
 
 /* Same operation with a/b/c HOST pointers (pinned for full speed; pageable works, slower).
  * The batch is cut into chunks; chunk i+1's host->device copies and chunk i-1's device->host
- * copy overlap chunk i's kernel on three streams of `device`.  Device staging comes from the
- * device's stream-ordered memory pool and is returned to it before the call returns.
+ * copy overlap chunk i's kernel on three streams of `device`.  The streams and a memory pool of
+ * the library's own (cudaMemPoolCreate; the application's default pool is not touched) are made
+ * on the first call for a device and kept; device staging is taken from that pool and returned to
+ * it before the call returns, so later calls reuse it.  One call at a time per device (calls for
+ * the same device serialise; different devices run side by side).
  * Synchronous: C is complete in host memory on return.  This is the path that stands in for
  * the reference's host-visible (USM shared) Matrix storage (BatchLAS src/matrix.cc:150-166),
  * where operands live on the host side and move to the GPU on use.
  * `chunk_items` = batch items per chunk, 0 = choose automatically. */
 int blb200_gemm_strided_batched_host(const blb200_gemm_desc* desc, int device, int32_t chunk_items);
+
+/* One call over several GPUs of the box: batch items are independent, so GPU g of G takes the
+ * contiguous item range [floor(g*B/G), floor((g+1)*B/G)) (blb200_shard_range), runs the pipeline
+ * above on its slice of the caller's host A, B, C from a host thread of its own, and writes its
+ * disjoint slice of C.  No data crosses between GPUs; the only gather is each GPU's device->host
+ * copy into the caller's C.  `devices` lists n_devices distinct CUDA device ordinals.  Synchronous;
+ * returns the first non-zero status of any shard.  This is the multi-GPU form of the call for
+ * which the reference would open one Queue per GPU (BatchLAS include/util/sycl-device-queue.hh:75)
+ * and split the batch by hand. */
+int blb200_gemm_strided_batched_host_multi(const blb200_gemm_desc* desc, const int32_t* devices, int32_t n_devices,
+                                           int32_t chunk_items);
+/* The shard rule, usable without a GPU: first item and item count of shard `shard` of `shards`. */
+void blb200_shard_range(int64_t batch, int32_t shard, int32_t shards, int64_t* first, int64_t* count);
+/* Returns the staging memory cached for `device` by the host entry points to the driver. */
+int blb200_host_staging_trim(int device);
 
 /* Name of the kernel the calling thread's most recent launch used ("" before any). */
 const char* blb200_last_kernel_name(void);
@@ -169,7 +188,8 @@ const char* blb200_version(void);
 int blb200_trace_flush(void);
 /* Synchronises the current device and reports whether any kernel of this library ever gave up
  * on one of its bounded waits: *out = 0 when none did, else a small code naming the wait
- * (1xx: 32^3 / 64^3 float rings, 2xx: gemv ring, 3xx: small-matrix ring, BLB200_WAIT_SELFTEST: the
+ * (1xx: 32^3 / 64^3 float rings, 2xx: gemv ring, 3xx: small-matrix ring, 4xx: TMA-fed DMMA tiles,
+ * BLB200_WAIT_SELFTEST: the
  * self-test below).  Failure detection in the sense of BatchLAS's queue error handling
  * (src/util/queue-impl.cc wait_and_throw): the host learns of a lost copy instead of hanging. */
 int blb200_device_status(int* out);

@@ -120,6 +120,29 @@ def test_unaligned_views_take_a_safe_path(bl, dt):
         assert_parity(p, A, B, C0, C, what=f"offset view via {kern}")
 
 
+@pytest.mark.parametrize("dt", ["s", "d", "c"])
+def test_unaligned_operands_stay_on_a_tile_kernel(bl, dt):
+    """Operands that are only element-aligned (a slice starting one element in, ld = 258: the
+    reference's own unaligned case, BatchLAS tests/gemm_tests.cc:320-332) keep a tile kernel and
+    only switch its load policy (as src/sycl/gemm/load_policies.hh:18-34 does) — every op pair,
+    ragged edges, beta != 0, canaries in the padding."""
+    code = oracle.DTYPES[dt]
+    ops = ["N", "T"] if dt in "sd" else ["N", "T", "C"]
+    for oa in ops:
+        for ob in ops:
+            for (m, n, k, batch, ld_extra, off) in [(256, 256, 256, 1, 2, 0), (130, 66, 40, 2, 1, 1), (64, 96, 17, 3, 0, 1)]:
+                ar = m if oa == "N" else k
+                br = k if ob == "N" else n
+                p = oracle.make_problem(dt, oa, ob, m, n, k, batch, lda=ar + ld_extra, ldb=br + ld_extra,
+                                        ldc=m + ld_extra, alpha=scalar_for(code, 1.5), beta=scalar_for(code, -0.5))
+                p.stride_a += 1
+                p.stride_c += 3
+                A, B, C0 = make_inputs(p)
+                C, kern = run_device(bl, p, A, B, C0, offset_elems=off)
+                assert kern in ("tiled", "dmma"), (dt, oa, ob, m, n, k, kern)
+                assert_parity(p, A, B, C0, C, what=f"element-aligned {dt} {oa}{ob} {m}x{n}x{k} via {kern}")
+
+
 @pytest.mark.parametrize("kernel", ["tiled", "dmma"])
 @pytest.mark.parametrize("dt", ["d", "z"])
 def test_both_fp64_tile_kernels_on_ragged_and_aligned_shapes(bl, kernel, dt):
@@ -138,6 +161,50 @@ def test_both_fp64_tile_kernels_on_ragged_and_aligned_shapes(bl, kernel, dt):
                 C, kern = run_device(bl, p, A, B, C0, kernel=kernel)
                 assert kern == kernel
                 assert_parity(p, A, B, C0, C, what=f"{kernel} {dt} {oa}{ob} {m}x{n}x{k}")
+
+
+@pytest.mark.parametrize("oa", ["N", "T"])
+@pytest.mark.parametrize("ob", ["N", "T"])
+def test_tma_fed_dmma_tiles(bl, oa, ob):
+    """The tensor-map fed DMMA kernel (128-byte swizzled stages, permuted row ownership) on full,
+    ragged and tiny shapes, padded even leading dimensions with canaries, stride gaps, many items,
+    beta == 0 over NaN and beta != 0; and it must agree with the cp.async DMMA kernel bit for bit
+    (same products summed in the same order)."""
+    shapes = [(256, 256, 256, 3, 2.0, 0.5, 8), (200, 130, 70, 3, 2.0, -1.0, 2), (64, 64, 16, 5, 1.0, 0.0, 0),
+              (66, 34, 6, 2, 1.0, 1.0, 4), (40, 190, 33, 2, -1.5, 0.0, 2), (128, 64, 1, 2, 1.0, 0.5, 0),
+              (1024, 96, 48, 1, 1.0, 1.0, 0), (33, 33, 100, 7, 1.0, 0.0, 6)]
+    for (m, n, k, batch, alpha, beta, pad) in shapes:
+        ar = m if oa == "N" else k
+        br = k if ob == "N" else n
+        ev = lambda x: x + (x & 1)  # tensor-map strides are multiples of 16 bytes: even ld
+        p = oracle.make_problem("d", oa, ob, m, n, k, batch, lda=ev(ar) + pad, ldb=ev(br) + pad, ldc=m + pad + 1,
+                                alpha=alpha, beta=beta)
+        p.stride_a += 2
+        p.stride_b += 4
+        p.stride_c += 5
+        A, B, C0 = make_inputs(p)
+        if beta == 0.0:
+            idx = (np.arange(p.batch)[:, None, None] * p.stride_c + np.arange(n)[None, :, None] * p.ldc
+                   + np.arange(m)[None, None, :]).ravel()
+            C0[idx] = np.nan
+        C, kern = run_device(bl, p, A, B, C0, kernel="dmma_tma")
+        assert kern == "dmma_tma"
+        C0chk = np.where(np.isnan(C0), 0.0, C0) if beta == 0.0 else C0
+        bad, worst = oracle.check(p, A, B, C0chk, C)
+        assert bad == 0, f"dmma_tma {oa}{ob} {m}x{n}x{k}: worst ratio {worst:.3g}"
+        assert oracle.untouched_outside_window(p, C0, C)
+        C2, kern2 = run_device(bl, p, A, B, C0, kernel="dmma")
+        assert kern2 == "dmma" and np.array_equal(C, C2, equal_nan=True)
+    # the dispatcher takes it for plain aligned double problems, and leaves odd ld to the cp.async kernel
+    p = oracle.make_problem("d", oa, ob, 128, 128, 64, 2, alpha=1.0, beta=0.0)
+    A, B, C0 = make_inputs(p)
+    assert run_device(bl, p, A, B, C0)[1] == "dmma_tma"
+    p = oracle.make_problem("d", oa, ob, 129, 127, 65, 2, alpha=1.0, beta=0.0)
+    A, B, C0 = make_inputs(p)
+    C, kern = run_device(bl, p, A, B, C0)
+    assert kern in ("dmma", "dmma_tma")
+    assert_parity(p, A, B, C0, C, what=f"odd dims via {kern}")
+    assert bl.device_status() == 0
 
 
 @pytest.mark.parametrize("dt", ["s", "d", "c"])
@@ -474,6 +541,47 @@ def test_host_buffer_entry_matches_device_entry(bl):
             hC.copy_(torch.from_numpy(C0))
             bl._lib.check(bl._lib.load().blb200_gemm_strided_batched_host(desc, 0, chunk))
             assert_parity(p, A, B, C0, hC.numpy(), what=f"host entry {dt} chunk={chunk}")
+
+
+def test_multi_gpu_host_entry_matches_one_gpu_bit_for_bit(bl):
+    """One call over every visible GPU (contiguous batch ranges, no exchange) gives exactly the bytes
+    the one-GPU host entry gives, padding and stride gaps included; with one GPU visible the device
+    list is [0] and the same comparison still exercises the entry.  Called twice: the second call
+    reuses the per-device streams and the library's own staging pool."""
+    import ctypes
+    ndev = torch.cuda.device_count()
+    devices = list(range(ndev))
+    L = bl._lib.load()
+    for (dt, oa, ob, m, n, k, batch, beta, ldc_extra) in [("s", "N", "T", 32, 32, 32, 4001, -0.5, 0),
+                                                         ("d", "T", "N", 72, 40, 56, 37, 0.5, 3),
+                                                         ("z", "C", "N", 24, 16, 40, 3, 0.0, 0)]:
+        p = oracle.make_problem(dt, oa, ob, m, n, k, batch, ldc=m + ldc_extra, alpha=1.5, beta=beta)
+        A, B, C0 = make_inputs(p)
+        hA, hB = torch.from_numpy(A).pin_memory(), torch.from_numpy(B).pin_memory()
+        hC1 = torch.from_numpy(C0.copy()).pin_memory()
+        hCn = torch.from_numpy(C0.copy()).pin_memory()
+
+        def desc(hc):
+            return bl.make_desc(hA.data_ptr(), hB.data_ptr(), hc.data_ptr(), p.dtype, p.op_a, p.op_b, m, n, k, batch,
+                                p.lda, p.ldb, p.ldc, p.stride_a, p.stride_b, p.stride_c, p.alpha, p.beta)
+        bl._lib.check(L.blb200_gemm_strided_batched_host(desc(hC1), 0, 0))
+        arr = (ctypes.c_int32 * ndev)(*devices)
+        for _ in range(2):
+            hCn.copy_(torch.from_numpy(C0))
+            bl._lib.check(L.blb200_gemm_strided_batched_host_multi(desc(hCn), arr, ndev, 0))
+            assert np.array_equal(hCn.numpy().view(np.uint8), hC1.numpy().view(np.uint8)), (dt, ndev)
+        assert_parity(p, A, B, C0, hCn.numpy(), what=f"multi-GPU host entry {dt} on {ndev} GPU(s)")
+    # more shards than items: the empty shards do nothing
+    if ndev > 1:
+        p = oracle.make_problem("d", "N", "N", 8, 8, 8, 1, alpha=1.0, beta=0.0)
+        A, B, C0 = make_inputs(p, tail=0)
+        hA, hB, hC = (torch.from_numpy(x.copy()).pin_memory() for x in (A, B, C0))
+        d = bl.make_desc(hA.data_ptr(), hB.data_ptr(), hC.data_ptr(), p.dtype, 0, 0, 8, 8, 8, 1, 8, 8, 8, 64, 64, 64)
+        bl._lib.check(L.blb200_gemm_strided_batched_host_multi(d, (ctypes.c_int32 * ndev)(*devices), ndev, 0))
+        assert_parity(p, A, B, C0, hC.numpy(), what="one item over several GPUs")
+    for dev in devices:
+        assert L.blb200_host_staging_trim(dev) == 0
+    torch.cuda.set_device(0)
 
 
 def test_device_fill_matches_numpy_statement(bl):

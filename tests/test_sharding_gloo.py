@@ -71,3 +71,36 @@ def test_contiguous_batch_sharding_over_gloo(world, tmp_path):
     out = str(tmp_path / "ok.npy")
     mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     assert np.load(out)[0]
+
+
+def test_c_shard_rule_matches_the_python_one(lib):
+    """blb200_shard_range (what the one-call multi-GPU host entry cuts the batch with) against
+    sharding.shard_range: contiguous, disjoint, complete, for awkward batch / shard counts."""
+    first, count = ctypes.c_int64(0), ctypes.c_int64(0)
+    for batch in (0, 1, 7, 64, 1000, 10_000, 1_000_000, 2**31 - 1):
+        for world in (1, 2, 3, 4, 8, 13):
+            covered = 0
+            for g in range(world):
+                lib.blb200_shard_range(batch, g, world, ctypes.byref(first), ctypes.byref(count))
+                assert (first.value, count.value) == shard_range(batch, g, world)
+                assert first.value == covered
+                covered += count.value
+            assert covered == batch
+    lib.blb200_shard_range(10, 5, 4, ctypes.byref(first), ctypes.byref(count))  # shard out of range: empty
+    assert (first.value, count.value) == (0, 0)
+
+
+def test_multi_gpu_host_entry_rejects_bad_device_lists(lib):
+    d = _lib.GemmDesc()
+    d.m = d.n = d.k = 4
+    d.batch = 2
+    d.lda = d.ldb = d.ldc = 4
+    d.stride_a = d.stride_b = d.stride_c = 16
+    buf = np.zeros(64)
+    d.a = d.b = d.c = buf.ctypes.data
+    two_same = (ctypes.c_int32 * 2)(0, 0)
+    assert lib.blb200_gemm_strided_batched_host_multi(d, None, 1, 0) == _lib.E_NULL
+    assert lib.blb200_gemm_strided_batched_host_multi(d, two_same, 0, 0) == _lib.E_NULL
+    assert lib.blb200_gemm_strided_batched_host_multi(d, two_same, 2, 0) == _lib.E_UNSUPPORTED
+    d.stride_c = 3  # overlapping C items
+    assert lib.blb200_gemm_strided_batched_host_multi(d, two_same, 1, 0) == _lib.E_SHAPE
