@@ -7,6 +7,8 @@
 #include <string>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "common.cuh"
 
 namespace blb200 {
@@ -24,6 +26,8 @@ void note_launch(const char* kernel_name) {
 //   that leave kernel_hint at 0 (the role BATCHLAS_GEMM_SYCL_KERNEL plays for the reference's SYCL
 //   family, src/sycl/gemm_kernels.cc:270-329); a problem the forced kernel cannot run is dispatched
 //   normally.
+// BATCHLAS_NVTX=1  wraps every gemm call in an NVTX range "blb200.gemm <dtype> m x n x k b<batch>" and
+//   marks the kernel variant chosen inside it, for timelines taken with an external profiler.
 // BATCHLAS_KERNEL_TRACE=1 [BATCHLAS_KERNEL_TRACE_PATH=file]  brackets every launch with CUDA events
 //   and writes a Chrome trace at exit (the reference's kernel tracer, src/util/kernel-trace.hh:46-215).
 static int env_forced_kernel() {
@@ -180,7 +184,29 @@ static int launch_tile_kernel(const GemmParams& p, int dtype, cudaStream_t strea
 
 int dispatch(const blb200_gemm_desc* d, cudaStream_t stream) { return dispatch_structured(d, nullptr, stream); }
 
+static bool nvtx_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("BATCHLAS_NVTX");
+    return v && *v && strcmp(v, "0") != 0;
+  }();
+  return on;
+}
+
+static int dispatch_traced(const blb200_gemm_desc* d, const StructureHints* hints, cudaStream_t stream);
+
 int dispatch_structured(const blb200_gemm_desc* d, const StructureHints* hints, cudaStream_t stream) {
+  if (!nvtx_enabled() || !d) return dispatch_traced(d, hints, stream);
+  char label[96];
+  snprintf(label, sizeof(label), "blb200.gemm %c %dx%dx%d b%d", "sdcz"[d->dtype & 3], d->m, d->n, d->k, d->batch);
+  nvtxRangePushA(label);
+  const int rc = dispatch_traced(d, hints, stream);
+  snprintf(label, sizeof(label), "kernel=%s rc=%d", t_last_kernel, rc);
+  nvtxMarkA(label);
+  nvtxRangePop();
+  return rc;
+}
+
+static int dispatch_traced(const blb200_gemm_desc* d, const StructureHints* hints, cudaStream_t stream) {
   Tracer& tr = tracer();
   if (!tr.enabled) return dispatch_untraced(d, hints, stream);
   TraceRecord rec{};

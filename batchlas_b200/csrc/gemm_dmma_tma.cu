@@ -11,8 +11,13 @@
 // Stage layout (BK = 16 doubles = 128 bytes, the widest row the 128-byte swizzle allows):
 //   K-major operand (A under op T, B under op N): one box of 16 k x 64 rows; stage row r holds the
 //     16 k of matrix row r, its 16-byte chunks XORed with (r & 7).
-//   M-major operand (A under op N, B under op T): four boxes of 16 rows x 16 k, 2 KiB each; box row
-//     kk holds 16 consecutive matrix rows at k = kk, chunks XORed with (kk & 7).
+//   M-major operand (A under op N, B under op T): four blocks of 16 rows x 16 k, 2 KiB each; block
+//     row kk holds 16 consecutive matrix rows at k = kk, chunks XORed with (kk & 7).  When the
+//     operand's row count is a multiple of 16 the four blocks come from ONE copy through a 4-D map
+//     that splits the rows into (16, rows / 16) — box 16 x 16 x 4 x 1 — otherwise from four 3-D
+//     copies whose row bound zero-fills the ragged edge (the 4-D view cannot bound a partial group
+//     of 16 rows; measured: four small boxes per operand cost 1-2 % against the cp.async kernel,
+//     one box gains).
 // The DMMA fragment of lane (g = lane >> 2, t = lane & 3) is element (row g, k t) of an 8 x 4 tile.
 // With all stage rows exactly 128 bytes apart, a half-warp request (4 g x 4 t) is conflict-free only
 // if the XOR spreads it over all eight chunks, which fixes which matrix rows the eight g-lanes of a
@@ -28,6 +33,8 @@
 // positive batch strides.  No load with cluster multicast is used; the maps cover this GPU's memory.
 #include <cuda.h>
 #include <string.h>
+
+#include <atomic>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -47,6 +54,12 @@ __device__ __forceinline__ void dmma(double& c0, double& c1, double a, double b)
                : "d"(a), "d"(b));
 }
 
+__device__ __forceinline__ void tma_load_4d(void* dst_smem, const CUtensorMap* map, int x, int y, int z, int w, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::
+          "r"(smem_u32(dst_smem)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar))
+      : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(void* dst_smem, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
@@ -78,7 +91,7 @@ template <int OPA, int OPB>
 __global__ void __launch_bounds__(kThreads, 4)
     gemm_dmma_tma_d_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                            double* __restrict__ C, long long sc, long long ldc, int m, int n, int k, int tiles_m,
-                           int tiles_n, double alpha, double beta) {
+                           int tiles_n, double alpha, double beta, int a_grouped, int b_grouped) {
   constexpr bool AK = (OPA != BLB200_N);   // A stored k x m: k fastest
   constexpr bool BKM = (OPB == BLB200_N);  // B stored k x n: k fastest
   extern __shared__ unsigned char smem_raw[];
@@ -109,12 +122,16 @@ __global__ void __launch_bounds__(kThreads, 4)
     mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
     if (AK) {
       tma_load_3d(st, &map_a, k0, m0, item, &full_bar[s]);
+    } else if (a_grouped) {
+      tma_load_4d(st, &map_a, 0, k0, m0 >> 4, item, &full_bar[s]);
     } else {
 #pragma unroll
       for (int b = 0; b < 4; ++b) tma_load_3d(st + b * 2048, &map_a, m0 + 16 * b, k0, item, &full_bar[s]);
     }
     if (BKM) {
       tma_load_3d(st + kOperandBytes, &map_b, k0, n0, item, &full_bar[s]);
+    } else if (b_grouped) {
+      tma_load_4d(st + kOperandBytes, &map_b, 0, k0, n0 >> 4, item, &full_bar[s]);
     } else {
 #pragma unroll
       for (int b = 0; b < 4; ++b) tma_load_3d(st + kOperandBytes + b * 2048, &map_b, n0 + 16 * b, k0, item, &full_bar[s]);
@@ -209,21 +226,37 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// 3-D map over a column-major double operand: dims (rows, cols, items), strides (ld, item stride).
-// KMAJOR operands (the contraction index runs along the stored rows) are fetched as one 16 x 64 box,
-// the others as 16 x 16 boxes; both 128 bytes wide, 128-byte swizzle, zero fill past the edges.
+enum MapKind { kMapKMajor = 0, kMapRows16 = 1, kMapRowGroups = 2 };
+
+// Map over a column-major double operand, 128 bytes wide boxes, 128-byte swizzle, zero fill past
+// the bounds.
+//   kMapKMajor    3-D (rows, cols, items), box 16 x 64: the contraction index runs along the rows
+//   kMapRows16    3-D (rows, cols, items), box 16 x 16: 16 matrix rows at 16 k, any row count
+//   kMapRowGroups 4-D (16, cols, rows / 16, items), box 16 x 16 x 4: 64 matrix rows at 16 k in one
+//                 copy; rows must be a multiple of 16 (a partial group of 16 has no bound in this view)
 int make_operand_map(CUtensorMap* map, const void* base, int rows, int cols, long long ld, long long stride, int batch,
-                     bool kmajor) {
+                     int kind) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return BLB200_E_INTERNAL;
-  const cuuint64_t dims[3] = {(cuuint64_t)rows, (cuuint64_t)cols, (cuuint64_t)(batch > 0 ? batch : 1)};
+  const cuuint64_t items = (cuuint64_t)(batch > 0 ? batch : 1);
   const long long item_stride = batch > 1 ? stride : ld * (long long)cols;
-  const cuuint64_t strides[2] = {(cuuint64_t)ld * 8, (cuuint64_t)item_stride * 8};
-  const cuuint32_t box[3] = {16, kmajor ? 64u : 16u, 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 3, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r;
+  if (kind == kMapRowGroups) {
+    const cuuint64_t dims[4] = {16, (cuuint64_t)cols, (cuuint64_t)(rows / 16), items};
+    const cuuint64_t strides[3] = {(cuuint64_t)ld * 8, 128, (cuuint64_t)item_stride * 8};
+    const cuuint32_t box[4] = {16, 16, 4, 1};
+    r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 4, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    const cuuint64_t dims[3] = {(cuuint64_t)rows, (cuuint64_t)cols, items};
+    const cuuint64_t strides[2] = {(cuuint64_t)ld * 8, (cuuint64_t)item_stride * 8};
+    const cuuint32_t box[3] = {16, kind == kMapKMajor ? 64u : 16u, 1};
+    r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 3, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   return r == CUDA_SUCCESS ? BLB200_OK : BLB200_E_INTERNAL;
 }
 
@@ -234,17 +267,18 @@ struct OperandMapCache {
     const void* base = nullptr;
     int rows = 0, cols = 0, batch = 0;
     long long ld = 0, stride = 0;
-    bool kmajor = false, valid = false;
+    int kind = 0;
+    bool valid = false;
     alignas(64) CUtensorMap map;
   };
   static constexpr int kEntries = 16;
   Entry e[kEntries];
   int next = 0;
-  int get(CUtensorMap* out, const void* base, int rows, int cols, long long ld, long long stride, int batch, bool kmajor) {
+  int get(CUtensorMap* out, const void* base, int rows, int cols, long long ld, long long stride, int batch, int kind) {
     for (int i = 0; i < kEntries; ++i) {
       const Entry& c = e[i];
       if (c.valid && c.base == base && c.rows == rows && c.cols == cols && c.ld == ld && c.stride == stride &&
-          c.batch == batch && c.kmajor == kmajor) {
+          c.batch == batch && c.kind == kind) {
         memcpy(out, &c.map, sizeof(CUtensorMap));
         return BLB200_OK;
       }
@@ -252,10 +286,10 @@ struct OperandMapCache {
     Entry& slot = e[next];
     next = (next + 1) % kEntries;
     slot.valid = false;
-    const int rc = make_operand_map(&slot.map, base, rows, cols, ld, stride, batch, kmajor);
+    const int rc = make_operand_map(&slot.map, base, rows, cols, ld, stride, batch, kind);
     if (rc != BLB200_OK) return rc;
     slot.base = base; slot.rows = rows; slot.cols = cols; slot.ld = ld; slot.stride = stride;
-    slot.batch = batch; slot.kmajor = kmajor; slot.valid = true;
+    slot.batch = batch; slot.kind = kind; slot.valid = true;
     memcpy(out, &slot.map, sizeof(CUtensorMap));
     return BLB200_OK;
   }
@@ -272,9 +306,25 @@ int launch_op(const GemmParams& p, cudaStream_t stream) {
   static thread_local OperandMapCache maps;
   const int a_rows = AK ? p.k : p.m, a_cols = AK ? p.m : p.k;
   const int b_rows = BKM ? p.k : p.n, b_cols = BKM ? p.n : p.k;
-  int rc = maps.get(&map_a, p.a, a_rows, a_cols, p.lda, p.sa, p.batch, AK);
+  // The grouped (4-D) view has a row-group stride (128 bytes) below its column stride; should a
+  // driver refuse to encode that, the operand is fetched as four 16-row boxes from then on.
+  static std::atomic<int> grouped_ok{1};
+  int a_kind = AK ? kMapKMajor : (a_rows % 16 == 0 && grouped_ok.load() ? kMapRowGroups : kMapRows16);
+  int b_kind = BKM ? kMapKMajor : (b_rows % 16 == 0 && grouped_ok.load() ? kMapRowGroups : kMapRows16);
+  int rc = maps.get(&map_a, p.a, a_rows, a_cols, p.lda, p.sa, p.batch, a_kind);
+  if (rc != BLB200_OK && a_kind == kMapRowGroups) {
+    grouped_ok.store(0);
+    a_kind = kMapRows16;
+    if (b_kind == kMapRowGroups) b_kind = kMapRows16;
+    rc = maps.get(&map_a, p.a, a_rows, a_cols, p.lda, p.sa, p.batch, a_kind);
+  }
   if (rc != BLB200_OK) return rc;
-  rc = maps.get(&map_b, p.b, b_rows, b_cols, p.ldb, p.sb, p.batch, BKM);
+  rc = maps.get(&map_b, p.b, b_rows, b_cols, p.ldb, p.sb, p.batch, b_kind);
+  if (rc != BLB200_OK && b_kind == kMapRowGroups) {
+    grouped_ok.store(0);
+    b_kind = kMapRows16;
+    rc = maps.get(&map_b, p.b, b_rows, b_cols, p.ldb, p.sb, p.batch, b_kind);
+  }
   if (rc != BLB200_OK) return rc;
   auto kern = gemm_dmma_tma_d_kernel<OPA, OPB>;
   static thread_local int configured_for = -1;
@@ -286,7 +336,8 @@ int launch_op(const GemmParams& p, cudaStream_t stream) {
     configured_for = cur;
   }
   kern<<<(unsigned)total, kThreads, smem, stream>>>(map_a, map_b, (double*)p.c, p.sc, p.ldc, p.m, p.n, p.k, tiles_m,
-                                                   tiles_n, p.alpha[0], p.beta[0]);
+                                                   tiles_n, p.alpha[0], p.beta[0], a_kind == kMapRowGroups ? 1 : 0,
+                                                   b_kind == kMapRowGroups ? 1 : 0);
   return (int)cudaGetLastError();
 }
 

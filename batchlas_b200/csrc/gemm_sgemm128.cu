@@ -14,8 +14,11 @@
 //      op T (N-major in memory): [32 k][128 n]; a lane owns columns 8tj..8tj+7 (two float4 per k).
 //   B values are duplicated into both halves of a 64-bit register for FFMA2; K-major B fragments
 //   are fetched one 4-k chunk ahead.
-// Preconditions as for the other tile kernels (16-byte aligned bases, ld and stride multiples of 4
-// elements); edges are zero-filled on load and predicated on store; beta == 0 never reads C.
+// Preconditions as for the other tile kernels.  Operands with 16-byte aligned bases and ld, stride
+// multiples of 4 elements take 16-byte copies (AL = true); operands that are only float-aligned (a
+// slice with an odd offset, ld = 258) are copied one float at a time into the same stage layout and
+// C is accessed by scalars (AL = false).  Edges are zero-filled on load and predicated on store;
+// beta == 0 never reads C.
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -37,9 +40,21 @@ __device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
 constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3, THREADS = 256;
 constexpr int A_STAGE = BK * BM * 4, B_STAGE = BK * BN * 4;  // 16 KiB each
 
-// A tile: 32 k-rows x 32 chunks of 4 rows.
+// A tile: 32 k-rows x 32 chunks of 4 rows.  AL = false: float by float, consecutive threads on
+// consecutive floats of a stored column, into the same layout.
+template <bool AL>
 __device__ __forceinline__ void load_a(unsigned char* dst, const float* __restrict__ A, long long lda, int m0, int M,
                                        int k0, int K, int tid) {
+  if constexpr (!AL) {
+#pragma unroll
+    for (int e = tid; e < BK * BM; e += THREADS) {
+      const int kk = e >> 7, mi = e & 127;
+      const int gk = k0 + kk, gm = m0 + mi;
+      const bool ok = gk < K && gm < M;
+      cp_async_elem<4>(dst + kk * (BM * 4) + mi * 4, ok ? A + (long long)gk * lda + gm : A, ok ? 4 : 0);
+    }
+    return;
+  }
 #pragma unroll
   for (int c = tid; c < BK * (BM / 4); c += THREADS) {
     const int kk = c >> 5, mc = c & 31;
@@ -52,9 +67,27 @@ __device__ __forceinline__ void load_a(unsigned char* dst, const float* __restri
 }
 
 // B tile.  KMAJOR (op N): 128 columns x 8 chunks of 4 k, swizzled; else (op T): 32 k-rows x 32 chunks of 4 columns.
-template <bool KMAJOR>
+template <bool KMAJOR, bool AL>
 __device__ __forceinline__ void load_b(unsigned char* dst, const float* __restrict__ B, long long ldb, int n0, int N,
                                        int k0, int K, int tid) {
+  if constexpr (!AL) {
+#pragma unroll
+    for (int e = tid; e < BK * BN; e += THREADS) {
+      if (KMAJOR) {
+        const int j = e >> 5, ke = e & 31;
+        const int gn = n0 + j, gk = k0 + ke;
+        const bool ok = gn < N && gk < K;
+        cp_async_elem<4>(dst + j * 128 + (((ke >> 2) ^ (j & 7)) * 16) + (ke & 3) * 4, ok ? B + (long long)gn * ldb + gk : B,
+                         ok ? 4 : 0);
+      } else {
+        const int kk = e >> 7, ni = e & 127;
+        const int gk = k0 + kk, gn = n0 + ni;
+        const bool ok = gk < K && gn < N;
+        cp_async_elem<4>(dst + kk * (BN * 4) + ni * 4, ok ? B + (long long)gk * ldb + gn : B, ok ? 4 : 0);
+      }
+    }
+    return;
+  }
   if (KMAJOR) {
 #pragma unroll
     for (int c = tid; c < BN * (BK / 4); c += THREADS) {
@@ -80,7 +113,7 @@ __device__ __forceinline__ void load_b(unsigned char* dst, const float* __restri
 
 // HINTS = false is the plain gemm; HINTS = true reads the structure hints of GemmParams (a separate
 // instantiation, so that the plain kernel's code and register allocation stay what they were).
-template <bool B_KMAJOR, bool HINTS>
+template <bool B_KMAJOR, bool HINTS, bool AL = true>
 __global__ void __launch_bounds__(THREADS, 2) sgemm128_kernel(GemmParams p, int tiles_m, int tiles_n) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* As = smem;
@@ -120,8 +153,8 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm128_kernel(GemmParams p, int 
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
     if (s < KT) {
-      load_a(As + s * A_STAGE, A, p.lda, m0, p.m, s * BK, K, tid);
-      load_b<B_KMAJOR>(Bs + s * B_STAGE, B, p.ldb, n0, p.n, s * BK, K, tid);
+      load_a<AL>(As + s * A_STAGE, A, p.lda, m0, p.m, s * BK, K, tid);
+      load_b<B_KMAJOR, AL>(Bs + s * B_STAGE, B, p.ldb, n0, p.n, s * BK, K, tid);
     }
     cp_async_commit();
   }
@@ -133,8 +166,8 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm128_kernel(GemmParams p, int 
       const int nxt = kt + STAGES - 1;
       if (nxt < KT) {
         const int s = nxt % STAGES;
-        load_a(As + s * A_STAGE, A, p.lda, m0, p.m, nxt * BK, K, tid);
-        load_b<B_KMAJOR>(Bs + s * B_STAGE, B, p.ldb, n0, p.n, nxt * BK, K, tid);
+        load_a<AL>(As + s * A_STAGE, A, p.lda, m0, p.m, nxt * BK, K, tid);
+        load_b<B_KMAJOR, AL>(Bs + s * B_STAGE, B, p.ldb, n0, p.n, nxt * BK, K, tid);
       }
       cp_async_commit();
     }
@@ -203,7 +236,7 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm128_kernel(GemmParams p, int 
       unpack2(accp[(2 * hgh + 1) * 8 + c], o[2], o[3]);
       // with a triangular output the vector store is used only strictly inside the wanted triangle
       const bool whole = !HINTS || p.out_tri == 0 || (p.out_tri == 1 ? row >= col : row + 3 <= col);
-      if (row + 4 <= p.m && whole) {
+      if (AL && row + 4 <= p.m && whole) {
         float4 out = make_float4(alpha * o[0], alpha * o[1], alpha * o[2], alpha * o[3]);
         if (!beta_zero) {
           const float4 pr = *reinterpret_cast<const float4*>(ccol + row);
@@ -226,13 +259,13 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm128_kernel(GemmParams p, int 
   }
 }
 
-template <bool B_KMAJOR, bool HINTS>
+template <bool B_KMAJOR, bool HINTS, bool AL = true>
 int launch_one(const GemmParams& p, cudaStream_t stream) {
   constexpr size_t smem = (size_t)STAGES * (A_STAGE + B_STAGE);
   const int tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BN - 1) / BN;
   const long long total = (long long)tiles_m * tiles_n * p.batch;
   if (total > 0x7fffffffLL) return BLB200_E_UNSUPPORTED;
-  auto kern = sgemm128_kernel<B_KMAJOR, HINTS>;
+  auto kern = sgemm128_kernel<B_KMAJOR, HINTS, AL>;
   static thread_local int configured_for = -1;
   int cur = 0;
   cudaGetDevice(&cur);
@@ -250,7 +283,6 @@ int launch_one(const GemmParams& p, cudaStream_t stream) {
 bool sgemm128_supported(const GemmParams& p, int dtype) {
   if (dtype != BLB200_S || p.op_a != BLB200_N) return false;
   if (p.m < 64 || p.n < 64) return false;  // smaller outputs waste most of a 128 x 128 tile
-  if (!operands_aligned_to(p, 4, 16)) return false;  // 16-byte copies only; other operands take the tiled kernel
   return tiled_supported(p, dtype);
 }
 
@@ -266,6 +298,12 @@ bool sgemm128_preferred(const GemmParams& p) {
 int launch_sgemm128(const GemmParams& p, int dtype, cudaStream_t stream) {
   if (!sgemm128_supported(p, dtype)) return BLB200_E_UNSUPPORTED;
   const bool hints = has_hints(p);
+  if (!operands_aligned_to(p, 4, 16)) {  // float-aligned operands (plain gemm only: tiled_supported saw to that)
+    if (hints || p.splits > 1) return BLB200_E_UNSUPPORTED;
+    const int rc_el = (p.op_b == BLB200_N) ? launch_one<true, false, false>(p, stream) : launch_one<false, false, false>(p, stream);
+    if (rc_el == BLB200_OK) note_launch("sgemm128");
+    return rc_el;
+  }
   const int rc = (p.op_b == BLB200_N) ? (hints ? launch_one<true, true>(p, stream) : launch_one<true, false>(p, stream))
                                       : (hints ? launch_one<false, true>(p, stream) : launch_one<false, false>(p, stream));
   if (rc == BLB200_OK) note_launch("sgemm128");

@@ -379,7 +379,11 @@ int blb200_trmm(const blb200_gemm_desc* desc, int32_t side, int32_t uplo, int32_
 int blb200_syrk(const blb200_gemm_desc* desc, int32_t uplo, int32_t hermitian, void* workspace, size_t workspace_bytes,
                 void* cuda_stream) {
   using namespace blb200;
-  int rc = check_common(desc, 0, uplo);
+  if (!desc) return BLB200_E_NULL;
+  blb200_gemm_desc seen = *desc;  // b, m and stride_b are documented as ignored: they are not validated
+  seen.m = seen.n;
+  seen.stride_b = 0;
+  int rc = check_common(&seen, 0, uplo);
   if (rc != BLB200_OK) return rc;
   if (hermitian && desc->dtype < BLB200_C) return BLB200_E_DTYPE;
   const int n = desc->n, k = desc->k;

@@ -52,7 +52,7 @@ FALLBACK_HBM_GBS = 6650.0         # earlier measurement on this pool, used when 
 # dram__bytes_read.sum + dram__bytes_write.sum per item of the dominant kernel, from the committed
 # ncu summary of a 100 000-item capture (mean of NT and TN); traffic grows in proportion to the
 # batch, so it is scaled to the full launch by the item count.
-NCU_TRAFFIC_BYTES_PER_ITEM = 16071.5
+NCU_TRAFFIC_BYTES_PER_ITEM = 16040.0
 
 
 def measured_peaks():
@@ -254,7 +254,7 @@ def desc_for(bl, c, op, tensors, meta, batch, kernel="auto"):
                         meta["a"][1], meta["b"][1], meta["c"][1], c["alpha"], c["beta"], kernel)
 
 
-def verify_sample(bl, torch, c, op, tensors, meta, batch, first_item, n_check=4):
+def verify_sample(bl, torch, c, op, tensors, meta, batch, first_item, n_check=4, kernel="auto"):
     """Restore C from the generator, run one launch, check a few items against the oracle."""
     import numpy as np
     from oracle import oracle
@@ -265,7 +265,7 @@ def verify_sample(bl, torch, c, op, tensors, meta, batch, first_item, n_check=4)
         tensors["c"].zero_()
     items = sorted(set([0, batch - 1] + [int(i) for i in np.linspace(0, batch - 1, n_check)]))
     c0 = {i: tensors["c"][i * sc:(i + 1) * sc].cpu().numpy() for i in items}
-    bl.gemm_strided_batched(desc_for(bl, c, op, tensors, meta, batch))
+    bl.gemm_strided_batched(desc_for(bl, c, op, tensors, meta, batch, kernel=kernel))
     torch.cuda.synchronize()
     code = oracle.DTYPES[c["dtype"]]
     worst_all = 0.0
@@ -850,10 +850,11 @@ def run_case(args):
             launch()
         torch.cuda.synchronize()
         ms = time_op(torch, launch, restore_fn(bl, torch, c, tens, mt, 0), args.steps)
-        w = verify_sample(bl, torch, c, o, tens, mt, batch, 0, n_check=2)
+        kern = "cublas" if args.impl == "cublas" else bl.last_kernel_name()
+        w = verify_sample(bl, torch, c, o, tens, mt, batch, 0, n_check=2, kernel=args.kernel)
         if args.impl == "cublas":
             out["impl"] = "cublas"
-        out["ops"][o[0] + o[1]] = {"ms": ms, "kernel": bl.last_kernel_name(), "worst_error_ratio": w,
+        out["ops"][o[0] + o[1]] = {"ms": ms, "kernel": kern, "worst_error_ratio": w,
                                    "gflops": flops_per_item(c) * batch / (ms * 1e-3) / 1e9,
                                    "hbm_gbs": algorithmic_bytes_per_item(c) * batch / (ms * 1e-3) / 1e9}
     print(json.dumps(out), flush=True)

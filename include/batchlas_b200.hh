@@ -31,6 +31,7 @@
 #include <limits>
 #include <memory>
 #include <random>
+#include <span>
 #include <stdexcept>
 #include <string>
 #include <type_traits>
@@ -280,6 +281,9 @@ inline std::pair<int64_t, int64_t> normalize_slice(Slice s, int64_t extent) {
 }  // namespace detail
 
 // Non-owning column-major view: element (i, j) of item b is data[b*stride + j*ld + i].
+// The reference's optional per-item pointer array (data_ptrs, include/blas/matrix.hh:672-686) is not
+// mirrored: nothing on the gemm path reads it (its users are the pointer-array solver calls such as
+// batched trsm and getrs, src/backends/cublas.cc:1245,1503-1557).
 template <typename T, MatrixFormat MType = MatrixFormat::Dense>
 class MatrixView {
   static_assert(MType == MatrixFormat::Dense, "only dense views are on this path");
@@ -462,6 +466,28 @@ inline auto with_backend(Queue& ctx, F&& f) {
                            "Check Queue::backend_available() before pinning a backend.");
 }
 
+namespace detail {
+// A backend this build certainly has, used only to ask whether a positional call would compile.
+inline constexpr Backend kProbeBackend = Backend::CUDA;
+}  // namespace detail
+
+// BATCHLAS_DISPATCH_ON_QUEUE(NAME): for an entry point declared as
+//     template <Backend Back, typename T, ...> R NAME(Queue&, ...);
+// defines NAME(queue, args...) that looks the backend up on the queue (BatchLAS
+// include/blas/queue-dispatch.hh:103-113).  The arguments travel as a pack, so the primary's default
+// arguments still apply, and the requires-clause admits only argument lists that the Backend-first
+// form accepts — any other call leaves this overload out of resolution instead of failing inside it.
+#define BATCHLAS_DISPATCH_ON_QUEUE(NAME)                                                        \
+  template <typename... CallArgs>                                                                \
+    requires requires(::Queue& probe_queue, CallArgs&&... probe_args) {                          \
+      NAME<::batchlas::detail::kProbeBackend>(probe_queue, std::forward<CallArgs>(probe_args)...); \
+    }                                                                                            \
+  inline auto NAME(::Queue& queue, CallArgs&&... call_args) {                                    \
+    return ::batchlas::with_backend(queue, [&](auto backend_tag) {                               \
+      return NAME<backend_tag.value>(queue, std::forward<CallArgs>(call_args)...);               \
+    });                                                                                          \
+  }
+
 // The seam: gemm<Backend::CUDA, T> (replaces BatchLAS src/backends/cublas.cc:1574-1585).
 template <Backend Back, typename T>
 Event gemm(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
@@ -579,6 +605,44 @@ template <typename T>
 inline Event gemm(Queue& ctx, const Matrix<T>& A, const Matrix<T>& B, const Matrix<T>& C,
                   const GemmOptions<std::type_identity_t<T>>& o = {}) {
   return gemm<T>(ctx, A.view(), B.view(), C.view(), o);
+}
+
+// gemm over several GPUs of the box with the operands in HOST memory (views over pinned or pageable
+// host storage): the batch is cut into contiguous ranges, one per queue's device, each range runs
+// its own copy / compute pipeline from a host thread of its own and writes its slice of C; nothing
+// crosses between GPUs.  One Queue per GPU is how BatchLAS addresses a specific GPU
+// (include/util/sycl-device-queue.hh:75); the reference itself has no multi-GPU call.  Synchronous.
+template <typename T>
+inline void gemm_host(std::span<Queue> queues, const MatrixView<T, MatrixFormat::Dense>& A,
+                      const MatrixView<T, MatrixFormat::Dense>& B, const MatrixView<T, MatrixFormat::Dense>& C,
+                      const GemmOptions<std::type_identity_t<T>>& o = {}) {
+  if (queues.empty()) throw std::runtime_error("gemm_host: no queue given");
+  if (o.precision != ComputePrecision::Default)
+    throw std::runtime_error("GEMM: reduced compute precision is not available on this path");
+  auto [m, k] = get_effective_dims(A, o.transA);
+  auto [kb, n] = get_effective_dims(B, o.transB);
+  if (A.batch_size() != B.batch_size() || A.batch_size() != C.batch_size() || k != kb || C.rows() != m || C.cols() != n)
+    throw std::runtime_error("GEMM: incompatible matrix dimensions");
+  blb200_gemm_desc d{};
+  d.a = A.data_ptr(); d.b = B.data_ptr(); d.c = C.data_ptr();
+  d.m = m; d.n = n; d.k = k; d.batch = A.batch_size();
+  d.lda = A.ld(); d.ldb = B.ld(); d.ldc = C.ld();
+  d.stride_a = A.stride(); d.stride_b = B.stride(); d.stride_c = C.stride();
+  if constexpr (std::is_floating_point_v<T>) {
+    d.alpha[0] = o.alpha; d.beta[0] = o.beta;
+  } else {
+    d.alpha[0] = o.alpha.real(); d.alpha[1] = o.alpha.imag();
+    d.beta[0] = o.beta.real(); d.beta[1] = o.beta.imag();
+  }
+  d.dtype = detail::dtype_code<T>();
+  d.op_a = (int)o.transA;
+  d.op_b = (int)o.transB;
+  std::vector<int32_t> devices;
+  for (Queue& q : queues) {
+    q.wait();  // the host entry runs on streams of its own: earlier work on the queues comes first
+    devices.push_back((int32_t)q.device().idx);
+  }
+  detail::status_check(blb200_gemm_strided_batched_host_multi(&d, devices.data(), (int32_t)devices.size(), 0));
 }
 
 // ---- level-3 calls the reference builds on gemm: symm, hemm, trmm, syrk, herk ---------------------

@@ -550,6 +550,63 @@ void WorkspaceLeases(Queue& ctx) {  // mempool_tests.cc:829-1078
   CHECK(ctx.trim_workspace() && ctx.workspace_capacity() == 0);
 }
 
+// A reference-style entry point (Backend first, a defaulted trailing argument) and its
+// queue-dispatched form generated by BATCHLAS_DISPATCH_ON_QUEUE, the way the reference declares its
+// own forwarders (BatchLAS include/blas/queue-dispatch.hh:103-113).
+namespace batchlas {
+template <Backend Back, typename T>
+Event scaled_product(Queue& ctx, const MatrixView<T, MatrixFormat::Dense>& A, const MatrixView<T, MatrixFormat::Dense>& B,
+                     const MatrixView<T, MatrixFormat::Dense>& C, T alpha = T(1)) {
+  return gemm<Back, T>(ctx, A, B, C, alpha, T(0), Transpose::NoTrans, Transpose::NoTrans);
+}
+BATCHLAS_DISPATCH_ON_QUEUE(scaled_product)
+}  // namespace batchlas
+
+template <typename T>
+void DispatchOnQueueMacro(Queue& ctx) {
+  const int n = 24, batch = 3;
+  auto A = Matrix<T>::Random(n, n, false, batch, 7), B = Matrix<T>::Random(n, n, false, batch, 8);
+  Matrix<T> C1(n, n, batch), C2(n, n, batch), C3(n, n, batch);
+  scaled_product(ctx, A.view(), B.view(), C1.view()).wait();                       // default alpha applies
+  scaled_product<Backend::CUDA>(ctx, A.view(), B.view(), C2.view(), T(1)).wait();  // explicit backend still resolves
+  scaled_product(ctx, A.view(), B.view(), C3.view(), T(2)).wait();
+  ctx.wait();
+  for (int b = 0; b < batch; ++b)
+    for (int j = 0; j < n; ++j)
+      for (int i = 0; i < n; ++i) {
+        CHECK(C1(i, j, b) == C2(i, j, b));
+        CHECK(std::abs(C3(i, j, b) - T(2) * C1(i, j, b)) <= 4 * tolerance<T>() * (1 + std::abs(C1(i, j, b))));
+      }
+}
+
+// One call over every GPU of the box with host-resident operands (one Queue per GPU).
+template <typename T>
+void MultiGpuHostGemm(Queue& ctx) {
+  const int m = 40, n = 24, k = 56, batch = 37;
+  auto A = Matrix<T>::Random(m, k, false, batch, 11), B = Matrix<T>::Random(k, n, false, batch, 12);
+  auto C0 = Matrix<T>::Random(m, n, false, batch, 13);
+  ctx.wait();
+  // plain host copies of the operands
+  std::vector<T> hA((size_t)m * k * batch), hB((size_t)k * n * batch), hC((size_t)m * n * batch);
+  for (int b = 0; b < batch; ++b) {
+    for (int j = 0; j < k; ++j) for (int i = 0; i < m; ++i) hA[((size_t)b * k + j) * m + i] = A(i, j, b);
+    for (int j = 0; j < n; ++j) for (int i = 0; i < k; ++i) hB[((size_t)b * n + j) * k + i] = B(i, j, b);
+    for (int j = 0; j < n; ++j) for (int i = 0; i < m; ++i) hC[((size_t)b * n + j) * m + i] = C0(i, j, b);
+  }
+  std::vector<Queue> queues;
+  for (auto& dev : Device::get_devices(DeviceType::GPU)) queues.emplace_back(dev);
+  const T alpha = T(1.5), beta = T(-0.5);
+  gemm_host<T>(std::span<Queue>(queues), MatrixView<T>(hA.data(), m, k, m, (int64_t)m * k, batch),
+               MatrixView<T>(hB.data(), k, n, k, (int64_t)k * n, batch), MatrixView<T>(hC.data(), m, n, m, (int64_t)m * n, batch),
+               {.alpha = alpha, .beta = beta});
+  Matrix<T> C(m, n, batch);
+  for (int b = 0; b < batch; ++b)
+    for (int j = 0; j < n; ++j) for (int i = 0; i < m; ++i) C(i, j, b) = hC[((size_t)b * n + j) * m + i];
+  const double worst = max_abs_diff(A, B, C0, C, alpha, beta, Transpose::NoTrans, Transpose::NoTrans, m, n, k, batch);
+  CHECK(worst <= tolerance<T>() * k * 4);
+  ctx.make_current();
+}
+
 int main(int argc, char** argv) {
   if (argc > 1 && std::strcmp(argv[1], "--compile-only-check") == 0) {
     std::puts("compiled: overload set resolves");
@@ -577,6 +634,8 @@ int main(int argc, char** argv) {
   FOR_TYPES(BatchedGemm)
   FOR_TYPES(ReferenceShapes)
   FOR_TYPES(DeducedBackendMatchesExplicit)
+  FOR_TYPES(DispatchOnQueueMacro)
+  FOR_TYPES(MultiGpuHostGemm)
   FOR_TYPES(HeterogeneousBatchedGemm)
   FOR_TYPES(LongKUsesSplitKFromTheArena)
   FOR_TYPES(SymmMatchesSymmetrizedGemm)

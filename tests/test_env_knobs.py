@@ -1,7 +1,8 @@
 """Environment knobs, exercised in a child process because they are read once per process:
-BATCHLAS_GEMM_B200_KERNEL (forced kernel, the role BATCHLAS_GEMM_SYCL_KERNEL plays in the reference)
-and BATCHLAS_KERNEL_TRACE / BATCHLAS_KERNEL_TRACE_PATH (Chrome trace of every launch, as the
-reference's kernel tracer writes, src/util/kernel-trace.hh:46-215)."""
+BATCHLAS_GEMM_B200_KERNEL (forced kernel, the role BATCHLAS_GEMM_SYCL_KERNEL plays in the reference),
+BATCHLAS_KERNEL_TRACE / BATCHLAS_KERNEL_TRACE_PATH (Chrome trace of every launch, as the
+reference's kernel tracer writes, src/util/kernel-trace.hh:46-215) and BATCHLAS_NVTX (an NVTX range
+around every call; without a profiler attached it must simply change nothing)."""
 import json
 import os
 import subprocess
@@ -36,7 +37,8 @@ print("KERNELS", ",".join(names))
 @pytest.mark.gpu
 def test_forced_kernel_and_trace_file(lib, tmp_path):
     trace = str(tmp_path / "trace.json")
-    env = dict(os.environ, BATCHLAS_GEMM_B200_KERNEL="tiled", BATCHLAS_KERNEL_TRACE="1", BATCHLAS_KERNEL_TRACE_PATH=trace)
+    env = dict(os.environ, BATCHLAS_GEMM_B200_KERNEL="tiled", BATCHLAS_KERNEL_TRACE="1", BATCHLAS_KERNEL_TRACE_PATH=trace,
+               BATCHLAS_NVTX="1")
     out = subprocess.run([sys.executable, "-c", CHILD % ROOT], capture_output=True, text=True, env=env, timeout=600)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
     line = [l for l in out.stdout.splitlines() if l.startswith("KERNELS")][0]

@@ -139,7 +139,7 @@ def test_unaligned_operands_stay_on_a_tile_kernel(bl, dt):
                 p.stride_c += 3
                 A, B, C0 = make_inputs(p)
                 C, kern = run_device(bl, p, A, B, C0, offset_elems=off)
-                assert kern in ("tiled", "dmma"), (dt, oa, ob, m, n, k, kern)
+                assert kern in ("tiled", "dmma", "sgemm128"), (dt, oa, ob, m, n, k, kern)
                 assert_parity(p, A, B, C0, C, what=f"element-aligned {dt} {oa}{ob} {m}x{n}x{k} via {kern}")
 
 
