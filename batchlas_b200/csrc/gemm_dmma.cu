@@ -48,36 +48,6 @@ template <int ES, int BMN, int BK, int THREADS, bool KMAJOR, bool AL = true>
 __device__ __forceinline__ void load_tile_pitched(unsigned char* smem, const unsigned char* __restrict__ base,
                                                   long long ld, int MN0, int MN, int k0, int K, int tid) {
   constexpr int V = 16 / ES;  // elements per 16-byte chunk
-  if constexpr (!AL) {
-    // Element-granular policy: consecutive threads copy consecutive elements of a stored column, so
-    // a warp's request is one contiguous run; the destination layout is the same as below.
-    constexpr int ELEMS = BMN * BK;
-    if (!KMAJOR) {
-      constexpr int PITCH = BMN * ES + pad_for(ES, false);
-#pragma unroll
-      for (int e = tid; e < ELEMS; e += THREADS) {
-        const int kk = e / BMN, mi = e % BMN;
-        const int gk = k0 + kk, gm = MN0 + mi;
-        const bool ok = gk < K && gm < MN;
-        const unsigned char* src = ok ? base + ((long long)gk * ld + gm) * ES : base;
-        cp_async_elem<ES>(smem + (size_t)kk * PITCH + (size_t)mi * ES, src, ok ? ES : 0);
-      }
-    } else {
-      constexpr int PITCH = BK * ES + pad_for(ES, true);
-#pragma unroll
-      for (int e = tid; e < ELEMS; e += THREADS) {
-        const int r = e / BK, ke = e % BK;
-        const int gmn = MN0 + r, gk = k0 + ke;
-        const bool ok = gmn < MN && gk < K;
-        const int kc = ke / V;
-        const unsigned char* src = ok ? base + ((long long)gmn * ld + gk) * ES : base;
-        unsigned char* dst = smem + (size_t)r * PITCH +
-                             (ES == 8 ? (size_t)((((kc >> 1) ^ (r & 3)) << 5) + ((kc & 1) << 4)) : (size_t)kc * 16) + (ke % V) * ES;
-        cp_async_elem<ES>(dst, src, ok ? ES : 0);
-      }
-    }
-    return;
-  }
   if (!KMAJOR) {
     constexpr int CH_PER_ROW = BMN / V, CHUNKS = BK * CH_PER_ROW, PITCH = BMN * ES + pad_for(ES, false);
 #pragma unroll
@@ -87,7 +57,13 @@ __device__ __forceinline__ void load_tile_pitched(unsigned char* smem, const uns
       int valid = (gk < K) ? (MN - gm) : 0;
       valid = valid < 0 ? 0 : (valid > V ? V : valid);
       const unsigned char* src = valid ? base + ((long long)gk * ld + gm) * ES : base;
-      cp_async16(smem + (size_t)kk * PITCH + (size_t)mc * 16, src, valid * ES);
+      unsigned char* dst = smem + (size_t)kk * PITCH + (size_t)mc * 16;
+      if constexpr (AL) {
+        cp_async16(dst, src, valid * ES);
+      } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) cp_async_elem<ES>(dst + e * ES, e < valid ? src + e * ES : src, e < valid ? ES : 0);
+      }
     }
   } else {
     constexpr int CH_PER_ROW = BK / V, CHUNKS = BMN * CH_PER_ROW, PITCH = BK * ES + pad_for(ES, true);
@@ -100,7 +76,12 @@ __device__ __forceinline__ void load_tile_pitched(unsigned char* smem, const uns
       const unsigned char* src = valid ? base + ((long long)gmn * ld + gk) * ES : base;
       // real double: 32-byte group kc / 2 of row r lives at group (kc / 2) ^ (r & 3)
       unsigned char* dst = smem + (size_t)r * PITCH + (ES == 8 ? (size_t)((((kc >> 1) ^ (r & 3)) << 5) + ((kc & 1) << 4)) : (size_t)kc * 16);
-      cp_async16(dst, src, valid * ES);
+      if constexpr (AL) {
+        cp_async16(dst, src, valid * ES);
+      } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) cp_async_elem<ES>(dst + e * ES, e < valid ? src + e * ES : src, e < valid ? ES : 0);
+      }
     }
   }
 }

@@ -29,8 +29,8 @@
 // element of C differs, and the epilogue applies the same permutations.
 //
 // Preconditions (dmma_tma_supported): real double, no structure hints / per-item dims / split-K,
-// 16-byte aligned bases, even ld and batch strides (tensor-map strides are multiples of 16 bytes),
-// positive batch strides.  No load with cluster multicast is used; the maps cover this GPU's memory.
+// 16-byte aligned bases and even ld and batch strides for A and B (tensor-map strides are multiples
+// of 16 bytes), positive batch strides; C needs element alignment only.  No load with cluster multicast is used; the maps cover this GPU's memory.
 #include <cuda.h>
 #include <string.h>
 
@@ -350,7 +350,12 @@ bool dmma_tma_supported(const GemmParams& p, int dtype) {
   if (dtype != BLB200_D) return false;
   if (p.k < 1 || (p.m <= 32 && p.n <= 32)) return false;
   if (has_hints(p) || p.splits > 1) return false;
-  if (!operands_aligned_to(p, 8, 16)) return false;
+  // tensor maps need 16-byte aligned bases and strides for A and B; C is stored element by element
+  auto map_ok = [](const void* base, long long ld, long long stride) {
+    return reinterpret_cast<uintptr_t>(base) % 16 == 0 && (ld * 8) % 16 == 0 && (stride * 8) % 16 == 0;
+  };
+  if (!map_ok(p.a, p.lda, p.sa) || !map_ok(p.b, p.ldb, p.sb)) return false;
+  if (reinterpret_cast<uintptr_t>(p.c) % 8 != 0) return false;
   if (p.batch > 1 && (p.sa <= 0 || p.sb <= 0)) return false;  // a broadcast operand has no tensor-map stride
   return encode_tiled_fn() != nullptr;
 }

@@ -44,9 +44,9 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(GemmParams p, HeteroD
     if (p.splits > 1) p.k = sv.k;
     const int m0 = (int)(rem % tiles_m) * BM;
     const int n0 = (int)(rem / tiles_m) * BN;
-    if (het.m) p.m = min(het.m[item], het.cap_m);
-    if (het.n) p.n = min(het.n[item], het.cap_n);
-    if (het.k) p.k = min(het.k[item], het.cap_k);
+    p.m = item_dim(het.m, item, het.m ? het.cap_m : p.m);  // clamped to [0, capacity], as in the tile kernels
+    p.n = item_dim(het.n, item, het.n ? het.cap_n : p.n);
+    p.k = item_dim(het.k, item, het.k ? het.cap_k : p.k);
     if (m0 >= p.m || n0 >= p.n) continue;  // uniform across the CTA
     const T* A = (const T*)p.a + item * p.sa + sv.a_off;
     const T* B = (const T*)p.b + item * p.sb + sv.b_off;

@@ -40,21 +40,22 @@ __device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
 constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3, THREADS = 256;
 constexpr int A_STAGE = BK * BM * 4, B_STAGE = BK * BN * 4;  // 16 KiB each
 
-// A tile: 32 k-rows x 32 chunks of 4 rows.  AL = false: float by float, consecutive threads on
-// consecutive floats of a stored column, into the same layout.
+// 16 bytes into a stage: one copy, or four float copies when the source is only float-aligned
+// (measured faster than giving consecutive threads consecutive floats: 1024^3 41.8 against 39.7 TFLOP/s).
+template <bool AL>
+__device__ __forceinline__ void copy_chunk(unsigned char* dst, const float* src, int valid) {
+  if constexpr (AL) {
+    cp_async16(dst, src, valid * 4);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) cp_async_elem<4>(dst + 4 * e, e < valid ? src + e : src, e < valid ? 4 : 0);
+  }
+}
+
+// A tile: 32 k-rows x 32 chunks of 4 rows.
 template <bool AL>
 __device__ __forceinline__ void load_a(unsigned char* dst, const float* __restrict__ A, long long lda, int m0, int M,
                                        int k0, int K, int tid) {
-  if constexpr (!AL) {
-#pragma unroll
-    for (int e = tid; e < BK * BM; e += THREADS) {
-      const int kk = e >> 7, mi = e & 127;
-      const int gk = k0 + kk, gm = m0 + mi;
-      const bool ok = gk < K && gm < M;
-      cp_async_elem<4>(dst + kk * (BM * 4) + mi * 4, ok ? A + (long long)gk * lda + gm : A, ok ? 4 : 0);
-    }
-    return;
-  }
 #pragma unroll
   for (int c = tid; c < BK * (BM / 4); c += THREADS) {
     const int kk = c >> 5, mc = c & 31;
@@ -62,7 +63,7 @@ __device__ __forceinline__ void load_a(unsigned char* dst, const float* __restri
     int valid = (gk < K) ? (M - gm) : 0;
     valid = valid < 0 ? 0 : (valid > 4 ? 4 : valid);
     const float* src = valid ? A + (long long)gk * lda + gm : A;
-    cp_async16(dst + kk * (BM * 4) + mc * 16, src, valid * 4);
+    copy_chunk<AL>(dst + kk * (BM * 4) + mc * 16, src, valid);
   }
 }
 
@@ -70,24 +71,6 @@ __device__ __forceinline__ void load_a(unsigned char* dst, const float* __restri
 template <bool KMAJOR, bool AL>
 __device__ __forceinline__ void load_b(unsigned char* dst, const float* __restrict__ B, long long ldb, int n0, int N,
                                        int k0, int K, int tid) {
-  if constexpr (!AL) {
-#pragma unroll
-    for (int e = tid; e < BK * BN; e += THREADS) {
-      if (KMAJOR) {
-        const int j = e >> 5, ke = e & 31;
-        const int gn = n0 + j, gk = k0 + ke;
-        const bool ok = gn < N && gk < K;
-        cp_async_elem<4>(dst + j * 128 + (((ke >> 2) ^ (j & 7)) * 16) + (ke & 3) * 4, ok ? B + (long long)gn * ldb + gk : B,
-                         ok ? 4 : 0);
-      } else {
-        const int kk = e >> 7, ni = e & 127;
-        const int gk = k0 + kk, gn = n0 + ni;
-        const bool ok = gk < K && gn < N;
-        cp_async_elem<4>(dst + kk * (BN * 4) + ni * 4, ok ? B + (long long)gk * ldb + gn : B, ok ? 4 : 0);
-      }
-    }
-    return;
-  }
   if (KMAJOR) {
 #pragma unroll
     for (int c = tid; c < BN * (BK / 4); c += THREADS) {
@@ -96,7 +79,7 @@ __device__ __forceinline__ void load_b(unsigned char* dst, const float* __restri
       int valid = (gn < N) ? (K - gk) : 0;
       valid = valid < 0 ? 0 : (valid > 4 ? 4 : valid);
       const float* src = valid ? B + (long long)gn * ldb + gk : B;
-      cp_async16(dst + j * 128 + ((kc ^ (j & 7)) * 16), src, valid * 4);
+      copy_chunk<AL>(dst + j * 128 + ((kc ^ (j & 7)) * 16), src, valid);
     }
   } else {
 #pragma unroll
@@ -106,7 +89,7 @@ __device__ __forceinline__ void load_b(unsigned char* dst, const float* __restri
       int valid = (gk < K) ? (N - gn) : 0;
       valid = valid < 0 ? 0 : (valid > 4 ? 4 : valid);
       const float* src = valid ? B + (long long)gk * ldb + gn : B;
-      cp_async16(dst + kk * (BN * 4) + nc * 16, src, valid * 4);
+      copy_chunk<AL>(dst + kk * (BN * 4) + nc * 16, src, valid);
     }
   }
 }

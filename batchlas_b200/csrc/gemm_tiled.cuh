@@ -61,39 +61,17 @@ __device__ __forceinline__ void unpack16(const uint4& raw, T (&out)[16 / sizeof(
 // Issue the async copies of one operand tile.
 //   MN0: first m (or n) index of the tile, MN: matrix extent along it, BMN: tile extent,
 //   k0: first k of the tile, K: extent along k, G: thread groups along this dimension.
+template <int ES>
+__device__ __forceinline__ void copy_chunk_by_elements(unsigned char* dst, const unsigned char* src, int valid) {
+  constexpr int V = 16 / ES;
+#pragma unroll
+  for (int e = 0; e < V; ++e) cp_async_elem<ES>(dst + e * ES, e < valid ? src + e * ES : src, e < valid ? ES : 0);
+}
+
 template <typename T, int BMN, int BK, int G, int THREADS, bool KMAJOR, bool AL = true>
 __device__ __forceinline__ void load_tile(unsigned char* smem, const T* __restrict__ base, long long ld,
                                           int MN0, int MN, int k0, int K, int tid) {
   constexpr int V = 16 / (int)sizeof(T);
-  constexpr int ES = (int)sizeof(T);
-  if constexpr (!AL) {
-    // Element-granular policy: consecutive threads copy consecutive elements of a stored column, so
-    // a warp's request is one contiguous run; the destination layout is the same as below.
-    constexpr int ELEMS = BMN * BK;
-    if (!KMAJOR) {
-#pragma unroll
-      for (int e = tid; e < ELEMS; e += THREADS) {
-        const int kk = e / BMN, mi = e % BMN;
-        const int gk = k0 + kk, gm = MN0 + mi;
-        const bool ok = gk < K && gm < MN;
-        const T* src = ok ? base + (long long)gk * ld + gm : base;
-        cp_async_elem<ES>(smem + (size_t)kk * (BMN * ES) + (size_t)mi * ES, src, ok ? ES : 0);
-      }
-    } else {
-      constexpr int PITCH = BK * ES + 16;
-#pragma unroll
-      for (int e = tid; e < ELEMS; e += THREADS) {
-        const int r = e / BK, ke = e % BK;
-        const int gmn = MN0 + r, gk = k0 + ke;
-        const bool ok = gmn < MN && gk < K;
-        const int v = r / (G * V), rem = r % (G * V), g = rem / V, ee = rem % V;
-        const int slot = (v * V + ee) * G + g;
-        const T* src = ok ? base + (long long)gmn * ld + gk : base;
-        cp_async_elem<ES>(smem + (size_t)slot * PITCH + (size_t)ke * ES, src, ok ? ES : 0);
-      }
-    }
-    return;
-  }
   if (!KMAJOR) {
     constexpr int CH_PER_ROW = BMN / V, CHUNKS = BK * CH_PER_ROW;
 #pragma unroll
@@ -103,7 +81,9 @@ __device__ __forceinline__ void load_tile(unsigned char* smem, const T* __restri
       int valid = (gk < K) ? (MN - gm) : 0;
       valid = valid < 0 ? 0 : (valid > V ? V : valid);
       const T* src = valid ? base + (long long)gk * ld + gm : base;
-      cp_async16(smem + (size_t)kk * (BMN * sizeof(T)) + (size_t)mc * 16, src, valid * (int)sizeof(T));
+      unsigned char* dst = smem + (size_t)kk * (BMN * sizeof(T)) + (size_t)mc * 16;
+      if constexpr (AL) cp_async16(dst, src, valid * (int)sizeof(T));
+      else copy_chunk_by_elements<(int)sizeof(T)>(dst, (const unsigned char*)src, valid);
     }
   } else {
     constexpr int CH_PER_ROW = BK / V, CHUNKS = BMN * CH_PER_ROW, PITCH = BK * (int)sizeof(T) + 16;
@@ -117,7 +97,9 @@ __device__ __forceinline__ void load_tile(unsigned char* smem, const T* __restri
       const int v = r / (G * V), rem = r % (G * V), g = rem / V, e = rem % V;
       const int slot = (v * V + e) * G + g;
       const T* src = valid ? base + (long long)gmn * ld + gk : base;
-      cp_async16(smem + (size_t)slot * PITCH + (size_t)kc * 16, src, valid * (int)sizeof(T));
+      unsigned char* dst = smem + (size_t)slot * PITCH + (size_t)kc * 16;
+      if constexpr (AL) cp_async16(dst, src, valid * (int)sizeof(T));
+      else copy_chunk_by_elements<(int)sizeof(T)>(dst, (const unsigned char*)src, valid);
     }
   }
 }
