@@ -228,14 +228,15 @@ EncodeTiledFn encode_tiled_fn() {
 
 enum MapKind { kMapKMajor = 0, kMapRows16 = 1, kMapRowGroups = 2 };
 
-// Map over a column-major double operand, 128 bytes wide boxes, 128-byte swizzle, zero fill past
-// the bounds.
+// Map over a column-major operand seen as doubles (a complex element is two), 128 bytes wide boxes,
+// 128-byte swizzle, zero fill past the bounds.  rows / ld / stride are in doubles.
 //   kMapKMajor    3-D (rows, cols, items), box 16 x 64: the contraction index runs along the rows
-//   kMapRows16    3-D (rows, cols, items), box 16 x 16: 16 matrix rows at 16 k, any row count
-//   kMapRowGroups 4-D (16, cols, rows / 16, items), box 16 x 16 x 4: 64 matrix rows at 16 k in one
-//                 copy; rows must be a multiple of 16 (a partial group of 16 has no bound in this view)
-int make_operand_map(CUtensorMap* map, const void* base, int rows, int cols, long long ld, long long stride, int batch,
-                     int kind) {
+//   kMapRows16    3-D (rows, cols, items), box 16 x box_k: 16 doubles of a column at box_k k, any row count
+//   kMapRowGroups 4-D (16, cols, rows / 16, items), box 16 x box_k x (64 * 16 / box_k / 16 ...) — all
+//                 64 tile rows at box_k k in one copy; rows must be a multiple of 16 doubles (a
+//                 partial group has no bound in this view)
+int make_operand_map(CUtensorMap* map, const void* base, long long rows, int cols, long long ld, long long stride,
+                     int batch, int kind, int box_k, int groups) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return BLB200_E_INTERNAL;
   const cuuint64_t items = (cuuint64_t)(batch > 0 ? batch : 1);
@@ -245,14 +246,14 @@ int make_operand_map(CUtensorMap* map, const void* base, int rows, int cols, lon
   if (kind == kMapRowGroups) {
     const cuuint64_t dims[4] = {16, (cuuint64_t)cols, (cuuint64_t)(rows / 16), items};
     const cuuint64_t strides[3] = {(cuuint64_t)ld * 8, 128, (cuuint64_t)item_stride * 8};
-    const cuuint32_t box[4] = {16, 16, 4, 1};
+    const cuuint32_t box[4] = {16, (cuuint32_t)box_k, (cuuint32_t)groups, 1};
     r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 4, const_cast<void*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   } else {
     const cuuint64_t dims[3] = {(cuuint64_t)rows, (cuuint64_t)cols, items};
     const cuuint64_t strides[2] = {(cuuint64_t)ld * 8, (cuuint64_t)item_stride * 8};
-    const cuuint32_t box[3] = {16, kind == kMapKMajor ? 64u : 16u, 1};
+    const cuuint32_t box[3] = {16, kind == kMapKMajor ? 64u : (cuuint32_t)box_k, 1};
     r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 3, const_cast<void*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -265,20 +266,22 @@ int make_operand_map(CUtensorMap* map, const void* base, int rows, int cols, lon
 struct OperandMapCache {
   struct Entry {
     const void* base = nullptr;
-    int rows = 0, cols = 0, batch = 0;
+    long long rows = 0;
+    int cols = 0, batch = 0;
     long long ld = 0, stride = 0;
-    int kind = 0;
+    int kind = 0, box_k = 0;
     bool valid = false;
     alignas(64) CUtensorMap map;
   };
   static constexpr int kEntries = 16;
   Entry e[kEntries];
   int next = 0;
-  int get(CUtensorMap* out, const void* base, int rows, int cols, long long ld, long long stride, int batch, int kind) {
+  int get(CUtensorMap* out, const void* base, long long rows, int cols, long long ld, long long stride, int batch,
+          int kind, int box_k = 16, int groups = 4) {
     for (int i = 0; i < kEntries; ++i) {
       const Entry& c = e[i];
       if (c.valid && c.base == base && c.rows == rows && c.cols == cols && c.ld == ld && c.stride == stride &&
-          c.batch == batch && c.kind == kind) {
+          c.batch == batch && c.kind == kind && c.box_k == box_k) {
         memcpy(out, &c.map, sizeof(CUtensorMap));
         return BLB200_OK;
       }
@@ -286,10 +289,10 @@ struct OperandMapCache {
     Entry& slot = e[next];
     next = (next + 1) % kEntries;
     slot.valid = false;
-    const int rc = make_operand_map(&slot.map, base, rows, cols, ld, stride, batch, kind);
+    const int rc = make_operand_map(&slot.map, base, rows, cols, ld, stride, batch, kind, box_k, groups);
     if (rc != BLB200_OK) return rc;
     slot.base = base; slot.rows = rows; slot.cols = cols; slot.ld = ld; slot.stride = stride;
-    slot.batch = batch; slot.kind = kind; slot.valid = true;
+    slot.batch = batch; slot.kind = kind; slot.box_k = box_k; slot.valid = true;
     memcpy(out, &slot.map, sizeof(CUtensorMap));
     return BLB200_OK;
   }
@@ -341,21 +344,221 @@ int launch_op(const GemmParams& p, cudaStream_t stream) {
   return (int)cudaGetLastError();
 }
 
+
+// ---- complex double ----------------------------------------------------------------------------------
+// CTA 64 x 64, 8 warps as 2 (m) x 4 (n), warp tile 32 x 16 (4 x 2 DMMA tiles, re and im planes), BK = 8
+// complex = 128 bytes, two CTAs per SM.  A lane's fragment is one complex element (16 bytes = one
+// swizzle chunk), a quarter-warp request is 2 rows x 4 k; it covers all eight chunks when the two
+// rows differ in bit 2, so lane group g owns row 4 (g & 1) + (g >> 1) of each 8-row tile — the same
+// assignment for both orientations.  M-major operands come as 8-row blocks of 1 KiB (one grouped
+// 4-D copy when the row count is a multiple of 8, else eight 3-D copies).
+constexpr int kZBK = 8, kZThreads = 256;
+__device__ __forceinline__ int perm_z(int g) { return 4 * (g & 1) + (g >> 1); }
+
+template <bool KMAJOR>
+__device__ __forceinline__ int z_fragment_base(int first_row, int g, int t) {  // first_row: of the warp, multiple of 8
+  const int chunk = ((g >> 1) ^ t) + 4 * (g & 1);
+  if (KMAJOR) return (first_row + perm_z(g)) * 128 + (chunk << 4);
+  return (first_row >> 3) * 1024 + t * 128 + (chunk << 4);
+}
+template <bool KMAJOR>
+__device__ __forceinline__ int z_fragment_offset(int base, int i, int k4) {
+  if (KMAJOR) return (base ^ (k4 << 6)) + i * 1024;
+  return (base ^ (k4 << 6)) + i * 1024 + k4 * 512;
+}
+
+template <int OPA, int OPB>
+__global__ void __launch_bounds__(kZThreads, 2)
+    gemm_dmma_tma_z_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                           double2* __restrict__ C, long long sc, long long ldc, int m, int n, int k, int tiles_m,
+                           int tiles_n, double2 alpha, double2 beta, int a_grouped, int b_grouped) {
+  constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
+  constexpr bool CONJ_A = (OPA == BLB200_H), CONJ_B = (OPB == BLB200_H);
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)kStages * kStageBytes);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int wm = warp & 1, wn = warp >> 1;
+
+  const long long tiles_per_item = (long long)tiles_m * tiles_n;
+  const long long tile = blockIdx.x;
+  const int item = (int)(tile / tiles_per_item);
+  const int rem = (int)(tile - (long long)item * tiles_per_item);
+  const int m0 = (rem % tiles_m) * kBM, n0 = (rem / tiles_m) * kBN;
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  const int KT = (k + kZBK - 1) / kZBK;
+  auto issue = [&](int s, int kt) {  // one thread; map coordinates along a complex dimension count doubles
+    unsigned char* st = smem + (size_t)s * kStageBytes;
+    const int k0 = kt * kZBK;
+    mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
+    if (AK) {
+      tma_load_3d(st, &map_a, 2 * k0, m0, item, &full_bar[s]);
+    } else if (a_grouped) {
+      tma_load_4d(st, &map_a, 0, k0, m0 >> 3, item, &full_bar[s]);
+    } else {
+#pragma unroll
+      for (int b = 0; b < 8; ++b) tma_load_3d(st + b * 1024, &map_a, 2 * (m0 + 8 * b), k0, item, &full_bar[s]);
+    }
+    if (BKM) {
+      tma_load_3d(st + kOperandBytes, &map_b, 2 * k0, n0, item, &full_bar[s]);
+    } else if (b_grouped) {
+      tma_load_4d(st + kOperandBytes, &map_b, 0, k0, n0 >> 3, item, &full_bar[s]);
+    } else {
+#pragma unroll
+      for (int b = 0; b < 8; ++b) tma_load_3d(st + kOperandBytes + b * 1024, &map_b, 2 * (n0 + 8 * b), k0, item, &full_bar[s]);
+    }
+  };
+  if (tid == 0)
+    for (int s = 0; s < kStages - 1 && s < KT; ++s) issue(s, s);
+
+  double accr[4][2][2], acci[4][2][2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) accr[i][j][0] = accr[i][j][1] = acci[i][j][0] = acci[i][j][1] = 0.0;
+
+  const int a_base = z_fragment_base<AK>(32 * wm, g, t);
+  const int b_base = z_fragment_base<BKM>(16 * wn, g, t);
+
+  int issued = KT < kStages - 1 ? KT : kStages - 1;
+  int kt = 0;
+  bool lost = false;
+  for (; kt < KT; ++kt) {
+    const int s = kt % kStages;
+    const bool ok = mbar_wait(&full_bar[s], (uint32_t)(kt / kStages) & 1u, kDmmaTmaWaitFull);
+    if (__syncthreads_or(!ok)) {
+      lost = true;
+      break;
+    }
+    if (tid == 0 && issued < KT) {
+      fence_async_smem();
+      issue(issued % kStages, issued);
+      ++issued;
+    }
+    const unsigned char* as = smem + (size_t)s * kStageBytes;
+    const unsigned char* bs = as + kOperandBytes;
+#pragma unroll
+    for (int k4 = 0; k4 < kZBK / 4; ++k4) {
+      double2 af[4], bf[2];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        af[i] = *reinterpret_cast<const double2*>(as + z_fragment_offset<AK>(a_base, i, k4));
+        if (CONJ_A) af[i].y = -af[i].y;
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        bf[j] = *reinterpret_cast<const double2*>(bs + z_fragment_offset<BKM>(b_base, j, k4));
+        if (CONJ_B) bf[j].y = -bf[j].y;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const double nai = -af[i].y;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          dmma(accr[i][j][0], accr[i][j][1], af[i].x, bf[j].x);
+          dmma(accr[i][j][0], accr[i][j][1], nai, bf[j].y);
+          dmma(acci[i][j][0], acci[i][j][1], af[i].x, bf[j].y);
+          dmma(acci[i][j][0], acci[i][j][1], af[i].y, bf[j].x);
+        }
+      }
+    }
+  }
+  if (lost) {
+    if (tid == 0)
+      for (int q = kt + 1; q < issued; ++q)
+        mbar_wait_limit(&full_bar[q % kStages], (uint32_t)(q / kStages) & 1u, kDmmaTmaWaitFull, 1u << 12);
+    return;
+  }
+
+  const bool beta_zero = beta.x == 0.0 && beta.y == 0.0;
+  C += (long long)item * sc;
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int col = n0 + 16 * wn + 8 * j + perm_z(2 * t + e);
+      if (col >= n) continue;
+      double2* ccol = C + (long long)col * ldc;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = m0 + 32 * wm + 8 * i + perm_z(g);
+        if (row >= m) continue;
+        ccol[row] = epilogue<double2>(alpha, make_double2(accr[i][j][e], acci[i][j][e]), beta, beta_zero, ccol + row);
+      }
+    }
+}
+
+template <int OPA, int OPB>
+int launch_op_z(const GemmParams& p, cudaStream_t stream) {
+  constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
+  const size_t smem = (size_t)kStages * kStageBytes + kStages * sizeof(uint64_t) + 1024;
+  const int tiles_m = (p.m + kBM - 1) / kBM, tiles_n = (p.n + kBN - 1) / kBN;
+  const long long total = (long long)tiles_m * tiles_n * p.batch;
+  if (total > 0x7fffffffLL) return BLB200_E_UNSUPPORTED;
+  alignas(64) CUtensorMap map_a, map_b;
+  static thread_local OperandMapCache maps;
+  const int a_rows = AK ? p.k : p.m, a_cols = AK ? p.m : p.k;
+  const int b_rows = BKM ? p.k : p.n, b_cols = BKM ? p.n : p.k;
+  static std::atomic<int> grouped_ok{1};
+  int a_kind = AK ? kMapKMajor : (a_rows % 8 == 0 && grouped_ok.load() ? kMapRowGroups : kMapRows16);
+  int b_kind = BKM ? kMapKMajor : (b_rows % 8 == 0 && grouped_ok.load() ? kMapRowGroups : kMapRows16);
+  // rows, ld and strides in doubles; M-major boxes span 8 k, a grouped copy takes 8 groups of 8 rows
+  int rc = maps.get(&map_a, p.a, 2LL * a_rows, a_cols, 2 * p.lda, 2 * p.sa, p.batch, a_kind, kZBK, 8);
+  if (rc != BLB200_OK && a_kind == kMapRowGroups) {
+    grouped_ok.store(0);
+    a_kind = kMapRows16;
+    if (b_kind == kMapRowGroups) b_kind = kMapRows16;
+    rc = maps.get(&map_a, p.a, 2LL * a_rows, a_cols, 2 * p.lda, 2 * p.sa, p.batch, a_kind, kZBK, 8);
+  }
+  if (rc != BLB200_OK) return rc;
+  rc = maps.get(&map_b, p.b, 2LL * b_rows, b_cols, 2 * p.ldb, 2 * p.sb, p.batch, b_kind, kZBK, 8);
+  if (rc != BLB200_OK && b_kind == kMapRowGroups) {
+    grouped_ok.store(0);
+    b_kind = kMapRows16;
+    rc = maps.get(&map_b, p.b, 2LL * b_rows, b_cols, 2 * p.ldb, 2 * p.sb, p.batch, b_kind, kZBK, 8);
+  }
+  if (rc != BLB200_OK) return rc;
+  auto kern = gemm_dmma_tma_z_kernel<OPA, OPB>;
+  static thread_local int configured_for = -1;
+  int cur = 0;
+  cudaGetDevice(&cur);
+  if (configured_for != cur) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured_for = cur;
+  }
+  kern<<<(unsigned)total, kZThreads, smem, stream>>>(map_a, map_b, (double2*)p.c, p.sc, p.ldc, p.m, p.n, p.k, tiles_m,
+                                                    tiles_n, make_double2(p.alpha[0], p.alpha[1]),
+                                                    make_double2(p.beta[0], p.beta[1]), a_kind == kMapRowGroups ? 1 : 0,
+                                                    b_kind == kMapRowGroups ? 1 : 0);
+  return (int)cudaGetLastError();
+}
+
 }  // namespace
 
 int dmma_tma_device_status(int* out) { return read_device_status_word(out); }
 int dmma_tma_device_status_clear() { return clear_device_status_word(); }
 
 bool dmma_tma_supported(const GemmParams& p, int dtype) {
-  if (dtype != BLB200_D) return false;
+  if (dtype != BLB200_D && dtype != BLB200_Z) return false;
   if (p.k < 1 || (p.m <= 32 && p.n <= 32)) return false;
   if (has_hints(p) || p.splits > 1) return false;
-  // tensor maps need 16-byte aligned bases and strides for A and B; C is stored element by element
-  auto map_ok = [](const void* base, long long ld, long long stride) {
-    return reinterpret_cast<uintptr_t>(base) % 16 == 0 && (ld * 8) % 16 == 0 && (stride * 8) % 16 == 0;
+  // tensor maps need 16-byte aligned bases and strides for A and B (always true of element-aligned
+  // complex operands); C is stored element by element
+  const long long es = dtype == BLB200_D ? 8 : 16;
+  auto map_ok = [es](const void* base, long long ld, long long stride) {
+    return reinterpret_cast<uintptr_t>(base) % 16 == 0 && (ld * es) % 16 == 0 && (stride * es) % 16 == 0;
   };
   if (!map_ok(p.a, p.lda, p.sa) || !map_ok(p.b, p.ldb, p.sb)) return false;
-  if (reinterpret_cast<uintptr_t>(p.c) % 8 != 0) return false;
+  if (reinterpret_cast<uintptr_t>(p.c) % (uintptr_t)es != 0) return false;
   if (p.batch > 1 && (p.sa <= 0 || p.sb <= 0)) return false;  // a broadcast operand has no tensor-map stride
   return encode_tiled_fn() != nullptr;
 }
@@ -363,10 +566,17 @@ bool dmma_tma_supported(const GemmParams& p, int dtype) {
 int launch_dmma_tma(const GemmParams& p, int dtype, cudaStream_t stream) {
   if (!dmma_tma_supported(p, dtype)) return BLB200_E_UNSUPPORTED;
   int rc = BLB200_E_INTERNAL;
+  if (dtype == BLB200_D) {
 #define BLB_OP(A_, B_) \
   if (p.op_a == A_ && p.op_b == B_) rc = launch_op<A_, B_>(p, stream);
-  BLB_OP(0, 0) BLB_OP(0, 1) BLB_OP(1, 0) BLB_OP(1, 1)
+    BLB_OP(0, 0) BLB_OP(0, 1) BLB_OP(1, 0) BLB_OP(1, 1)
 #undef BLB_OP
+  } else {
+#define BLB_OP(A_, B_) \
+  if (p.op_a == A_ && p.op_b == B_) rc = launch_op_z<A_, B_>(p, stream);
+    BLB_OP(0, 0) BLB_OP(0, 1) BLB_OP(0, 2) BLB_OP(1, 0) BLB_OP(1, 1) BLB_OP(1, 2) BLB_OP(2, 0) BLB_OP(2, 1) BLB_OP(2, 2)
+#undef BLB_OP
+  }
   if (rc == BLB200_OK) note_launch("dmma_tma");
   return rc;
 }

@@ -207,6 +207,39 @@ def test_tma_fed_dmma_tiles(bl, oa, ob):
     assert bl.device_status() == 0
 
 
+@pytest.mark.parametrize("oa", ["N", "T", "C"])
+@pytest.mark.parametrize("ob", ["N", "T", "C"])
+def test_tma_fed_dmma_tiles_complex(bl, oa, ob):
+    """The complex<double> form of the tensor-map fed DMMA kernel: all nine op pairs on full, ragged
+    and tiny shapes (row counts that are and are not multiples of 8: one grouped copy or eight small
+    ones per M-major operand), padded leading dimensions with canaries, stride gaps, beta == 0 over
+    NaN; bit-for-bit agreement with the cp.async DMMA kernel."""
+    shapes = [(128, 64, 256, 3, 1.0 + 0.5j, 0.0, 0), (70, 50, 37, 3, 2.0 - 1.0j, -1.0 + 0.25j, 3), (64, 64, 8, 4, 1.0, 0.0, 0),
+              (36, 20, 5, 2, 1.0, 1.0, 1), (200, 24, 64, 2, -1.5j, 0.5, 2), (33, 129, 19, 2, 1.0, 0.0, 5)]
+    for (m, n, k, batch, alpha, beta, pad) in shapes:
+        ar = m if oa == "N" else k
+        br = k if ob == "N" else n
+        p = oracle.make_problem("z", oa, ob, m, n, k, batch, lda=ar + pad, ldb=br + pad, ldc=m + pad + 1,
+                                alpha=alpha, beta=beta)
+        p.stride_a += 1
+        p.stride_b += 2
+        p.stride_c += 3
+        A, B, C0 = make_inputs(p)
+        if beta == 0.0:
+            idx = (np.arange(p.batch)[:, None, None] * p.stride_c + np.arange(n)[None, :, None] * p.ldc
+                   + np.arange(m)[None, None, :]).ravel()
+            C0[idx] = np.nan
+        C, kern = run_device(bl, p, A, B, C0, kernel="dmma_tma")
+        assert kern == "dmma_tma"
+        C0chk = np.where(np.isnan(C0), 0.0, C0) if beta == 0.0 else C0
+        bad, worst = oracle.check(p, A, B, C0chk, C)
+        assert bad == 0, f"dmma_tma z {oa}{ob} {m}x{n}x{k}: worst ratio {worst:.3g}"
+        assert oracle.untouched_outside_window(p, C0, C)
+        C2, kern2 = run_device(bl, p, A, B, C0, kernel="dmma")
+        assert kern2 == "dmma" and np.array_equal(C, C2, equal_nan=True)
+    assert bl.device_status() == 0
+
+
 @pytest.mark.parametrize("dt", ["s", "d", "c"])
 def test_64x64_tiles_of_the_tiled_kernel(bl, dt):
     """The 64 x 64 tile configuration (float below 1024^2, double and complex<float> up to one tile):
@@ -273,15 +306,14 @@ def test_large_float_tiles_with_packed_fma(bl):
                                              (100, 260, 44, 1, 1.0, 0.0)]:
             p = oracle.make_problem("s", "N", ob, m, n, k, batch, alpha=alpha, beta=beta)
             A, B, C0 = make_inputs(p)
-            aligned = p.lda % 4 == 0 and p.ldb % 4 == 0 and p.ldc % 4 == 0
             C, kern = run_device(bl, p, A, B, C0)
-            # unaligned ld must decline the fast paths; aligned shapes go to whichever tile wastes less
-            assert kern in (("sgemm128", "tiled") if aligned else ("generic",)), kern
+            # every shape goes to whichever tile wastes less; an ld that is not a multiple of 4 floats
+            # (33, 257, 70 here) only switches the tile kernel's load policy
+            assert kern in ("sgemm128", "tiled"), kern
             assert_parity(p, A, B, C0, C, what=f"{kern} N{ob} {m}x{n}x{k}")
-            if aligned:
-                C, kern = run_device(bl, p, A, B, C0, kernel="sgemm128")
-                assert kern == "sgemm128"
-                assert_parity(p, A, B, C0, C, what=f"forced sgemm128 N{ob} {m}x{n}x{k}")
+            C, kern = run_device(bl, p, A, B, C0, kernel="sgemm128")
+            assert kern == "sgemm128"
+            assert_parity(p, A, B, C0, C, what=f"forced sgemm128 N{ob} {m}x{n}x{k}")
             Cn = C0.copy()
             Cn[:] = np.nan if beta == 0.0 else Cn
             if beta == 0.0:
