@@ -346,13 +346,15 @@ int launch_op(const GemmParams& p, cudaStream_t stream) {
 
 
 // ---- complex double ----------------------------------------------------------------------------------
-// CTA 64 x 64, 8 warps as 2 (m) x 4 (n), warp tile 32 x 16 (4 x 2 DMMA tiles, re and im planes), BK = 8
-// complex = 128 bytes, two CTAs per SM.  A lane's fragment is one complex element (16 bytes = one
+// CTA 64 x 64, 8 warps as 2 (m) x 4 (n), warp tile 32 x 16 (4 x 2 DMMA tiles, re and im planes), two
+// CTAs per SM (registers).  A stage holds kZSubs sub-tiles of 8 complex k = 128-byte rows each (the
+// widest row the swizzle allows), so one barrier round covers 16 k.  A lane's fragment is one complex element (16 bytes = one
 // swizzle chunk), a quarter-warp request is 2 rows x 4 k; it covers all eight chunks when the two
 // rows differ in bit 2, so lane group g owns row 4 (g & 1) + (g >> 1) of each 8-row tile — the same
 // assignment for both orientations.  M-major operands come as 8-row blocks of 1 KiB (one grouped
 // 4-D copy when the row count is a multiple of 8, else eight 3-D copies).
-constexpr int kZBK = 8, kZThreads = 256;
+constexpr int kZSubs = 2, kZBK = 8 * kZSubs, kZThreads = 256;
+constexpr int kZStageBytes = kZSubs * kStageBytes;  // per sub-tile: A tile (8 KiB) then B tile (8 KiB)
 __device__ __forceinline__ int perm_z(int g) { return 4 * (g & 1) + (g >> 1); }
 
 template <bool KMAJOR>
@@ -376,7 +378,7 @@ __global__ void __launch_bounds__(kZThreads, 2)
   constexpr bool CONJ_A = (OPA == BLB200_H), CONJ_B = (OPB == BLB200_H);
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)kStages * kStageBytes);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)kStages * kZStageBytes);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -396,24 +398,27 @@ __global__ void __launch_bounds__(kZThreads, 2)
 
   const int KT = (k + kZBK - 1) / kZBK;
   auto issue = [&](int s, int kt) {  // one thread; map coordinates along a complex dimension count doubles
-    unsigned char* st = smem + (size_t)s * kStageBytes;
-    const int k0 = kt * kZBK;
-    mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
-    if (AK) {
-      tma_load_3d(st, &map_a, 2 * k0, m0, item, &full_bar[s]);
-    } else if (a_grouped) {
-      tma_load_4d(st, &map_a, 0, k0, m0 >> 3, item, &full_bar[s]);
-    } else {
+    mbar_arrive_expect_tx(&full_bar[s], kZStageBytes);
 #pragma unroll
-      for (int b = 0; b < 8; ++b) tma_load_3d(st + b * 1024, &map_a, 2 * (m0 + 8 * b), k0, item, &full_bar[s]);
-    }
-    if (BKM) {
-      tma_load_3d(st + kOperandBytes, &map_b, 2 * k0, n0, item, &full_bar[s]);
-    } else if (b_grouped) {
-      tma_load_4d(st + kOperandBytes, &map_b, 0, k0, n0 >> 3, item, &full_bar[s]);
-    } else {
+    for (int sub = 0; sub < kZSubs; ++sub) {
+      unsigned char* st = smem + (size_t)s * kZStageBytes + (size_t)sub * kStageBytes;
+      const int k0 = kt * kZBK + 8 * sub;  // sub-tiles wholly past k are zero-filled by the maps' bounds
+      if (AK) {
+        tma_load_3d(st, &map_a, 2 * k0, m0, item, &full_bar[s]);
+      } else if (a_grouped) {
+        tma_load_4d(st, &map_a, 0, k0, m0 >> 3, item, &full_bar[s]);
+      } else {
 #pragma unroll
-      for (int b = 0; b < 8; ++b) tma_load_3d(st + kOperandBytes + b * 1024, &map_b, 2 * (n0 + 8 * b), k0, item, &full_bar[s]);
+        for (int b = 0; b < 8; ++b) tma_load_3d(st + b * 1024, &map_a, 2 * (m0 + 8 * b), k0, item, &full_bar[s]);
+      }
+      if (BKM) {
+        tma_load_3d(st + kOperandBytes, &map_b, 2 * k0, n0, item, &full_bar[s]);
+      } else if (b_grouped) {
+        tma_load_4d(st + kOperandBytes, &map_b, 0, k0, n0 >> 3, item, &full_bar[s]);
+      } else {
+#pragma unroll
+        for (int b = 0; b < 8; ++b) tma_load_3d(st + kOperandBytes + b * 1024, &map_b, 2 * (n0 + 8 * b), k0, item, &full_bar[s]);
+      }
     }
   };
   if (tid == 0)
@@ -443,10 +448,11 @@ __global__ void __launch_bounds__(kZThreads, 2)
       issue(issued % kStages, issued);
       ++issued;
     }
-    const unsigned char* as = smem + (size_t)s * kStageBytes;
-    const unsigned char* bs = as + kOperandBytes;
 #pragma unroll
-    for (int k4 = 0; k4 < kZBK / 4; ++k4) {
+    for (int k4all = 0; k4all < kZBK / 4; ++k4all) {
+      const int k4 = k4all & 1;
+      const unsigned char* as = smem + (size_t)s * kZStageBytes + (size_t)(k4all >> 1) * kStageBytes;
+      const unsigned char* bs = as + kOperandBytes;
       double2 af[4], bf[2];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -499,7 +505,7 @@ __global__ void __launch_bounds__(kZThreads, 2)
 template <int OPA, int OPB>
 int launch_op_z(const GemmParams& p, cudaStream_t stream) {
   constexpr bool AK = (OPA != BLB200_N), BKM = (OPB == BLB200_N);
-  const size_t smem = (size_t)kStages * kStageBytes + kStages * sizeof(uint64_t) + 1024;
+  const size_t smem = (size_t)kStages * kZStageBytes + kStages * sizeof(uint64_t) + 1024;
   const int tiles_m = (p.m + kBM - 1) / kBM, tiles_n = (p.n + kBN - 1) / kBN;
   const long long total = (long long)tiles_m * tiles_n * p.batch;
   if (total > 0x7fffffffLL) return BLB200_E_UNSUPPORTED;
@@ -511,19 +517,19 @@ int launch_op_z(const GemmParams& p, cudaStream_t stream) {
   int a_kind = AK ? kMapKMajor : (a_rows % 8 == 0 && grouped_ok.load() ? kMapRowGroups : kMapRows16);
   int b_kind = BKM ? kMapKMajor : (b_rows % 8 == 0 && grouped_ok.load() ? kMapRowGroups : kMapRows16);
   // rows, ld and strides in doubles; M-major boxes span 8 k, a grouped copy takes 8 groups of 8 rows
-  int rc = maps.get(&map_a, p.a, 2LL * a_rows, a_cols, 2 * p.lda, 2 * p.sa, p.batch, a_kind, kZBK, 8);
+  int rc = maps.get(&map_a, p.a, 2LL * a_rows, a_cols, 2 * p.lda, 2 * p.sa, p.batch, a_kind, 8, 8);
   if (rc != BLB200_OK && a_kind == kMapRowGroups) {
     grouped_ok.store(0);
     a_kind = kMapRows16;
     if (b_kind == kMapRowGroups) b_kind = kMapRows16;
-    rc = maps.get(&map_a, p.a, 2LL * a_rows, a_cols, 2 * p.lda, 2 * p.sa, p.batch, a_kind, kZBK, 8);
+    rc = maps.get(&map_a, p.a, 2LL * a_rows, a_cols, 2 * p.lda, 2 * p.sa, p.batch, a_kind, 8, 8);
   }
   if (rc != BLB200_OK) return rc;
-  rc = maps.get(&map_b, p.b, 2LL * b_rows, b_cols, 2 * p.ldb, 2 * p.sb, p.batch, b_kind, kZBK, 8);
+  rc = maps.get(&map_b, p.b, 2LL * b_rows, b_cols, 2 * p.ldb, 2 * p.sb, p.batch, b_kind, 8, 8);
   if (rc != BLB200_OK && b_kind == kMapRowGroups) {
     grouped_ok.store(0);
     b_kind = kMapRows16;
-    rc = maps.get(&map_b, p.b, 2LL * b_rows, b_cols, 2 * p.ldb, 2 * p.sb, p.batch, b_kind, kZBK, 8);
+    rc = maps.get(&map_b, p.b, 2LL * b_rows, b_cols, 2 * p.ldb, 2 * p.sb, p.batch, b_kind, 8, 8);
   }
   if (rc != BLB200_OK) return rc;
   auto kern = gemm_dmma_tma_z_kernel<OPA, OPB>;
