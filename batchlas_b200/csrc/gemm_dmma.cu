@@ -61,8 +61,7 @@ __device__ __forceinline__ void load_tile_pitched(unsigned char* smem, const uns
       if constexpr (AL) {
         cp_async16(dst, src, valid * ES);
       } else {
-#pragma unroll
-        for (int e = 0; e < V; ++e) cp_async_elem<ES>(dst + e * ES, e < valid ? src + e * ES : src, e < valid ? ES : 0);
+        cp_async_chunk_widest<ES>(dst, src, valid);  // a warp copies one stored column: a 16-byte copy where that column is aligned
       }
     }
   } else {

@@ -40,12 +40,17 @@ __device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
 constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3, THREADS = 256;
 constexpr int A_STAGE = BK * BM * 4, B_STAGE = BK * BN * 4;  // 16 KiB each
 
-// 16 bytes into a stage: one copy, or four float copies when the source is only float-aligned
-// (measured faster than giving consecutive threads consecutive floats: 1024^3 41.8 against 39.7 TFLOP/s).
-template <bool AL>
+// 16 bytes into a stage: one copy, or — when the source is only float-aligned — the widest copies its
+// address allows (WIDEST: rows of an M- or N-major tile, where a warp copies one stored column and the
+// choice is uniform) or four float copies (K-major rows, whose alignment changes from row to row
+// inside a warp).  Chunk-wise measured faster than giving consecutive threads consecutive floats
+// (1024^3: 41.8 against 39.7 TFLOP/s).
+template <bool AL, bool WIDEST = false>
 __device__ __forceinline__ void copy_chunk(unsigned char* dst, const float* src, int valid) {
   if constexpr (AL) {
     cp_async16(dst, src, valid * 4);
+  } else if constexpr (WIDEST) {
+    cp_async_chunk_widest<4>(dst, reinterpret_cast<const unsigned char*>(src), valid);
   } else {
 #pragma unroll
     for (int e = 0; e < 4; ++e) cp_async_elem<4>(dst + 4 * e, e < valid ? src + e : src, e < valid ? 4 : 0);
@@ -63,7 +68,7 @@ __device__ __forceinline__ void load_a(unsigned char* dst, const float* __restri
     int valid = (gk < K) ? (M - gm) : 0;
     valid = valid < 0 ? 0 : (valid > 4 ? 4 : valid);
     const float* src = valid ? A + (long long)gk * lda + gm : A;
-    copy_chunk<AL>(dst + kk * (BM * 4) + mc * 16, src, valid);
+    copy_chunk<AL, true>(dst + kk * (BM * 4) + mc * 16, src, valid);
   }
 }
 
@@ -89,7 +94,7 @@ __device__ __forceinline__ void load_b(unsigned char* dst, const float* __restri
       int valid = (gk < K) ? (N - gn) : 0;
       valid = valid < 0 ? 0 : (valid > 4 ? 4 : valid);
       const float* src = valid ? B + (long long)gk * ldb + gn : B;
-      copy_chunk<AL>(dst + kk * (BN * 4) + nc * 16, src, valid);
+      copy_chunk<AL, true>(dst + kk * (BN * 4) + nc * 16, src, valid);
     }
   }
 }

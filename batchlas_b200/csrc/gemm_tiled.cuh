@@ -83,7 +83,7 @@ __device__ __forceinline__ void load_tile(unsigned char* smem, const T* __restri
       const T* src = valid ? base + (long long)gk * ld + gm : base;
       unsigned char* dst = smem + (size_t)kk * (BMN * sizeof(T)) + (size_t)mc * 16;
       if constexpr (AL) cp_async16(dst, src, valid * (int)sizeof(T));
-      else copy_chunk_by_elements<(int)sizeof(T)>(dst, (const unsigned char*)src, valid);
+      else cp_async_chunk_widest<(int)sizeof(T)>(dst, (const unsigned char*)src, valid);  // a warp copies one stored column: uniform choice
     }
   } else {
     constexpr int CH_PER_ROW = BK / V, CHUNKS = BMN * CH_PER_ROW, PITCH = BK * (int)sizeof(T) + 16;

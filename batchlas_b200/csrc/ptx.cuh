@@ -113,6 +113,25 @@ __device__ __forceinline__ void cp_async_elem(void* dst_smem, const void* src_gm
                "r"(src_bytes)
                : "memory");
 }
+// One 16-byte stage chunk from a source that is only ES-aligned (ES = 4 or 8 bytes per element,
+// `valid` elements of the chunk exist, the rest is zero-filled): the widest copies the source
+// address allows — one 16-byte copy when it happens to be 16-byte aligned (with an odd leading
+// dimension every second column of doubles is), two 8-byte copies for floats on an 8-byte boundary
+// (ld = 258: every other column), else element by element.  The destination is 16-byte aligned.
+template <int ES>
+__device__ __forceinline__ void cp_async_chunk_widest(unsigned char* dst, const unsigned char* src, int valid) {
+  constexpr int V = 16 / ES;
+  const uintptr_t a = reinterpret_cast<uintptr_t>(src);
+  if (valid == V && (a & 15u) == 0) {
+    cp_async_elem<16>(dst, src, 16);
+  } else if (ES == 4 && valid == V && (a & 7u) == 0) {
+    cp_async_elem<8>(dst, src, 8);
+    cp_async_elem<8>(dst + 8, src + 8, 8);
+  } else {
+#pragma unroll
+    for (int e = 0; e < V; ++e) cp_async_elem<ES>(dst + e * ES, e < valid ? src + e * ES : src, e < valid ? ES : 0);
+  }
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
