@@ -1,4 +1,8 @@
-// Per-queue workspace arena backed by the stream-ordered allocator (cudaMallocAsync).
+// Per-queue workspace arena backed by a stream-ordered memory pool of its own: every arena creates
+// one cudaMemPool_t on its device (cudaMemPoolCreate) and takes its blocks from it with
+// cudaMallocFromPoolAsync on the queue's stream, so a queue's scratch never mixes with the
+// application's default pool, trim() really returns the bytes to the driver (cudaMemPoolTrimTo), and
+// destroying the queue destroys the pool.
 //
 // Lease semantics follow BatchLAS's WorkspaceArena (src/queue.hh:41-226) and WorkspaceLease
 // (include/util/workspace.hh:70-162):
@@ -9,8 +13,7 @@
 //     and then also reclaims any loans beneath it that were already returned out of order;
 //   * releasing any other loan only marks it; its bytes stay reserved until it becomes innermost;
 //   * trim() refuses while any loan is outstanding, otherwise drains the stream and frees all.
-// The reference's blocks are shared USM; here they are device memory owned by the queue's
-// stream, so a block freed by trim/destroy goes back to the device's memory pool, not the OS.
+// The reference's blocks are shared USM; here they are device memory of the arena's own pool.
 #include <algorithm>
 #include <new>
 #include <stdlib.h>
@@ -30,6 +33,7 @@ struct blb200_arena {
   };
   int device;  // < 0: host malloc backing (bookkeeping tests without a GPU)
   cudaStream_t stream;
+  cudaMemPool_t pool = nullptr;  // created with the first block
   size_t align;
   std::vector<Block> blocks;
   size_t cur_block = 0, cur_offset = 0;
@@ -43,8 +47,17 @@ struct blb200_arena {
       *out = (char*)p;
       return BLB200_OK;
     }
+    if (!pool) {
+      cudaMemPoolProps props = {};
+      props.allocType = cudaMemAllocationTypePinned;  // ordinary device memory
+      props.handleTypes = cudaMemHandleTypeNone;
+      props.location.type = cudaMemLocationTypeDevice;
+      props.location.id = device;
+      cudaError_t e = cudaMemPoolCreate(&pool, &props);
+      if (e != cudaSuccess) return (int)e;
+    }
     void* p = nullptr;
-    cudaError_t e = cudaMallocAsync(&p, bytes, stream);
+    cudaError_t e = cudaMallocFromPoolAsync(&p, bytes, pool, stream);
     if (e != cudaSuccess) return (int)e;
     *out = (char*)p;
     return BLB200_OK;
@@ -81,6 +94,10 @@ int blb200_arena_destroy(blb200_arena* a) {
   if (!a) return BLB200_E_NULL;
   if (a->device >= 0 && !a->blocks.empty()) cudaStreamSynchronize(a->stream);
   a->free_all();
+  if (a->pool) {
+    cudaStreamSynchronize(a->stream);  // the frees above are stream-ordered
+    cudaMemPoolDestroy(a->pool);
+  }
   delete a;
   return BLB200_OK;
 }
@@ -155,6 +172,10 @@ int blb200_arena_trim(blb200_arena* a) {
     if (e != cudaSuccess) return BLB200_E_INTERNAL;
   }
   a->free_all();
+  if (a->pool) {
+    cudaStreamSynchronize(a->stream);  // the frees above are stream-ordered
+    cudaMemPoolTrimTo(a->pool, 0);     // back to the driver, as the reference's trim frees its USM blocks
+  }
   return 1;
 }
 

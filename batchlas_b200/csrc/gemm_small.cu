@@ -38,8 +38,6 @@
 #include <stdlib.h>
 #include <string.h>
 
-#include <type_traits>
-
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -290,25 +288,22 @@ __host__ __device__ constexpr PackMode pack_mode() {
 
 // One half-K (32 k) of the product for this lane's 8 x 8 block.  `acc` is float[8][8] in scalar
 // mode; in the packed modes the same 64 registers are addressed as uint64_t[32].
-// CS selects the columns: 0 = all eight of the lane, 1 = its first four, 2 = its last four (two warp
-// pairs sharing one item in the last round of an SM take half the columns each).
-template <bool A_KMAJOR, bool B_KMAJOR, int CS = 0>
+template <bool A_KMAJOR, bool B_KMAJOR>
 __device__ __forceinline__ void mma64_half(const unsigned char* __restrict__ As, const unsigned char* __restrict__ Bs,
                                            int ti, int tj, int hw, float (&acc)[8][8], uint64_t (&accp)[32]) {
   constexpr PackMode PM = pack_mode<A_KMAJOR, B_KMAJOR>();
-  constexpr int C0 = CS == 2 ? 4 : 0, NC = CS == 0 ? 8 : 4;  // this call's columns: C0 .. C0 + NC - 1
   const float4* As4 = reinterpret_cast<const float4*>(As);
   const float4* Bs4 = reinterpret_cast<const float4*>(Bs);
   const ulonglong2* As2 = reinterpret_cast<const ulonglong2*>(As);
   const ulonglong2* Bs2 = reinterpret_cast<const ulonglong2*>(Bs);
   if constexpr (PM == kRowPairs && B_KMAJOR) {
-    // B fragments for a whole 4-k chunk come from swizzled loads, one per column; they are fetched
-    // one chunk ahead (two register buffers) so that their latency hides behind the previous chunk's FMAs.
-    float bf[2][NC][4];  // [buffer][col][kk]; column j = 32hw + tj + 4c
-    auto load_b = [&](int kc, float (&dst)[NC][4]) {
+    // B fragments for a whole 4-k chunk come from 8 swizzled loads; they are fetched one chunk
+    // ahead (two register buffers) so that their latency hides behind the previous chunk's FMAs.
+    float bf[2][8][4];  // [buffer][col][kk]; column j = 32hw + tj + 4c
+    auto load_b = [&](int kc, float (&dst)[8][4]) {
 #pragma unroll
-      for (int c = 0; c < NC; ++c) {
-        const int j = 32 * hw + tj + 4 * (C0 + c);
+      for (int c = 0; c < 8; ++c) {
+        const int j = 32 * hw + tj + 4 * c;
         const float4 v = Bs4[j * 8 + (kc ^ (j & 7))];
         dst[c][0] = v.x; dst[c][1] = v.y; dst[c][2] = v.z; dst[c][3] = v.w;
       }
@@ -323,10 +318,10 @@ __device__ __forceinline__ void mma64_half(const unsigned char* __restrict__ As,
         const ulonglong2 hi = As2[(4 * kc + kk) * 16 + 8 + ti];
         const uint64_t a2[4] = {lo.x, lo.y, hi.x, hi.y};
 #pragma unroll
-        for (int c = 0; c < NC; ++c) {
+        for (int c = 0; c < 8; ++c) {
           const uint64_t bd = dup2(bf[kc & 1][c][kk]);
 #pragma unroll
-          for (int rp = 0; rp < 4; ++rp) ffma2(accp[rp * 8 + C0 + c], a2[rp], bd);
+          for (int rp = 0; rp < 4; ++rp) ffma2(accp[rp * 8 + c], a2[rp], bd);
         }
       }
     }
@@ -335,17 +330,13 @@ __device__ __forceinline__ void mma64_half(const unsigned char* __restrict__ As,
 #pragma unroll 2
   for (int kc = 0; kc < 8; ++kc) {
     if constexpr (PM == kRowPairs) {
-      float bf[NC][4];  // [col][kk], k-rows of 256 bytes: columns 32hw + 8tj + C0 + c
+      float bf[8][4];  // [col][kk], k-rows of 256 bytes: columns 32hw + 8tj + c
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
-        if constexpr (CS != 2) {
-          const float4 v0 = Bs4[(4 * kc + kk) * 16 + 8 * hw + 2 * tj];
-          bf[0][kk] = v0.x; bf[1][kk] = v0.y; bf[2][kk] = v0.z; bf[3][kk] = v0.w;
-        }
-        if constexpr (CS != 1) {
-          const float4 v1 = Bs4[(4 * kc + kk) * 16 + 8 * hw + 2 * tj + 1];
-          bf[NC - 4][kk] = v1.x; bf[NC - 3][kk] = v1.y; bf[NC - 2][kk] = v1.z; bf[NC - 1][kk] = v1.w;
-        }
+        const float4 v0 = Bs4[(4 * kc + kk) * 16 + 8 * hw + 2 * tj];
+        const float4 v1 = Bs4[(4 * kc + kk) * 16 + 8 * hw + 2 * tj + 1];
+        bf[0][kk] = v0.x; bf[1][kk] = v0.y; bf[2][kk] = v0.z; bf[3][kk] = v0.w;
+        bf[4][kk] = v1.x; bf[5][kk] = v1.y; bf[6][kk] = v1.z; bf[7][kk] = v1.w;
       }
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
@@ -354,10 +345,10 @@ __device__ __forceinline__ void mma64_half(const unsigned char* __restrict__ As,
         const ulonglong2 hi = As2[(4 * kc + kk) * 16 + 8 + ti];
         const uint64_t a2[4] = {lo.x, lo.y, hi.x, hi.y};
 #pragma unroll
-        for (int c = 0; c < NC; ++c) {
+        for (int c = 0; c < 8; ++c) {
           const uint64_t bd = dup2(bf[c][kk]);
 #pragma unroll
-          for (int rp = 0; rp < 4; ++rp) ffma2(accp[rp * 8 + C0 + c], a2[rp], bd);
+          for (int rp = 0; rp < 4; ++rp) ffma2(accp[rp * 8 + c], a2[rp], bd);
         }
       }
     } else if constexpr (PM == kColPairs) {
@@ -369,33 +360,26 @@ __device__ __forceinline__ void mma64_half(const unsigned char* __restrict__ As,
       }
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
-        // column pairs (8tj+0,1) (2,3) from the first 16 bytes, (4,5) (6,7) from the second
-        uint64_t b2[4] = {0, 0, 0, 0};
-        if constexpr (CS != 2) {
-          const ulonglong2 v0 = Bs2[(4 * kc + kk) * 16 + 8 * hw + 2 * tj];
-          b2[0] = v0.x; b2[1] = v0.y;
-        }
-        if constexpr (CS != 1) {
-          const ulonglong2 v1 = Bs2[(4 * kc + kk) * 16 + 8 * hw + 2 * tj + 1];
-          b2[2] = v1.x; b2[3] = v1.y;
-        }
+        const ulonglong2 v0 = Bs2[(4 * kc + kk) * 16 + 8 * hw + 2 * tj];
+        const ulonglong2 v1 = Bs2[(4 * kc + kk) * 16 + 8 * hw + 2 * tj + 1];
+        const uint64_t b2[4] = {v0.x, v0.y, v1.x, v1.y};  // column pairs (8tj+0,1) (2,3) (4,5) (6,7)
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
           const uint64_t ad = dup2(af[r][kk]);
 #pragma unroll
-          for (int cp = C0 / 2; cp < (C0 + NC) / 2; ++cp) ffma2(accp[r * 4 + cp], ad, b2[cp]);
+          for (int cp = 0; cp < 4; ++cp) ffma2(accp[r * 4 + cp], ad, b2[cp]);
         }
       }
     } else {
-      float af[8][4], bf[NC][4];
+      float af[8][4], bf[8][4];
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
         const float4 v = As4[(ti + 8 * r) * 8 + (kc ^ ti)];
         af[r][0] = v.x; af[r][1] = v.y; af[r][2] = v.z; af[r][3] = v.w;
       }
 #pragma unroll
-      for (int c = 0; c < NC; ++c) {
-        const int j = 32 * hw + tj + 4 * (C0 + c);
+      for (int c = 0; c < 8; ++c) {
+        const int j = 32 * hw + tj + 4 * c;
         const float4 v = Bs4[j * 8 + (kc ^ (j & 7))];
         bf[c][0] = v.x; bf[c][1] = v.y; bf[c][2] = v.z; bf[c][3] = v.w;
       }
@@ -404,7 +388,7 @@ __device__ __forceinline__ void mma64_half(const unsigned char* __restrict__ As,
 #pragma unroll
         for (int r = 0; r < 8; ++r)
 #pragma unroll
-          for (int c = 0; c < NC; ++c) acc[r][C0 + c] = fmaf(af[r][kk], bf[c][kk], acc[r][C0 + c]);
+          for (int c = 0; c < 8; ++c) acc[r][c] = fmaf(af[r][kk], bf[c][kk], acc[r][c]);
     }
   }
 }
@@ -442,13 +426,13 @@ __global__ void __launch_bounds__(64 * PAIRS, 1)
   // the 128-byte swizzle is a function of the shared-memory address: slots must be 1024-byte aligned
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)kSlots64 * kSlotBytes64);
-  uint32_t* left_cnt = reinterpret_cast<uint32_t*>(full_bar + kSlots64);  // per slot: warps that have left it, ever
+  uint32_t* left = reinterpret_cast<uint32_t*>(full_bar + kSlots64);  // per slot: warps that have left it, ever
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSlots64; ++s) {
       mbar_init(&full_bar[s], 1);
-      left_cnt[s] = 0u;
+      left[s] = 0u;
     }
     mbar_fence_init();
   }
@@ -464,29 +448,14 @@ __global__ void __launch_bounds__(64 * PAIRS, 1)
 
   const int pair = warp >> 1, hw = warp & 1;
   const int ti = lane & 7, tj = lane >> 3;
-  // Items of this pair: pair, pair + PAIRS, ... for the SM's full rounds.  Of the items left over
-  // for a last round, each goes to one pair — or, when at most half the pairs would have one, to two
-  // pairs that take half of the columns each (both fetch the whole item into their own slots), so
-  // that the round's work is spread over twice as many warps.
-  const int full_rounds = my_items / kPairs64, left = my_items - full_rounds * kPairs64;
-  const bool shared_tail = left > 0 && 2 * left <= kPairs64;
-  int tail_item = -1, tail_cs = 0;
-  if (shared_tail) {
-    if (pair < 2 * left) {
-      tail_item = full_rounds * kPairs64 + (pair >> 1);
-      tail_cs = 1 + (pair & 1);
-    }
-  } else if (pair < left) {
-    tail_item = full_rounds * kPairs64 + pair;
-  }
-  const int pair_items = full_rounds + (tail_item >= 0 ? 1 : 0);
+  // items of this pair: pair, pair + PAIRS, ...
+  const int pair_items = (my_items > pair) ? (my_items - 1 - pair) / kPairs64 + 1 : 0;
   const int pair_halves = 2 * pair_items;
-  auto item_of = [&](int it) { return it < full_rounds ? pair + it * kPairs64 : tail_item; };
 
   auto issue = [&](int q, int slot_of_pair) {
     const int s = pair * kSlotsPerPair64 + slot_of_pair;
     unsigned char* st = smem + (size_t)s * kSlotBytes64;
-    const int j = item_of(q >> 1), half = q & 1;
+    const int j = pair + (q >> 1) * kPairs64, half = q & 1;
     const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
     mbar_arrive_expect_tx(&full_bar[s], kSlotBytes64);
     if (A_KMAJOR) tma_load_3d(st, &map_a, 32 * half, 0, (int)item, &full_bar[s]);
@@ -500,13 +469,7 @@ __global__ void __launch_bounds__(64 * PAIRS, 1)
   int slot_i = 0;      // q % SPP
   uint32_t round = 0;  // q / SPP
   int q = 0;
-  bool lost = false;
-
-  // One item: both K halves out of the pair's slots, then alpha / beta and the stores of this
-  // warp's columns (CS: all of them, or one half of them in a shared last round).
-  auto do_item = [&](int j, auto cs_tag) {
-    constexpr int CS = decltype(cs_tag)::value;
-    constexpr int C0 = CS == 2 ? 4 : 0, NC = CS == 0 ? 8 : 4;
+  for (int j = pair; j < my_items; j += kPairs64) {
     constexpr PackMode PM = pack_mode<A_KMAJOR, B_KMAJOR>();
     float acc[8][8];
     uint64_t accp[32];
@@ -519,15 +482,12 @@ __global__ void __launch_bounds__(64 * PAIRS, 1)
 #pragma unroll 1
     for (int half = 0; half < 2; ++half, ++q) {
       const int s = pair * kSlotsPerPair64 + slot_i;
-      if (!mbar_wait(&full_bar[s], round & 1u, kWaitFull)) {
-        lost = true;
-        return;
-      }
+      if (!mbar_wait(&full_bar[s], round & 1u, kWaitFull)) return;
       const unsigned char* st = smem + (size_t)s * kSlotBytes64;
-      mma64_half<A_KMAJOR, B_KMAJOR, CS>(st, st + kHalfBytes64, ti, tj, hw, acc, accp);
+      mma64_half<A_KMAJOR, B_KMAJOR>(st, st + kHalfBytes64, ti, tj, hw, acc, accp);
       __syncwarp();
       if (lane == 0) {
-        const uint32_t before = smem_add_acq_rel(&left_cnt[s], 1u);
+        const uint32_t before = smem_add_acq_rel(&left[s], 1u);
         if ((before & 1u) && q + kSlotsPerPair64 < pair_halves) {  // the pair's other warp left earlier
           fence_async_smem();
           issue(q + kSlotsPerPair64, slot_i);
@@ -562,7 +522,7 @@ __global__ void __launch_bounds__(64 * PAIRS, 1)
     const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
     float* Cg = C + item * sc;
 #pragma unroll
-    for (int c = C0; c < C0 + NC; ++c) {
+    for (int c = 0; c < 8; ++c) {
       const int col = B_KMAJOR ? (32 * hw + tj + 4 * c) : (32 * hw + 8 * tj + c);
       if (A_KMAJOR) {
 #pragma unroll
@@ -591,13 +551,6 @@ __global__ void __launch_bounds__(64 * PAIRS, 1)
         }
       }
     }
-  };
-
-  for (int it = 0; it < full_rounds && !lost; ++it) do_item(pair + it * kPairs64, std::integral_constant<int, 0>{});
-  if (tail_item >= 0 && !lost) {
-    if (tail_cs == 0) do_item(tail_item, std::integral_constant<int, 0>{});
-    else if (tail_cs == 1) do_item(tail_item, std::integral_constant<int, 1>{});
-    else do_item(tail_item, std::integral_constant<int, 2>{});
   }
 }
 

@@ -317,7 +317,7 @@ def time_op(torch, launch, restore, reps):
 def sustained_run(torch, launch, restore, one_ms, local_rank, seconds=2.0):
     """The same launch repeated for `seconds` or more of device time; returns ms per launch and the
     clocks sampled meanwhile (median SM MHz under load, throttle reasons)."""
-    reps = int(max(3, min(20000, seconds * 1e3 / max(one_ms, 1e-3))))
+    reps = int(max(3, min(150000, seconds * 1e3 / max(one_ms, 1e-3))))
     smp = ClockSampler(local_rank)
     smp.start()
     time.sleep(0.15)

@@ -329,8 +329,7 @@ def test_small_kernel_rings_over_many_items(bl, size, oa, ob):
     a sample of items is checked against the oracle and every item against the generic kernel."""
     rng = np.random.default_rng(size)
     sms = torch.cuda.get_device_properties(0).multi_processor_count
-    # 6 + r items per SM for r = 1..5: the 64^3 kernel's last round with one, two or three leftover
-    # items (each shared by two warp pairs, half the columns each) and with four or five (one pair each)
+    # 6 + r items per SM for r = 1..5: the 64^3 kernel's six warp pairs with a partly filled last round
     tails = [(sms * (6 + r) - (r & 1), 0.0 if r & 1 else -0.5) for r in range(1, 6)] if size == 64 else []
     for batch, beta in [(1, 0.0), (7, -0.5), (147, 0.0), (149, 1.0), (1000, -0.5), (1250, 1.0), (5003, 0.0)] + tails:
         p = oracle.make_problem("s", oa, ob, size, size, size, batch, alpha=1.5, beta=beta)
