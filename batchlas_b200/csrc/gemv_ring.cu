@@ -1,7 +1,8 @@
 // gemv for large batches of small packed matrices, fed by the same loader as the small-matrix gemm
-// kernels: one producer warp streams whole matrices into a shared-memory ring with untiled TMA bulk
-// copies (one producer lane per slot, full/empty mbarriers), consumer warps each take a matrix out of
-// the ring and form y = A x or y = A^T x from shared memory.  HBM sees nothing but long sequential
+// kernels: whole matrices stream into a shared-memory ring by untiled TMA bulk copies that complete
+// on one "full" mbarrier per slot; a slot belongs to one warp for the whole launch, which forms
+// y = A x or y = A^T x out of it and then itself issues the copies of the item that uses the slot
+// next (no producer warp, no "empty" barriers: see gemm_small.cu).  HBM sees nothing but long sequential
 // reads of A, so the kernel runs at copy speed where the load/compute loop of the general kernel is
 // latency-bound (a 32 x 32 float matrix is only 4 KiB).
 //
@@ -13,8 +14,8 @@
 // at most 128, item size at most 16 KiB; A, x and y items each a multiple of 16 bytes long and
 // starting on 16-byte boundaries (what a bulk copy needs).
 //
-// Ring discipline: the slot count is a multiple of the consumer count and slot s always belongs to
-// consumer s % CW, so a consumer never waits on a round of a slot before finishing the previous one.
+// Ring discipline: the slot count is a multiple of the warp count and slot s always belongs to
+// warp s % CW, so a warp never waits on a round of a slot before finishing the previous one.
 // Every wait is bounded; on expiry the waiter records a code in the device status word and returns.
 #include "common.cuh"
 #include "ptx.cuh"
@@ -22,7 +23,7 @@
 namespace blb200 {
 namespace {
 
-enum WaitCode { kRingWaitFull = 201, kRingWaitEmpty = 202 };
+enum WaitCode { kRingWaitFull = 201 };
 constexpr int kMaxItemBytes = 16384;
 constexpr int kMaxDim = 128;
 
@@ -40,30 +41,55 @@ __device__ __forceinline__ T add2(T a, T b) {
   else return a + b;
 }
 
-// CW consumer warps; blockDim = 32 * (1 + CW); dynamic smem: stages * slot_bytes, then the barriers,
+// What one lane needs to issue the copies of an item into a slot.  Kept out of line: inlined into
+// the item loop it pushed the transposed variants past their register budget (720 bytes of spills).
+template <typename T>
+struct RingCopy {
+  const T* A;
+  const T* X;
+  const T* Y;
+  long long sa, sx, sy;
+  unsigned char* smem;
+  uint64_t* full_bar;
+  int slot_bytes;
+  uint32_t a_bytes, x_bytes, y_bytes;
+  bool beta_zero;
+};
+template <typename T, bool XY_RING>
+__device__ __noinline__ void ring_issue(RingCopy<T> c, int slot, int jj) {
+  unsigned char* st = c.smem + (size_t)slot * c.slot_bytes;
+  const long long item = (long long)blockIdx.x + (long long)jj * gridDim.x;
+  if (XY_RING) {
+    mbar_arrive_expect_tx(&c.full_bar[slot], c.a_bytes + c.x_bytes + (c.beta_zero ? 0u : c.y_bytes));
+    bulk_g2s(st, c.A + item * c.sa, c.a_bytes, &c.full_bar[slot]);
+    bulk_g2s(st + c.a_bytes, c.X + item * c.sx, c.x_bytes, &c.full_bar[slot]);
+    if (!c.beta_zero) bulk_g2s(st + c.a_bytes + c.x_bytes, c.Y + item * c.sy, c.y_bytes, &c.full_bar[slot]);
+  } else {
+    mbar_arrive_expect_tx(&c.full_bar[slot], c.a_bytes);
+    bulk_g2s(st, c.A + item * c.sa, c.a_bytes, &c.full_bar[slot]);
+  }
+}
+
+// CW warps; blockDim = 32 * CW; dynamic smem: stages * slot_bytes, then the barriers,
 // then (XY_RING = false) CW * kMaxDim elements of per-warp scratch for x.
 // XY_RING = true:  a slot holds [A item | x item | old y item (only when beta != 0)].
 // XY_RING = false: a slot holds the A item; each consumer warp fetches x and the old y itself, one
 //                  item ahead.  For matrices of a few KiB the two extra 128-byte bulk copies per item
 //                  cost more than they save (32 x 32 float: 0.55 of the copy bandwidth against 0.85).
 template <typename T, int CW, bool TRANS, bool XY_RING>
-__global__ void __launch_bounds__(32 * (1 + CW), 1)
+__global__ void __launch_bounds__(32 * CW, 1)
     gemv_ring_kernel(const T* __restrict__ A, const T* __restrict__ X, T* __restrict__ Y, int m, int n, long long sa,
                      long long sx, long long sy, int batch, T alpha, T beta, bool beta_zero, bool conj, int stages,
                      int slot_bytes) {
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)stages * slot_bytes);
-  uint64_t* empty_bar = full_bar + stages;
   const int xlen = TRANS ? m : n, ylen = TRANS ? n : m;
   const uint32_t a_bytes = (uint32_t)(m * n * (int)sizeof(T)), x_bytes = (uint32_t)(xlen * (int)sizeof(T)),
                  y_bytes = (uint32_t)(ylen * (int)sizeof(T));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
-    }
+    for (int s = 0; s < stages; ++s) mbar_init(&full_bar[s], 1);
     mbar_fence_init();
   }
   __syncthreads();
@@ -71,30 +97,14 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
   // Items of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...; the j-th one uses slot j % stages.
   const int my_items = (batch > (int)blockIdx.x) ? (batch - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
-  if (warp == 0) {
-    if (lane < stages) {  // lane == slot
-      unsigned char* st = smem + (size_t)lane * slot_bytes;
-      uint32_t round = 0;
-      for (int j = lane; j < my_items; j += stages, ++round) {
-        if (!mbar_wait(&empty_bar[lane], (round & 1u) ^ 1u, kRingWaitEmpty)) return;
-        const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
-        if (XY_RING) {
-          mbar_arrive_expect_tx(&full_bar[lane], a_bytes + x_bytes + (beta_zero ? 0u : y_bytes));
-          bulk_g2s(st, A + item * sa, a_bytes, &full_bar[lane]);
-          bulk_g2s(st + a_bytes, X + item * sx, x_bytes, &full_bar[lane]);
-          if (!beta_zero) bulk_g2s(st + a_bytes + x_bytes, Y + item * sy, y_bytes, &full_bar[lane]);
-        } else {
-          mbar_arrive_expect_tx(&full_bar[lane], a_bytes);
-          bulk_g2s(st, A + item * sa, a_bytes, &full_bar[lane]);
-        }
-      }
-    }
-    return;
-  }
+  const RingCopy<T> copy{A, X, Y, sa, sx, sy, smem, full_bar, slot_bytes, a_bytes, x_bytes, y_bytes, beta_zero};
+  auto issue = [&](int slot, int jj) { ring_issue<T, XY_RING>(copy, slot, jj); };
 
-  const int cw = warp - 1;
+  const int cw = warp;
   constexpr int RV = kMaxDim / 32;
-  T* x_scratch = reinterpret_cast<T*>(empty_bar + stages) + (size_t)cw * kMaxDim;  // XY_RING = false only
+  T* x_scratch = reinterpret_cast<T*>(full_bar + stages) + (size_t)cw * kMaxDim;  // XY_RING = false only
+  if (lane == 0)
+    for (int slot = cw; slot < stages && slot < my_items; slot += CW) issue(slot, slot);
 
   // XY_RING = false: x and the old y of the next item are requested while this one is worked on
   T xr[RV], prior[RV];
@@ -208,13 +218,17 @@ __global__ void __launch_bounds__(32 * (1 + CW), 1)
         }
       }
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty_bar[s]);  // the slot may be refilled while we store
-
 #pragma unroll
     for (int r = 0; r < RV; ++r) {
       const int i = lane + 32 * r;
       if (i < ylen) yg[i] = epilogue<T>(alpha, acc[r], beta, beta_zero, &prior_now[r]);
+    }
+    // every lane is past its reads of the slot; the refill goes out right behind the (asynchronous)
+    // stores, where nothing of the item is live in registers any more
+    __syncwarp();
+    if (lane == 0 && j + stages < my_items) {
+      fence_async_smem();
+      issue(s, j + stages);
     }
     s += CW;
     if (s >= stages) {
@@ -230,7 +244,7 @@ template <typename T, int CW, bool TRANS, bool XY_RING>
 int launch_cw(const void* a, const void* x, void* y, int m, int n, int batch, long long sa, long long sx, long long sy,
               const double* alpha, const double* beta, bool conj, int stages, int slot_bytes, cudaStream_t stream) {
   const DeviceInfo& dev = device_info();
-  const size_t smem = (size_t)stages * slot_bytes + (size_t)stages * 2 * sizeof(uint64_t) +
+  const size_t smem = (size_t)stages * slot_bytes + (size_t)stages * sizeof(uint64_t) +
                       (XY_RING ? 0 : (size_t)CW * kMaxDim * sizeof(T));
   auto kern = gemv_ring_kernel<T, CW, TRANS, XY_RING>;
   static thread_local int configured_for = -1;
@@ -242,7 +256,7 @@ int launch_cw(const void* a, const void* x, void* y, int m, int n, int batch, lo
     configured_for = cur;
   }
   const int grid = batch < dev.sm_count ? batch : dev.sm_count;
-  kern<<<grid, 32 * (1 + CW), smem, stream>>>((const T*)a, (const T*)x, (T*)y, m, n, sa, sx, sy, batch,
+  kern<<<grid, 32 * CW, smem, stream>>>((const T*)a, (const T*)x, (T*)y, m, n, sa, sx, sy, batch,
                                             Scalar<T>::make(alpha[0], alpha[1]), Scalar<T>::make(beta[0], beta[1]),
                                             beta[0] == 0.0 && beta[1] == 0.0, conj, stages, slot_bytes);
   return (int)cudaGetLastError();
