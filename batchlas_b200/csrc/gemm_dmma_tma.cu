@@ -114,6 +114,10 @@ __global__ void __launch_bounds__(kThreads, 4)
     mbar_fence_init();
   }
   __syncthreads();
+  // Programmatic dependent launch: the next kernel's first CTAs may take their places while this
+  // grid drains; nothing here touches global memory before every earlier grid has finished.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const int KT = (k + kBK - 1) / kBK;
   auto issue = [&](int s, int kt) {  // one thread: the copies of k-tile kt into stage s
@@ -338,10 +342,19 @@ int launch_op(const GemmParams& p, cudaStream_t stream) {
     if (e != cudaSuccess) return (int)e;
     configured_for = cur;
   }
-  kern<<<(unsigned)total, kThreads, smem, stream>>>(map_a, map_b, (double*)p.c, p.sc, p.ldc, p.m, p.n, p.k, tiles_m,
-                                                   tiles_n, p.alpha[0], p.beta[0], a_kind == kMapRowGroups ? 1 : 0,
-                                                   b_kind == kMapRowGroups ? 1 : 0);
-  return (int)cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)total);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, kern, map_a, map_b, (double*)p.c, (long long)p.sc, (long long)p.ldc, p.m, p.n, p.k,
+                                 tiles_m, tiles_n, p.alpha[0], p.beta[0], a_kind == kMapRowGroups ? 1 : 0,
+                                 b_kind == kMapRowGroups ? 1 : 0);
 }
 
 
@@ -395,6 +408,10 @@ __global__ void __launch_bounds__(kZThreads, 2)
     mbar_fence_init();
   }
   __syncthreads();
+  // Programmatic dependent launch: the next kernel's first CTAs may take their places while this
+  // grid drains; nothing here touches global memory before every earlier grid has finished.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const int KT = (k + kZBK - 1) / kZBK;
   auto issue = [&](int s, int kt) {  // one thread; map coordinates along a complex dimension count doubles
@@ -541,11 +558,19 @@ int launch_op_z(const GemmParams& p, cudaStream_t stream) {
     if (e != cudaSuccess) return (int)e;
     configured_for = cur;
   }
-  kern<<<(unsigned)total, kZThreads, smem, stream>>>(map_a, map_b, (double2*)p.c, p.sc, p.ldc, p.m, p.n, p.k, tiles_m,
-                                                    tiles_n, make_double2(p.alpha[0], p.alpha[1]),
-                                                    make_double2(p.beta[0], p.beta[1]), a_kind == kMapRowGroups ? 1 : 0,
-                                                    b_kind == kMapRowGroups ? 1 : 0);
-  return (int)cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)total);
+  cfg.blockDim = dim3(kZThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, kern, map_a, map_b, (double2*)p.c, (long long)p.sc, (long long)p.ldc, p.m, p.n, p.k,
+                                 tiles_m, tiles_n, make_double2(p.alpha[0], p.alpha[1]), make_double2(p.beta[0], p.beta[1]),
+                                 a_kind == kMapRowGroups ? 1 : 0, b_kind == kMapRowGroups ? 1 : 0);
 }
 
 }  // namespace

@@ -402,6 +402,15 @@ __device__ __forceinline__ void tma_load_3d(void* dst_smem, const CUtensorMap* m
       : "memory");
 }
 
+// L2 prefetch hints: an untiled run, and one (32 k) x (64 rows) x (1 item) box of a tensor map.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src_gmem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int x0, int y0, int z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(map), "r"(x0), "r"(y0), "r"(z)
+               : "memory");
+}
+
 // Release-acquire counter bump in shared memory: whoever reads an odd old value knows that the
 // other warp of its pair has finished reading the slot as well.
 __device__ __forceinline__ uint32_t smem_add_acq_rel(uint32_t* p, uint32_t v) {
@@ -444,13 +453,27 @@ __global__ void __launch_bounds__(64 * PAIRS, 1)
   // grid drains (its barrier set-up then overlaps our tail); no thread touches global memory
   // (operand copies, the old C, the C stores) before every earlier grid in the stream has finished.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const int pair = warp >> 1, hw = warp & 1;
   const int ti = lane & 7, tj = lane >> 3;
   // items of this pair: pair, pair + PAIRS, ...
   const int pair_items = (my_items > pair) ? (my_items - 1 - pair) / kPairs64 + 1 : 0;
   const int pair_halves = 2 * pair_items;
+
+  // While the earlier grid is still running: ask for the pair's first half-items to be brought into
+  // L2.  A prefetch changes nothing that a program can observe (L2 is the point of coherence: a line
+  // that the earlier grid writes afterwards is simply updated there), so it may come before the
+  // dependency wait; the real copies then start from L2 instead of HBM.
+  if (hw == 0 && lane == 0)
+    for (int q = 0; q < kSlotsPerPair64 && q < pair_halves; ++q) {
+      const int j = pair + (q >> 1) * kPairs64, half = q & 1;
+      const long long item = (long long)blockIdx.x + (long long)j * gridDim.x;
+      if (A_KMAJOR) tma_prefetch_3d(&map_a, 32 * half, 0, (int)item);
+      else bulk_prefetch_l2(A + item * sa + half * (kMatElems64 / 2), kHalfBytes64);
+      if (B_KMAJOR) tma_prefetch_3d(&map_b, 32 * half, 0, (int)item);
+      else bulk_prefetch_l2(B + item * sb + half * (kMatElems64 / 2), kHalfBytes64);
+    }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   auto issue = [&](int q, int slot_of_pair) {
     const int s = pair * kSlotsPerPair64 + slot_of_pair;
