@@ -48,6 +48,32 @@ template <int ES, int BMN, int BK, int THREADS, bool KMAJOR, bool AL = true>
 __device__ __forceinline__ void load_tile_pitched(unsigned char* smem, const unsigned char* __restrict__ base,
                                                   long long ld, int MN0, int MN, int k0, int K, int tid) {
   constexpr int V = 16 / ES;  // elements per 16-byte chunk
+  if constexpr (!KMAJOR && !AL && ES == 8) {
+    // A stage row is one stored column: BMN consecutive doubles that may start on an odd 8-byte
+    // boundary.  Copy the 16-byte aligned superset of the run with 16-byte copies (one more chunk
+    // than an aligned row; it fits the row's 32 bytes of padding) and let the fragment reads of that
+    // row start 8 bytes further in (row_shift_bytes below: a per-lane constant).  The 8 bytes in front
+    // of a shifted row are never read; src-size stops every copy at the row's last valid element.
+    constexpr int CPR = BMN / 2 + 1, PITCH = BMN * ES + pad_for(ES, false);
+    const unsigned char* aligned_dummy = reinterpret_cast<const unsigned char*>(reinterpret_cast<uintptr_t>(base) & ~(uintptr_t)15);
+    const int left = MN - MN0;  // valid elements of a tile row (may exceed BMN)
+    // THREADS / BK threads share a row and take every (THREADS / BK)-th chunk of it (no division by 33)
+    constexpr int TPR = THREADS / BK;
+    static_assert(THREADS % BK == 0, "whole thread groups per stage row");
+    const int kk = tid / TPR, j0 = tid % TPR;
+    const int gk = k0 + kk;
+    const unsigned char* row = base + ((long long)gk * ld + MN0) * ES;
+    const int sh = (int)(reinterpret_cast<uintptr_t>(row) & 8u);
+    unsigned char* drow = smem + (size_t)kk * PITCH;
+#pragma unroll
+    for (int j = j0; j < CPR; j += TPR) {
+      const int e0 = 2 * j - (sh >> 3);  // this chunk holds tile elements e0 and e0 + 1
+      int bytes = 0;
+      if (gk < K && e0 < BMN) bytes = (e0 + 1 < left) ? 16 : (e0 < left ? 8 : 0);
+      cp_async16(drow + (size_t)j * 16, bytes ? row - sh + 16 * j : aligned_dummy, bytes);
+    }
+    return;
+  }
   if (!KMAJOR) {
     constexpr int CH_PER_ROW = BMN / V, CHUNKS = BK * CH_PER_ROW, PITCH = BMN * ES + pad_for(ES, false);
 #pragma unroll
@@ -156,6 +182,10 @@ __global__ void __launch_bounds__(32 * WM * WN, 16 / (WM * WN)) gemm_dmma_d_kern
   const int b_off = BKM ? (wn * 32 + g) * B_PITCH + t * 8 : t * B_PITCH + (wn * 32 + g) * 8;
   constexpr int A_MB = AK ? 8 * A_PITCH : 64;       // next 8 rows of m
   constexpr int B_NB = BKM ? 8 * B_PITCH : 64;      // next 8 columns of n
+  // element-aligned M-major rows are stored 8 bytes further in when their stored column starts on an
+  // odd 8-byte boundary; the row of this lane's fragments is k = 4 k4 + t, whose parity is t's
+  const int a_shift = (!AL && !AK) ? (int)(((reinterpret_cast<uintptr_t>(A) >> 3) + (unsigned long long)t * (unsigned long long)p.lda) & 1u) * 8 : 0;
+  const int b_shift = (!AL && BKM == false) ? (int)(((reinterpret_cast<uintptr_t>(B) >> 3) + (unsigned long long)t * (unsigned long long)p.ldb) & 1u) * 8 : 0;
   constexpr int A_K4 = AK ? 0 : 4 * A_PITCH;        // next 4 k (K-major: the swizzled group below)
   constexpr int B_K4 = BKM ? 0 : 4 * B_PITCH;
   const int ksw = (g & 3) << 5;                      // K-major rows: 4-k group q is stored at q ^ (row & 3)
@@ -172,8 +202,8 @@ __global__ void __launch_bounds__(32 * WM * WN, 16 / (WM * WN)) gemm_dmma_d_kern
       }
       cp_async_commit();
     }
-    const unsigned char* as = As + (size_t)(kt % STAGES) * A_STAGE + a_off;
-    const unsigned char* bs = Bs + (size_t)(kt % STAGES) * B_STAGE + b_off;
+    const unsigned char* as = As + (size_t)(kt % STAGES) * A_STAGE + a_off + a_shift;
+    const unsigned char* bs = Bs + (size_t)(kt % STAGES) * B_STAGE + b_off + b_shift;
 #pragma unroll
     for (int k4 = 0; k4 < BK / 4; ++k4) {
       double af[4], bf[4];
