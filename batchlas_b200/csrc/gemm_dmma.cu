@@ -176,6 +176,13 @@ __global__ void __launch_bounds__(32 * WM * WN, 16 / (WM * WN)) gemm_dmma_d_kern
     }
     cp_async_commit();
   }
+  if (!HINTS && p.beta[0] != 0.0) {  // the epilogue reads this tile of C: ask L2 for its 128-byte lines now
+    constexpr int LPC = BM / 16;     // lines per stored column of the tile
+    for (int c = tid; c < BN * LPC; c += THREADS) {
+      const int col = n0 + c / LPC, r0 = m0 + 16 * (c % LPC);
+      if (col < p.n && r0 < p.m) asm volatile("prefetch.global.L2 [%0];" ::"l"(C + (long long)col * p.ldc + r0));
+    }
+  }
 
   // byte offsets of this lane's fragment element inside a stage, for k-step 0
   const int a_off = AK ? (wm * 32 + g) * A_PITCH + t * 8 : t * A_PITCH + (wm * 32 + g) * 8;

@@ -28,6 +28,12 @@
 // result is the same sum in the same order as the other DMMA kernel; only which lane holds which
 // element of C differs, and the epilogue applies the same permutations.
 //
+// Epilogue of the real kernel, chosen per call: for k <= 128 the tile is staged through the (now idle)
+// stage buffers and leaves as whole stored columns, 16 bytes per lane (C's prior values read the same
+// way, all sixteen requests of a lane in flight at once); for longer k each lane writes its
+// fragment elements directly and the C tile is asked into L2 before the main loop when beta != 0.
+// Both compute alpha * acc, then fma(beta, prior, .): the same bits.
+//
 // Preconditions (dmma_tma_supported): real double, no structure hints / per-item dims / split-K,
 // 16-byte aligned bases and even ld and batch strides for A and B (tensor-map strides are multiples
 // of 16 bytes), positive batch strides; C needs element alignment only.  No load with cluster multicast is used; the maps cover this GPU's memory.
@@ -47,6 +53,7 @@ enum WaitCode { kDmmaTmaWaitFull = 401 };
 constexpr int kBM = 64, kBN = 64, kBK = 16, kStages = 3, kThreads = 128;
 constexpr int kOperandBytes = 64 * kBK * 8;       // 8 KiB
 constexpr int kStageBytes = 2 * kOperandBytes;    // A tile + B tile
+enum EpilogueFlags { kEpiPairs = 1, kEpiStaged = 2, kEpiPrefetch = 4 };
 
 __device__ __forceinline__ void dmma(double& c0, double& c1, double a, double b) {
   asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
@@ -87,12 +94,21 @@ __device__ __forceinline__ int fragment_offset(int base, int i, int k4) {
   return (base ^ ((i & 1) << 5) ^ ((k4 & 1) << 6)) + (i >> 1) * 2048 + k4 * 512;
 }
 
+// Position swizzle of the staged C tile (see the epilogue): which 16-byte chunk positions the column
+// bits that vary inside one store request must flip, given which row bits vary there.
+template <bool AK>
+__device__ __forceinline__ int c_swizzle(int col) {
+  const int lo = ((col >> 1) ^ (col >> 2)) & 1, hi = (col >> 3) & 1;
+  return AK ? ((lo << 1) | (hi << 2)) : (lo | (hi << 1));
+}
+
 template <int OPA, int OPB>
 __global__ void __launch_bounds__(kThreads, 4)
     gemm_dmma_tma_d_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                            double* __restrict__ C, long long sc, long long ldc, int m, int n, int k, int tiles_m,
-                           int tiles_n, double alpha, double beta, int a_grouped, int b_grouped) {
+                           int tiles_n, double alpha, double beta, int a_grouped, int b_grouped, int epi) {
   constexpr bool AK = (OPA != BLB200_N);   // A stored k x m: k fastest
+  const bool c_vec = epi & kEpiPairs, staged = epi & kEpiStaged;
   constexpr bool BKM = (OPB == BLB200_N);  // B stored k x n: k fastest
   extern __shared__ unsigned char smem_raw[];
   // the swizzle is a function of the shared-memory address: tiles must start on 1024-byte boundaries
@@ -118,6 +134,15 @@ __global__ void __launch_bounds__(kThreads, 4)
   // grid drains; nothing here touches global memory before every earlier grid has finished.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  if ((epi & kEpiPrefetch) && beta != 0.0) {  // the epilogue reads this tile of C: ask L2 for it now (two threads per column, 128-byte lines)
+    const int col = n0 + (tid >> 1), r0 = m0 + 32 * (tid & 1);
+    if (col < n && r0 < m) {
+      const double* pc = C + (long long)item * sc + (long long)col * ldc + r0;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(pc));
+      if (r0 + 16 < m) asm volatile("prefetch.global.L2 [%0];" ::"l"(pc + 16));
+    }
+  }
 
   const int KT = (k + kBK - 1) / kBK;
   auto issue = [&](int s, int kt) {  // one thread: the copies of k-tile kt into stage s
@@ -193,25 +218,97 @@ __global__ void __launch_bounds__(kThreads, 4)
     return;
   }
 
-  const bool beta_zero = beta == 0.0;
-  C += (long long)item * sc;
+  if (!staged) {  // long k: the epilogue is a small part of the tile's life; write straight from the fragment layout
+    const bool bz = beta == 0.0;
+    double* Ci = C + (long long)item * sc;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int col = n0 + 32 * wn + (BKM ? perm_kmajor(2 * t + e, j) : perm_mmajor(2 * t + e, j));
+        if (col >= n) continue;
+        double* ccol = Ci + (long long)col * ldc;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int row = m0 + 32 * wm + (AK ? perm_kmajor(g, i) : perm_mmajor(g, i));
+          if (row >= m) continue;
+          double out = alpha * acc[i][j][e];
+          if (!bz) out = fma(beta, ccol[row], out);
+          ccol[row] = out;
+        }
+      }
+    return;
+  }
+  // Epilogue through shared memory: the accumulators of a lane are scattered over the tile (8-byte
+  // pieces of many columns), so the tile is first laid down column by column in the stage buffers,
+  // which no copy targets any more, and then read back so that a warp handles one whole stored column per
+  // step: 512 contiguous bytes of C, 16 per lane, for the read of the prior value and for the store.
+  // Column `col` keeps its 16-byte chunk `ch` (rows 2ch, 2ch+1) at position ch ^ c_swizzle(col): that
+  // spreads every store request of the fragment layout over all banks, and a permutation inside a
+  // column costs the read-back nothing.
+  __syncthreads();  // every warp has left the last stage; every copy was waited for above
+  double* cs = reinterpret_cast<double*>(smem);
 #pragma unroll
   for (int j = 0; j < 4; ++j)
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
-      const int cl = BKM ? perm_kmajor(2 * t + e, j) : perm_mmajor(2 * t + e, j);
-      const int col = n0 + 32 * wn + cl;
-      if (col >= n) continue;
-      double* ccol = C + (long long)col * ldc;
+      const int cl = 32 * wn + (BKM ? perm_kmajor(2 * t + e, j) : perm_mmajor(2 * t + e, j));
+      double* col_s = cs + cl * kBM;
+      const int h = c_swizzle<AK>(cl);
+      if (AK) {  // tiles 2ip and 2ip + 1 hold rows r and r + 1: one 16-byte chunk
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int row = m0 + 32 * wm + (AK ? perm_kmajor(g, i) : perm_mmajor(g, i));
-        if (row >= m) continue;
-        double out = alpha * acc[i][j][e];
-        if (!beta_zero) out = fma(beta, ccol[row], out);
-        ccol[row] = out;
+        for (int ip = 0; ip < 2; ++ip) {
+          const int ch = (32 * wm + perm_kmajor(g, 2 * ip)) >> 1;
+          *reinterpret_cast<double2*>(col_s + ((ch ^ h) << 1)) = make_double2(acc[2 * ip][j][e], acc[2 * ip + 1][j][e]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int row = 32 * wm + perm_mmajor(g, i);
+          col_s[(((row >> 1) ^ h) << 1) + (row & 1)] = acc[i][j][e];
+        }
       }
     }
+  const bool beta_zero = beta == 0.0;
+  C += (long long)item * sc;
+  const int row = m0 + 2 * lane;
+  const bool pair = c_vec && row + 1 < m;
+  // the reads of prior values go out first, sixteen independent requests, once the accumulators have left their registers, and fly across the barrier
+  double2 prior[kBN / 4];
+  if (!beta_zero) {
+#pragma unroll
+    for (int q = 0; q < kBN / 4; ++q) {
+      const int col = n0 + warp + 4 * q;
+      prior[q] = make_double2(0.0, 0.0);
+      if (col >= n || row >= m) continue;
+      const double* pc = C + (long long)col * ldc + row;
+      if (pair) {
+        prior[q] = *reinterpret_cast<const double2*>(pc);
+      } else {
+        prior[q].x = pc[0];
+        if (row + 1 < m) prior[q].y = pc[1];
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int q = 0; q < kBN / 4; ++q) {
+    const int cl = warp + 4 * q, col = n0 + cl;
+    if (col >= n || row >= m) continue;
+    const double2 v = *reinterpret_cast<const double2*>(cs + cl * kBM + ((lane ^ c_swizzle<AK>(cl)) << 1));
+    double2 out = make_double2(alpha * v.x, alpha * v.y);
+    if (!beta_zero) {
+      out.x = fma(beta, prior[q].x, out.x);
+      out.y = fma(beta, prior[q].y, out.y);
+    }
+    double* pc = C + (long long)col * ldc + row;
+    if (pair) {
+      *reinterpret_cast<double2*>(pc) = out;
+    } else {
+      pc[0] = out.x;
+      if (row + 1 < m) pc[1] = out.y;
+    }
+  }
 }
 
 // cuTensorMapEncodeTiled, resolved from the driver at run time (no link-time libcuda dependency).
@@ -333,6 +430,12 @@ int launch_op(const GemmParams& p, cudaStream_t stream) {
     rc = maps.get(&map_b, p.b, b_rows, b_cols, p.ldb, p.sb, p.batch, b_kind);
   }
   if (rc != BLB200_OK) return rc;
+  // C read and written as 16-byte pairs of rows when every column of every item starts on a 16-byte boundary
+  int epi = (reinterpret_cast<uintptr_t>(p.c) % 16 == 0 && p.ldc % 2 == 0 && p.sc % 2 == 0) ? kEpiPairs : 0;
+  // Measured (B200, beta = 1): staging wins while the epilogue is a large part of a tile's life — k = 64: 20.3
+  // against 16.5 TFLOP/s, k = 128: 29.1 against 26.9 — and loses 2 % at k = 256, where the direct
+  // epilogue with the L2 prefetch of its C tile is the faster one (k = 192: 32.6 against 31.9).
+  epi |= (p.k <= 128) ? kEpiStaged : kEpiPrefetch;
   auto kern = gemm_dmma_tma_d_kernel<OPA, OPB>;
   static thread_local int configured_for = -1;
   int cur = 0;
@@ -354,7 +457,7 @@ int launch_op(const GemmParams& p, cudaStream_t stream) {
   cfg.numAttrs = 1;
   return (int)cudaLaunchKernelEx(&cfg, kern, map_a, map_b, (double*)p.c, (long long)p.sc, (long long)p.ldc, p.m, p.n, p.k,
                                  tiles_m, tiles_n, p.alpha[0], p.beta[0], a_kind == kMapRowGroups ? 1 : 0,
-                                 b_kind == kMapRowGroups ? 1 : 0);
+                                 b_kind == kMapRowGroups ? 1 : 0, epi);
 }
 
 

@@ -146,6 +146,14 @@ __global__ void __launch_bounds__(THREADS, 2) sgemm128_kernel(GemmParams p, int 
     }
     cp_async_commit();
   }
+  if (!HINTS && p.beta[0] != 0.0) {  // the epilogue reads this tile of C: ask L2 for it now (two threads per column, 128-byte lines)
+    const int col = n0 + (tid >> 1), r0 = m0 + 64 * (tid & 1);
+    if (col < p.n && r0 < p.m) {
+      const float* pc = C + (long long)col * p.ldc + r0;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(pc));
+      if (r0 + 32 < p.m) asm volatile("prefetch.global.L2 [%0];" ::"l"(pc + 32));
+    }
+  }
 
   for (int kt = 0; kt < KT; ++kt) {
     cp_async_wait<STAGES - 2>();

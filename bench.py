@@ -860,6 +860,57 @@ def run_case(args):
     print(json.dumps(out), flush=True)
 
 
+# BatchLAS's own batched-gemm benchmark sizes: cubes with these batches (include/util/minibench.hh:869-887,
+# `CubeBatchSizes`), run by BM_GEMM with alpha = beta = 1, NN (benchmarks/gemm_benchmark.cc:8-33).
+CUBE_BATCH_SIZES = ((16, (4096, 8192, 16384)), (32, (2048, 4096, 8192)), (64, (1024, 2048, 4096)),
+                    (128, (512, 1024, 2048)), (256, (128, 256, 512, 1024)), (512, (32, 64, 128, 256)),
+                    (1024, (8, 16, 32, 64)), (2048, (2, 4, 8, 16)), (4096, (1, 2, 4, 8)))
+
+
+def run_sweep(args):
+    """The reference's cube sizes (largest batch of each), float and double, alpha = beta = 1, NN: our
+    launch and cuBLAS on the same buffers, one JSON line per point.  Where the three operands of the
+    listed batch would fit in L2, the batch is doubled until they exceed 256 MiB (`batch` against
+    `listed_batch`), so that every figure is measured from HBM."""
+    import torch
+
+    import batchlas_b200 as bl
+    torch.cuda.set_device(0)
+    cublas = Cublas(torch)
+    dtypes = args.sweep.split(",") if args.sweep != "all" else ["s", "d"]
+    for dt in dtypes:
+        es = {"s": 4, "d": 8, "c": 8, "z": 16}[dt]
+        for size, batches in CUBE_BATCH_SIZES:
+            listed = batches[-1]
+            batch = listed
+            while 3 * size * size * es * batch < (256 << 20):
+                batch *= 2
+            c = dict(dtype=dt, ops=[("N", "N")], m=size, n=size, k=size, batch=batch, alpha=1.0, beta=1.0, pad=0,
+                     dist_ab=("uniform", 1.0), dist_c=("uniform", 1.0))
+            tens, mt = alloc_config(bl, torch, c, batch, 0, torch.device("cuda", 0))
+            d = desc_for(bl, c, ("N", "N"), tens, mt, batch)
+            restore = restore_fn(bl, torch, c, tens, mt, 0)
+            ours = lambda: bl.gemm_strided_batched(d)
+            theirs = cublas.launcher(c, ("N", "N"), tens, mt, batch)
+            res = {}
+            for label, launch in (("ours", ours), ("cublas", theirs)):
+                for _ in range(args.warmup):
+                    launch()
+                torch.cuda.synchronize()
+                res[label] = time_op(torch, launch, restore, args.steps)
+            ours()
+            kern = bl.last_kernel_name()
+            worst = verify_sample(bl, torch, c, ("N", "N"), tens, mt, batch, 0, n_check=2)
+            fl = flops_per_item(c) * batch / 1e6
+            print(json.dumps({"sweep": f"{dt}{size}", "listed_batch": listed, "batch": batch, "kernel": kern,
+                              "ms": res["ours"], "gflops": fl / res["ours"], "cublas_ms": res["cublas"],
+                              "cublas_gflops": fl / res["cublas"], "vs_cublas": res["cublas"] / res["ours"],
+                              "hbm_gbs": algorithmic_bytes_per_item(c) * batch / res["ours"] / 1e6,
+                              "worst_error_ratio": worst}), flush=True)
+            del tens, d
+            torch.cuda.empty_cache()
+
+
 def run_level3(args):
     """symm / hemm / trmm / syrk / herk / syr2k / her2k (the calls BatchLAS builds on gemm) on square operands, each
     beside the plain gemm of the same shape: the difference is the cost of expanding the triangle
@@ -1024,6 +1075,7 @@ def main():
     ap.add_argument("--beta", type=float, default=-0.5, help="beta of a --case given as a shape (DTYPE MxNxK, e.g. d32x32x32:TN)")
     ap.add_argument("--kernel", default="auto", help="forced kernel for --case")
     ap.add_argument("--ld-extra", type=int, default=0, help="extra elements on every leading dimension of a --case")
+    ap.add_argument("--sweep", default="", help="the reference's cube benchmark sizes against cuBLAS: all, s or d (1 GPU)")
     ap.add_argument("--hetero", action="store_true", help="time heterogeneous batches on the reference's pattern (1 GPU)")
     ap.add_argument("--aux", action="store_true", help="time gemv and the elementwise helpers against HBM bandwidth (1 GPU)")
     ap.add_argument("--aux-gemv", default="", help="with --aux: only this gemv case, DTYPE,M,N,BATCH (e.g. s,32,32,100000)")
@@ -1041,6 +1093,9 @@ def main():
                          "cublas_gflops beside every figure already)")
     if args.case:
         run_case(args)
+        return
+    if args.sweep:
+        run_sweep(args)
         return
     if args.level3:
         run_level3(args)
