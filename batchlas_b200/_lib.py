@@ -13,9 +13,9 @@ LIB_PATH = os.path.join(_HERE, "libbatchlas_b200.so")
 
 S, D, C, Z = 0, 1, 2, 3
 OP_N, OP_T, OP_H = 0, 1, 2
-K_AUTO, K_GENERIC, K_SMALL32, K_SMALL64, K_TILED, K_DMMA, K_SGEMM128, K_SMALL_RING, K_DMMA_TMA = 0, 1, 2, 3, 4, 5, 6, 7, 8
+K_AUTO, K_GENERIC, K_SMALL32, K_SMALL64, K_TILED, K_DMMA, K_SGEMM128, K_SMALL_RING, K_DMMA_TMA, K_SGEMM_TMA = 0, 1, 2, 3, 4, 5, 6, 7, 8, 9
 KERNEL_IDS = {"auto": K_AUTO, "generic": K_GENERIC, "small32": K_SMALL32, "small64": K_SMALL64,
-              "tiled": K_TILED, "dmma": K_DMMA, "sgemm128": K_SGEMM128, "small_ring": K_SMALL_RING, "dmma_tma": K_DMMA_TMA}
+              "tiled": K_TILED, "dmma": K_DMMA, "sgemm128": K_SGEMM128, "small_ring": K_SMALL_RING, "dmma_tma": K_DMMA_TMA, "sgemm_tma": K_SGEMM_TMA}
 
 E_NULL, E_SHAPE, E_DTYPE, E_UNSUPPORTED, E_NO_DEVICE, E_TOO_LARGE, E_INTERNAL = -1, -2, -3, -4, -5, -6, -7
 

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libbatchlas_b200.so")
-SOURCES = ["dispatch.cu", "gemm_generic.cu", "gemm_small.cu", "gemm_small_ring.cu", "gemm_tiled.cu", "gemm_tiled_s.cu", "gemm_tiled_d.cu", "gemm_tiled_c.cu", "gemm_tiled_z.cu", "gemm_dmma.cu", "gemm_dmma_tma.cu", "gemm_sgemm128.cu", "gemm_splitk.cu", "level3.cu", "gemv.cu", "gemv_ring.cu", "elementwise.cu", "arena.cu", "fill.cu",
+SOURCES = ["dispatch.cu", "gemm_generic.cu", "gemm_small.cu", "gemm_small_ring.cu", "gemm_tiled.cu", "gemm_tiled_s.cu", "gemm_tiled_d.cu", "gemm_tiled_c.cu", "gemm_tiled_z.cu", "gemm_dmma.cu", "gemm_dmma_tma.cu", "gemm_sgemm128.cu", "gemm_sgemm_tma.cu", "gemm_splitk.cu", "level3.cu", "gemv.cu", "gemv_ring.cu", "elementwise.cu", "arena.cu", "fill.cu",
            "host_pipeline.cu", "status.cu", "peak.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]

@@ -218,6 +218,7 @@ int launch_tiled(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_dmma(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_sgemm128(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_dmma_tma(const GemmParams& p, int dtype, cudaStream_t stream);
+int launch_sgemm_tma(const GemmParams& p, int dtype, cudaStream_t stream);
 int launch_splitk_reduce(const GemmParams& orig, int dtype, const void* partials, int splits, long long part_ld,
                          long long part_stride, cudaStream_t stream);
 
@@ -228,6 +229,7 @@ int launch_small_ring(const GemmParams& p, int dtype, cudaStream_t stream);
 bool tiled_supported(const GemmParams& p, int dtype);
 bool dmma_supported(const GemmParams& p, int dtype);
 bool dmma_tma_supported(const GemmParams& p, int dtype);
+bool sgemm_tma_supported(const GemmParams& p, int dtype);
 bool sgemm128_supported(const GemmParams& p, int dtype);
 bool sgemm128_preferred(const GemmParams& p);  // against the tiled kernel, by padded work
 

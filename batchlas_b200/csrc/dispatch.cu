@@ -22,7 +22,7 @@ void note_launch(const char* kernel_name) {
 }
 
 // ---- environment knobs (conventions of BatchLAS include/util/env.hh) -------------------------------
-// BATCHLAS_GEMM_B200_KERNEL=<generic|small32|small64|small_ring|tiled|dmma|dmma_tma|sgemm128>  forces a kernel for calls
+// BATCHLAS_GEMM_B200_KERNEL=<generic|small32|small64|small_ring|tiled|dmma|dmma_tma|sgemm128|sgemm_tma>  forces a kernel for calls
 //   that leave kernel_hint at 0 (the role BATCHLAS_GEMM_SYCL_KERNEL plays for the reference's SYCL
 //   family, src/sycl/gemm_kernels.cc:270-329); a problem the forced kernel cannot run is dispatched
 //   normally.
@@ -37,7 +37,7 @@ static int env_forced_kernel() {
     const struct { const char* name; int id; } names[] = {
         {"generic", BLB200_K_GENERIC}, {"small32", BLB200_K_SMALL32}, {"small64", BLB200_K_SMALL64},
         {"tiled", BLB200_K_TILED},     {"dmma", BLB200_K_DMMA},       {"sgemm128", BLB200_K_SGEMM128},
-        {"small_ring", BLB200_K_SMALL_RING}, {"dmma_tma", BLB200_K_DMMA_TMA}};
+        {"small_ring", BLB200_K_SMALL_RING}, {"dmma_tma", BLB200_K_DMMA_TMA}, {"sgemm_tma", BLB200_K_SGEMM_TMA}};
     for (const auto& n : names)
       if (strcmp(v, n.name) == 0) return n.id;
     return (int)BLB200_K_AUTO;
@@ -127,7 +127,7 @@ static int validate(const blb200_gemm_desc* d) {
   if (d->ldb < (b_rows > 1 ? b_rows : 1)) return BLB200_E_SHAPE;
   if (d->ldc < (d->m > 1 ? d->m : 1)) return BLB200_E_SHAPE;
   if (d->stride_a < 0 || d->stride_b < 0 || d->stride_c < 0) return BLB200_E_SHAPE;
-  if (d->kernel_hint < BLB200_K_AUTO || d->kernel_hint > BLB200_K_DMMA_TMA) return BLB200_E_UNSUPPORTED;
+  if (d->kernel_hint < BLB200_K_AUTO || d->kernel_hint > BLB200_K_SGEMM_TMA) return BLB200_E_UNSUPPORTED;
   const bool has_work = d->m > 0 && d->n > 0 && d->batch > 0;
   if (has_work) {
     if (!d->c) return BLB200_E_NULL;
@@ -177,7 +177,12 @@ static int dispatch_untraced(const blb200_gemm_desc* d, const StructureHints* hi
 static int launch_tile_kernel(const GemmParams& p, int dtype, cudaStream_t stream, bool generic_fallback = true) {
   if (dmma_tma_supported(p, dtype)) return launch_dmma_tma(p, dtype, stream);
   if (dmma_supported(p, dtype)) return launch_dmma(p, dtype, stream);
-  if (sgemm128_supported(p, dtype) && sgemm128_preferred(p)) return launch_sgemm128(p, dtype, stream);
+  if (sgemm128_supported(p, dtype) && sgemm128_preferred(p)) {
+    // the same 128 x 128 tile in two forms: from k = 256 on the TMA-fed one is the faster (256^3: 51.0
+    // against 47.4 TFLOP/s, 1024^3: 56.6 against 51.6), below that its deeper ring does not fill (128^3: 37.9 against 42.7)
+    if (p.k >= 256 && sgemm_tma_supported(p, dtype)) return launch_sgemm_tma(p, dtype, stream);
+    return launch_sgemm128(p, dtype, stream);
+  }
   if (tiled_supported(p, dtype)) return launch_tiled(p, dtype, stream);
   return generic_fallback ? launch_generic(p, dtype, stream) : BLB200_E_UNSUPPORTED;
 }
@@ -253,6 +258,7 @@ static int dispatch_untraced(const blb200_gemm_desc* d, const StructureHints* hi
       case BLB200_K_SGEMM128: if (sgemm128_supported(p, dt)) return launch_sgemm128(p, dt, stream); break;
       case BLB200_K_SMALL_RING: if (small_ring_supported(p, dt)) return launch_small_ring(p, dt, stream); break;
       case BLB200_K_DMMA_TMA: if (dmma_tma_supported(p, dt)) return launch_dmma_tma(p, dt, stream); break;
+      case BLB200_K_SGEMM_TMA: if (sgemm_tma_supported(p, dt)) return launch_sgemm_tma(p, dt, stream); break;
       default: break;
     }
   }
@@ -265,6 +271,7 @@ static int dispatch_untraced(const blb200_gemm_desc* d, const StructureHints* hi
     case BLB200_K_SGEMM128: return launch_sgemm128(p, d->dtype, stream);
     case BLB200_K_SMALL_RING: return launch_small_ring(p, d->dtype, stream);
     case BLB200_K_DMMA_TMA: return launch_dmma_tma(p, d->dtype, stream);
+    case BLB200_K_SGEMM_TMA: return launch_sgemm_tma(p, d->dtype, stream);
     default: break;
   }
   if (small32_supported(p, d->dtype)) return launch_small32(p, d->dtype, stream);

@@ -9,6 +9,8 @@ int gemv_ring_device_status(int* out);
 int small_ring_device_status(int* out);
 int dmma_tma_device_status(int* out);
 int dmma_tma_device_status_clear();
+int sgemm_tma_device_status(int* out);
+int sgemm_tma_device_status_clear();
 int small_device_status_clear();
 int gemv_ring_device_status_clear();
 int small_ring_device_status_clear();
@@ -55,6 +57,10 @@ extern "C" int blb200_device_status(int* out) {
     if (rc != 0) return rc;
   }
   if (word == 0) {
+    rc = blb200::sgemm_tma_device_status(&word);
+    if (rc != 0) return rc;
+  }
+  if (word == 0) {
     rc = blb200::read_device_status_word(&word);
     if (rc != 0) return rc;
   }
@@ -69,6 +75,7 @@ extern "C" int blb200_device_status_reset(void) {
   if (rc == 0) rc = blb200::gemv_ring_device_status_clear();
   if (rc == 0) rc = blb200::small_ring_device_status_clear();
   if (rc == 0) rc = blb200::dmma_tma_device_status_clear();
+  if (rc == 0) rc = blb200::sgemm_tma_device_status_clear();
   if (rc == 0) rc = blb200::clear_device_status_word();
   return rc;
 }

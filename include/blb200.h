@@ -53,7 +53,8 @@ enum {
   BLB200_K_DMMA = 5,    /* FP64 tensor-core (mma.sync m8n8k4) tiles, double and complex<double> */
   BLB200_K_SGEMM128 = 6, /* float, A not transposed: 128x128x32 tiles, 8x8 blocks, packed FP32 FMA */
   BLB200_K_SMALL_RING = 7, /* any dtype, packed items up to 32x32 (k <= 64): whole items per warp, TMA ring */
-  BLB200_K_DMMA_TMA = 8 /* double: the DMMA tiles fed by tensor-map TMA copies (128-byte swizzle) instead of cp.async */
+  BLB200_K_DMMA_TMA = 8, /* double: the DMMA tiles fed by tensor-map TMA copies (128-byte swizzle) instead of cp.async */
+  BLB200_K_SGEMM_TMA = 9 /* float, A not transposed, long k: 128x128x32 tiles fed by tensor-map TMA copies, 16x8 blocks, no CTA barrier */
 };
 /* Split-K has no kernel id: it needs scratch, which only its own entry points below receive. */
 

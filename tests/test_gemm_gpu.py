@@ -207,6 +207,45 @@ def test_tma_fed_dmma_tiles(bl, oa, ob):
     assert bl.device_status() == 0
 
 
+@pytest.mark.parametrize("ob", ["N", "T"])
+def test_tma_fed_sgemm_tiles(bl, ob):
+    """The tensor-map fed float tile kernel (128 x 128 x 32 stages, 16 x 8 blocks, the last warp out of a
+    stage refills it) on full, ragged and tiny shapes, k that is and is not a multiple of the stage depth and
+    shorter than the ring, padded leading dimensions (multiples of 4 floats) with canaries, stride gaps,
+    several items, beta == 0 over NaN and beta != 0; and it must agree with the cp.async kernel of the
+    same tile bit for bit (same products in the same order)."""
+    shapes = [(256, 256, 256, 3, 2.0, 0.5, 8), (200, 136, 70, 3, 2.0, -1.0, 4), (128, 128, 32, 5, 1.0, 0.0, 0),
+              (64, 64, 1, 2, 1.0, 1.0, 4), (68, 196, 33, 2, -1.5, 0.0, 0), (132, 64, 97, 2, 1.0, 0.5, 0),
+              (1024, 96, 200, 1, 1.0, 1.0, 0), (260, 300, 129, 2, 1.0, 0.0, 12), (128, 128, 1024, 1, 1.0, 0.0, 0)]
+    r4 = lambda x: (x + 3) // 4 * 4  # tensor-map strides are multiples of 16 bytes
+    for (m, n, k, batch, alpha, beta, pad) in shapes:
+        br = k if ob == "N" else n
+        p = oracle.make_problem("s", "N", ob, m, n, k, batch, lda=r4(m) + pad, ldb=r4(br) + pad, ldc=r4(m) + pad,
+                                alpha=alpha, beta=beta)
+        p.stride_a += 4
+        p.stride_b += 8
+        p.stride_c += 12
+        A, B, C0 = make_inputs(p)
+        if beta == 0.0:
+            idx = (np.arange(p.batch)[:, None, None] * p.stride_c + np.arange(n)[None, :, None] * p.ldc
+                   + np.arange(m)[None, None, :]).ravel()
+            C0[idx] = np.nan
+        C, kern = run_device(bl, p, A, B, C0, kernel="sgemm_tma")
+        assert kern == "sgemm_tma"
+        C0chk = np.where(np.isnan(C0), 0.0, C0) if beta == 0.0 else C0
+        bad, worst = oracle.check(p, A, B, C0chk, C)
+        assert bad == 0, f"sgemm_tma N{ob} {m}x{n}x{k}: worst ratio {worst:.3g}"
+        assert oracle.untouched_outside_window(p, C0, C)
+        C2, kern2 = run_device(bl, p, A, B, C0, kernel="sgemm128")
+        assert kern2 == "sgemm128" and np.array_equal(C, C2, equal_nan=True)
+    # operands that are only float-aligned are not its business
+    p = oracle.make_problem("s", "N", ob, 128, 128, 64, 2, lda=129, alpha=1.0, beta=0.0)
+    A, B, C0 = make_inputs(p)
+    with pytest.raises(Exception):
+        run_device(bl, p, A, B, C0, kernel="sgemm_tma")
+    assert bl.device_status() == 0
+
+
 @pytest.mark.parametrize("oa", ["N", "T", "C"])
 @pytest.mark.parametrize("ob", ["N", "T", "C"])
 def test_tma_fed_dmma_tiles_complex(bl, oa, ob):
@@ -309,7 +348,12 @@ def test_large_float_tiles_with_packed_fma(bl):
             C, kern = run_device(bl, p, A, B, C0)
             # every shape goes to whichever tile wastes less; an ld that is not a multiple of 4 floats
             # (33, 257, 70 here) only switches the tile kernel's load policy
-            assert kern in ("sgemm128", "tiled"), kern
+            # (and from k = 256 on, 16-byte aligned operands take the TMA-fed form of the 128 x 128 tile)
+            assert kern in ("sgemm128", "sgemm_tma", "tiled"), kern
+            if (m, n, k) == (256, 256, 256):
+                assert kern == "sgemm_tma", kern
+            if k < 256:
+                assert kern != "sgemm_tma", (kern, m, n, k)
             assert_parity(p, A, B, C0, C, what=f"{kern} N{ob} {m}x{n}x{k}")
             C, kern = run_device(bl, p, A, B, C0, kernel="sgemm128")
             assert kern == "sgemm128"
