@@ -222,36 +222,57 @@ __global__ void __launch_bounds__(THREADS, 2)
     return;
   }
 
+  // Epilogue: column by column of the lane's eight, the prior values of the next column requested
+  // before the current one is stored (C's loads and stores may alias as far as the compiler knows, so
+  // left to itself it would finish each column's round trip to L2 before starting the next).
   const bool beta_zero = beta == 0.f;
+  auto col_of = [&](int c) { return n0 + wn * 32 + (B_KMAJOR ? (tj + 4 * c) : (8 * tj + c)); };
+  auto load_prior = [&](int c, float4 (&dst)[RG]) {
+    const int col = col_of(c);
+#pragma unroll
+    for (int g = 0; g < RG; ++g) {
+      dst[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+      const int row = m0 + 32 * g + 4 * ti;
+      if (col >= n || row >= m) continue;
+      const float* pc = C + (long long)col * ldc + row;
+      if (row + 4 <= m) {
+        dst[g] = *reinterpret_cast<const float4*>(pc);
+      } else {
+        dst[g].x = pc[0];
+        if (row + 1 < m) dst[g].y = pc[1];
+        if (row + 2 < m) dst[g].z = pc[2];
+      }
+    }
+  };
+  float4 prior[2][RG];
+  if (!beta_zero) load_prior(0, prior[0]);
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
-    const int col = n0 + wn * 32 + (B_KMAJOR ? (tj + 4 * c) : (8 * tj + c));
+    if (!beta_zero && c + 1 < 8) load_prior(c + 1, prior[(c + 1) & 1]);
+    const int col = col_of(c);
     if (col >= n) continue;
     float* ccol = C + (long long)col * ldc;
 #pragma unroll
     for (int g = 0; g < RG; ++g) {
       const int row = m0 + 32 * g + 4 * ti;
+      if (row >= m) continue;
       float o[4];
       unpack2(accp[(2 * g) * 8 + c], o[0], o[1]);
       unpack2(accp[(2 * g + 1) * 8 + c], o[2], o[3]);
+      float4 out = make_float4(alpha * o[0], alpha * o[1], alpha * o[2], alpha * o[3]);
+      if (!beta_zero) {
+        const float4 pr = prior[c & 1][g];
+        out.x = fmaf(beta, pr.x, out.x);
+        out.y = fmaf(beta, pr.y, out.y);
+        out.z = fmaf(beta, pr.z, out.z);
+        out.w = fmaf(beta, pr.w, out.w);
+      }
       if (row + 4 <= m) {
-        float4 out = make_float4(alpha * o[0], alpha * o[1], alpha * o[2], alpha * o[3]);
-        if (!beta_zero) {
-          const float4 pr = *reinterpret_cast<const float4*>(ccol + row);
-          out.x = fmaf(beta, pr.x, out.x);
-          out.y = fmaf(beta, pr.y, out.y);
-          out.z = fmaf(beta, pr.z, out.z);
-          out.w = fmaf(beta, pr.w, out.w);
-        }
         *reinterpret_cast<float4*>(ccol + row) = out;
       } else {
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-          if (row + e < m) {
-            float out = alpha * o[e];
-            if (!beta_zero) out = fmaf(beta, ccol[row + e], out);
-            ccol[row + e] = out;
-          }
+        ccol[row] = out.x;
+        if (row + 1 < m) ccol[row + 1] = out.y;
+        if (row + 2 < m) ccol[row + 2] = out.z;
       }
     }
   }
