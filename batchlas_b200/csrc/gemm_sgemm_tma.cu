@@ -1,4 +1,4 @@
-// Large float GEMM with A not transposed (op pairs NN and NT), fed by TMA: the long-k form of the
+// Large float GEMM for op pairs NN, NT and TT, fed by TMA: the long-k form of the
 // 128 x 128 x 32 float tile.  Four warps per CTA, each owning all 128 rows and 32 columns of the tile
 // with a 16 x 8 register block per lane (64 packed FP32 FMAs, fma.rn.f32x2, per 8 duplicated B values
 // and 6 fragment reads of 16 bytes — half the non-FMA instructions per FMA of the 8 x 8 block), two
@@ -20,8 +20,12 @@
 //                      8tj .. 8tj + 7.
 // The products and their order per output element are those of the cp.async kernel of the same tile
 // (k ascending, one FMA per k): the same bits.
+// Op pair TT runs as the NN problem of the transposed product (C^T = B_stored A_stored: B as stored has
+// n fastest, A as stored k fastest), and the epilogue transposes the tile through shared memory into
+// whole stored columns of C.  TN is not taken: neither operand has an output dimension fastest, so no
+// operand comes in the row pairs the packed FMA wants.
 //
-// Preconditions (sgemm_tma_supported): float, op(A) = N, plain gemm (no structure hints, per-item dims
+// Preconditions (sgemm_tma_supported): float, op pair NN, NT or TT, plain gemm (no structure hints, per-item dims
 // or split-K), A, B and C 16-byte aligned (base, ld and batch stride), positive batch strides.  No
 // load with cluster multicast is used; the maps cover this GPU's memory only.  Every wait is bounded;
 // a wait that runs out records code 501, and the CTA leaves as a unit after giving the copies it
@@ -66,7 +70,9 @@ __device__ __forceinline__ uint32_t smem_add_acq_rel(uint32_t* p, uint32_t v) {
   return old;
 }
 
-template <bool B_KMAJOR>
+// OUT_T: the kernel computes the transpose of the caller's C (see the file comment on op pair TT): its rows
+// are the caller's columns, and the epilogue transposes the tile through shared memory.
+template <bool B_KMAJOR, bool OUT_T = false>
 __global__ void __launch_bounds__(THREADS, 2)
     sgemm_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      float* __restrict__ C, long long sc, long long ldc, int m, int n, int k, int tiles_m, int tiles_n,
@@ -104,13 +110,13 @@ __global__ void __launch_bounds__(THREADS, 2)
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
   C += (long long)item * sc;
-  if (beta != 0.f) {  // the epilogue reads this tile of C: ask L2 for its 128-byte lines now (one thread per column)
-    const int col = n0 + tid;
-    if (col < n) {
-      const float* pc = C + (long long)col * ldc + m0;
+  if (beta != 0.f) {  // the epilogue reads this tile of C: ask L2 for its 128-byte lines now (one thread per stored column)
+    const int col = (OUT_T ? m0 : n0) + tid, first_row = OUT_T ? n0 : m0;
+    if (col < (OUT_T ? m : n)) {
+      const float* pc = C + (long long)col * ldc + first_row;
 #pragma unroll
       for (int l = 0; l < BM / 32; ++l)
-        if (m0 + 32 * l < m) asm volatile("prefetch.global.L2 [%0];" ::"l"(pc + 32 * l));
+        if (first_row + 32 * l < (OUT_T ? n : m)) asm volatile("prefetch.global.L2 [%0];" ::"l"(pc + 32 * l));
     }
   }
 
@@ -222,10 +228,73 @@ __global__ void __launch_bounds__(THREADS, 2)
     return;
   }
 
+  const bool beta_zero = beta == 0.f;
+  if constexpr (OUT_T) {
+    // The tile in hand is the transpose of the caller's: lay it down in the stage buffers (idle now; every
+    // copy was waited for by every warp) as [kernel row r][kernel column c], which is one stored column
+    // of the caller's C per r, and write those out whole: 512 contiguous bytes per warp step, 16 per
+    // lane, eight rows' prior values requested before the first of them is stored.
+    constexpr int PITCH = BN + 4;  // floats; keeps every row 16-byte aligned
+    float* S = reinterpret_cast<float*>(smem);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int cl = wn * 32 + tj + 4 * c;
+#pragma unroll
+      for (int g = 0; g < RG; ++g) {
+        float o[4];
+        unpack2(accp[(2 * g) * 8 + c], o[0], o[1]);
+        unpack2(accp[(2 * g + 1) * 8 + c], o[2], o[3]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) S[(32 * g + 4 * ti + e) * PITCH + cl] = o[e];
+      }
+    }
+    __syncthreads();
+    const int urow = n0 + 4 * lane;  // caller's row = kernel column
+#pragma unroll 1
+    for (int rb = 0; rb < 32; rb += 8) {
+      float4 pr[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        pr[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int ucol = m0 + wn * 32 + rb + q;  // caller's column = kernel row
+        if (beta_zero || ucol >= m || urow >= n) continue;
+        const float* pc = C + (long long)ucol * ldc + urow;
+        if (urow + 4 <= n) {
+          pr[q] = *reinterpret_cast<const float4*>(pc);
+        } else {
+          pr[q].x = pc[0];
+          if (urow + 1 < n) pr[q].y = pc[1];
+          if (urow + 2 < n) pr[q].z = pc[2];
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const int r = wn * 32 + rb + q, ucol = m0 + r;
+        if (ucol >= m || urow >= n) continue;
+        const float4 v = *reinterpret_cast<const float4*>(S + r * PITCH + 4 * lane);
+        float4 out = make_float4(alpha * v.x, alpha * v.y, alpha * v.z, alpha * v.w);
+        if (!beta_zero) {
+          out.x = fmaf(beta, pr[q].x, out.x);
+          out.y = fmaf(beta, pr[q].y, out.y);
+          out.z = fmaf(beta, pr[q].z, out.z);
+          out.w = fmaf(beta, pr[q].w, out.w);
+        }
+        float* pc = C + (long long)ucol * ldc + urow;
+        if (urow + 4 <= n) {
+          *reinterpret_cast<float4*>(pc) = out;
+        } else {
+          pc[0] = out.x;
+          if (urow + 1 < n) pc[1] = out.y;
+          if (urow + 2 < n) pc[2] = out.z;
+        }
+      }
+    }
+    return;
+  }
+
   // Epilogue: column by column of the lane's eight, the prior values of the next column requested
   // before the current one is stored (C's loads and stores may alias as far as the compiler knows, so
   // left to itself it would finish each column's round trip to L2 before starting the next).
-  const bool beta_zero = beta == 0.f;
   auto col_of = [&](int c) { return n0 + wn * 32 + (B_KMAJOR ? (tj + 4 * c) : (8 * tj + c)); };
   auto load_prior = [&](int c, float4 (&dst)[RG]) {
     const int col = col_of(c);
@@ -347,8 +416,17 @@ struct FloatMapCache {
   }
 };
 
-template <bool B_KMAJOR>
-int launch_op(const GemmParams& p, cudaStream_t stream) {
+// OUT_T (op pair TT): C^T = op(B)^T op(A)^T = B_stored A_stored, which is the NN problem on swapped
+// operands — B as stored (n x k, n fastest) is the M-major operand, A as stored (k x m, k fastest) the
+// K-major one — with the kernel's m and n being the caller's n and m.
+template <bool B_KMAJOR, bool OUT_T = false>
+int launch_op(const GemmParams& q, cudaStream_t stream) {
+  GemmParams p = q;
+  if (OUT_T) {
+    p.a = q.b; p.lda = q.ldb; p.sa = q.sb;
+    p.b = q.a; p.ldb = q.lda; p.sb = q.sa;
+    p.m = q.n; p.n = q.m;
+  }
   constexpr size_t smem = (size_t)STAGES * STAGE + 1024 + 128;
   const int tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BN - 1) / BN;
   const long long total = (long long)tiles_m * tiles_n * p.batch;
@@ -360,7 +438,7 @@ int launch_op(const GemmParams& p, cudaStream_t stream) {
   rc = B_KMAJOR ? maps.get(&map_b, p.b, p.k, p.n, p.ldb, p.sb, p.batch, true)
                 : maps.get(&map_b, p.b, p.n, p.k, p.ldb, p.sb, p.batch, false);
   if (rc != BLB200_OK) return rc;
-  auto kern = sgemm_tma_kernel<B_KMAJOR>;
+  auto kern = sgemm_tma_kernel<B_KMAJOR, OUT_T>;
   static thread_local int configured_for = -1;
   int cur = 0;
   cudaGetDevice(&cur);
@@ -386,7 +464,8 @@ int launch_op(const GemmParams& p, cudaStream_t stream) {
 }  // namespace
 
 bool sgemm_tma_supported(const GemmParams& p, int dtype) {
-  if (dtype != BLB200_S || p.op_a != BLB200_N) return false;
+  if (dtype != BLB200_S) return false;
+  if (p.op_a != BLB200_N && p.op_b == BLB200_N) return false;  // TN: neither operand has an output dimension fastest
   if (has_hints(p) || p.splits > 1) return false;
   if (p.m < 64 || p.n < 64 || p.k < 1) return false;
   if (p.batch > 1 && (p.sa <= 0 || p.sb <= 0)) return false;  // a broadcast operand has no item stride to map
@@ -396,7 +475,8 @@ bool sgemm_tma_supported(const GemmParams& p, int dtype) {
 
 int launch_sgemm_tma(const GemmParams& p, int dtype, cudaStream_t stream) {
   if (!sgemm_tma_supported(p, dtype)) return BLB200_E_UNSUPPORTED;
-  const int rc = (p.op_b == BLB200_N) ? launch_op<true>(p, stream) : launch_op<false>(p, stream);
+  const int rc = (p.op_a != BLB200_N) ? launch_op<true, true>(p, stream)
+                                      : (p.op_b == BLB200_N) ? launch_op<true>(p, stream) : launch_op<false>(p, stream);
   if (rc == BLB200_OK) note_launch("sgemm_tma");
   return rc;
 }
