@@ -183,9 +183,9 @@ static int launch_tile_kernel(const GemmParams& p, int dtype, cudaStream_t strea
     if (p.k >= 256 && sgemm_tma_supported(p, dtype)) return launch_sgemm_tma(p, dtype, stream);
     return launch_sgemm128(p, dtype, stream);
   }
-  // float A^T B^T with long k: the transposed product on the TMA-fed 128 x 128 tile (1024^3: 57.1 against 39.9 TFLOP/s on the 64 x 64 tiles; 256^3: 52.1 against 38.4)
-  if (dtype == BLB200_S && p.op_a != BLB200_N && p.op_b != BLB200_N && p.k >= 256 && sgemm128_preferred(p) &&
-      sgemm_tma_supported(p, dtype))
+  // float with A transposed and long k, on the TMA-fed 128 x 128 tile: A^T B^T as the transposed product (1024^3:
+  // 57.1 against 39.9 TFLOP/s on the 64 x 64 tiles; 256^3: 52.1 against 38.4), A^T B by k-pairs (1024^3: 48.3 against 39.8)
+  if (dtype == BLB200_S && p.op_a != BLB200_N && p.k >= 256 && sgemm128_preferred(p) && sgemm_tma_supported(p, dtype))
     return launch_sgemm_tma(p, dtype, stream);
   if (tiled_supported(p, dtype)) return launch_tiled(p, dtype, stream);
   return generic_fallback ? launch_generic(p, dtype, stream) : BLB200_E_UNSUPPORTED;

@@ -1,4 +1,4 @@
-// Large float GEMM for op pairs NN, NT and TT, fed by TMA: the long-k form of the
+// Large float GEMM for all four op pairs, fed by TMA (A^T B has a kernel of its own further down): the long-k form of the
 // 128 x 128 x 32 float tile.  Four warps per CTA, each owning all 128 rows and 32 columns of the tile
 // with a 16 x 8 register block per lane (64 packed FP32 FMAs, fma.rn.f32x2, per 8 duplicated B values
 // and 6 fragment reads of 16 bytes — half the non-FMA instructions per FMA of the 8 x 8 block), two
@@ -22,10 +22,10 @@
 // (k ascending, one FMA per k): the same bits.
 // Op pair TT runs as the NN problem of the transposed product (C^T = B_stored A_stored: B as stored has
 // n fastest, A as stored k fastest), and the epilogue transposes the tile through shared memory into
-// whole stored columns of C.  TN is not taken: neither operand has an output dimension fastest, so no
-// operand comes in the row pairs the packed FMA wants.
+// whole stored columns of C.  For TN neither operand has an output dimension fastest, so no operand
+// comes in the row pairs the packed FMA wants: sgemm_tma_tn_kernel pairs along k instead.
 //
-// Preconditions (sgemm_tma_supported): float, op pair NN, NT or TT, plain gemm (no structure hints, per-item dims
+// Preconditions (sgemm_tma_supported): float, plain gemm (no structure hints, per-item dims
 // or split-K), A, B and C 16-byte aligned (base, ld and batch stride), positive batch strides.  No
 // load with cluster multicast is used; the maps cover this GPU's memory only.  Every wait is bounded;
 // a wait that runs out records code 501, and the CTA leaves as a unit after giving the copies it
@@ -347,6 +347,167 @@ __global__ void __launch_bounds__(THREADS, 2)
   }
 }
 
+// ---- A^T B: both operands have k fastest ------------------------------------------------------------
+// Neither operand offers pairs along an output dimension, but both offer pairs along k: a 64-bit
+// register (a[i][k], a[i][k+1]) times (b[k][j], b[k+1][j]) accumulates the even-k and the odd-k partial
+// sum of c[i][j] side by side, with nothing to duplicate; the two halves are added once, in the
+// epilogue.  (So the sum is ordered as even k ascending plus odd k ascending, not k ascending: within
+// the parity bound, not bit-identical to the other float kernels.)  An 8 x 8 block per lane is 128
+// accumulator registers; per four k a lane reads eight 16-byte fragments of each operand for 128
+// packed FMAs.  CTA 128 x 128 x 32 with 8 warps as 2 (m) x 4 (n), one CTA per SM, four stages.
+//   A  [128 m][32 k], B [128 n][32 k]: one box 32 x 128 each with the 128-byte swizzle (16-byte chunk
+//      index XOR (row & 7)).  A lane owns rows ti + 8i of its warp's 64 — the eight lanes of a
+//      quarter-warp differ in (row & 7), so a fragment request covers all banks once — and columns
+//      tj + 4j of its warp's 32 (one address per quarter-warp).
+constexpr int TN_THREADS = 256, TN_WARPS = TN_THREADS / 32, TN_STAGES = 4;
+
+__global__ void __launch_bounds__(TN_THREADS, 1)
+    sgemm_tma_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                        float* __restrict__ C, long long sc, long long ldc, int m, int n, int k, int tiles_m, int tiles_n,
+                        float alpha, float beta) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)TN_STAGES * STAGE);
+  uint32_t* left = reinterpret_cast<uint32_t*>(full_bar + TN_STAGES);
+  int* issued_kt = reinterpret_cast<int*>(left + TN_STAGES);
+  int* dead = issued_kt + TN_STAGES;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wm = warp & 1, wn = warp >> 1;
+  const int ti = lane & 7, tj = lane >> 3;
+
+  const long long tiles_per_item = (long long)tiles_m * tiles_n;
+  const long long tile = blockIdx.x;
+  const int item = (int)(tile / tiles_per_item);
+  const int rem = (int)(tile - (long long)item * tiles_per_item);
+  const int m0 = (rem % tiles_m) * BM, n0 = (rem / tiles_m) * BN;
+
+  if (tid == 0) {
+    for (int s = 0; s < TN_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      left[s] = 0;
+      issued_kt[s] = -1;
+    }
+    *dead = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  C += (long long)item * sc;
+  if (beta != 0.f && tid < BN) {  // the epilogue reads this tile of C: ask L2 for its 128-byte lines now
+    const int col = n0 + tid;
+    if (col < n) {
+      const float* pc = C + (long long)col * ldc + m0;
+#pragma unroll
+      for (int l = 0; l < BM / 32; ++l)
+        if (m0 + 32 * l < m) asm volatile("prefetch.global.L2 [%0];" ::"l"(pc + 32 * l));
+    }
+  }
+
+  const int KT = (k + BK - 1) / BK;
+  auto issue = [&](int s, int kt) {
+    unsigned char* st = smem + (size_t)s * STAGE;
+    issued_kt[s] = kt;
+    mbar_arrive_expect_tx(&full_bar[s], STAGE);
+    tma_load_3d(st, &map_a, kt * BK, m0, item, &full_bar[s]);
+    tma_load_3d(st + A_STAGE, &map_b, kt * BK, n0, item, &full_bar[s]);
+  };
+  if (tid == 0)
+    for (int s = 0; s < TN_STAGES && s < KT; ++s) issue(s, s);
+
+  uint64_t acc[8][8];  // [row i][col j]: (even-k sum, odd-k sum) of element (ti + 8i, tj + 4j) of the warp tile
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0ull;
+
+  const int a_row0 = wm * 64 + ti, b_col0 = wn * 32 + tj;
+  bool lost = false;
+  for (int kt = 0; kt < KT; ++kt) {
+    const int s = kt % TN_STAGES;
+    const bool ok = mbar_wait(&full_bar[s], (uint32_t)(kt / TN_STAGES) & 1u, kSgemmTmaWaitFull);
+    if (!__all_sync(0xffffffffu, ok)) {
+      lost = true;
+      break;
+    }
+    const ulonglong2* As2 = reinterpret_cast<const ulonglong2*>(smem + (size_t)s * STAGE);
+    const ulonglong2* Bs2 = reinterpret_cast<const ulonglong2*>(smem + (size_t)s * STAGE + A_STAGE);
+#pragma unroll
+    for (int kc = 0; kc < BK / 4; ++kc) {
+      ulonglong2 af[8], bf[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int r = a_row0 + 8 * i;
+        af[i] = As2[r * 8 + (kc ^ (r & 7))];
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int c = b_col0 + 4 * j;
+        bf[j] = Bs2[c * 8 + (kc ^ (c & 7))];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ffma2(acc[i][j], af[i].x, bf[j].x);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ffma2(acc[i][j], af[i].y, bf[j].y);
+    }
+    __syncwarp();
+    if (lane == 0) {
+      const uint32_t before = smem_add_acq_rel(&left[s], 1u);
+      if ((before & (TN_WARPS - 1)) == TN_WARPS - 1 && kt + TN_STAGES < KT) {
+        fence_async_smem();
+        issue(s, kt + TN_STAGES);
+      }
+    }
+  }
+  if (lost && lane == 0) atomicExch(dead, 1);
+  __syncthreads();
+  if (*reinterpret_cast<volatile int*>(dead)) {
+    if (tid == 0)
+      for (int s = 0; s < TN_STAGES; ++s) {
+        const int q = issued_kt[s];
+        if (q >= 0) mbar_wait_limit(&full_bar[s], (uint32_t)(q / TN_STAGES) & 1u, kSgemmTmaWaitFull, 1u << 12);
+      }
+    return;
+  }
+
+  // Epilogue: a quarter-warp holds 8 consecutive rows of a column (one 32-byte sector); the prior values
+  // of the next column are requested before the current one is stored.
+  const bool beta_zero = beta == 0.f;
+  auto load_prior = [&](int j, float (&dst)[8]) {
+    const int col = n0 + b_col0 + 4 * j;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int row = m0 + a_row0 + 8 * i;
+      dst[i] = (col < n && row < m) ? C[(long long)col * ldc + row] : 0.f;
+    }
+  };
+  float prior[2][8];
+  if (!beta_zero) load_prior(0, prior[0]);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (!beta_zero && j + 1 < 8) load_prior(j + 1, prior[(j + 1) & 1]);
+    const int col = n0 + b_col0 + 4 * j;
+    if (col >= n) continue;
+    float* ccol = C + (long long)col * ldc;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int row = m0 + a_row0 + 8 * i;
+      if (row >= m) continue;
+      float even, odd;
+      unpack2(acc[i][j], even, odd);
+      float out = alpha * (even + odd);
+      if (!beta_zero) out = fmaf(beta, prior[j & 1][i], out);
+      ccol[row] = out;
+    }
+  }
+}
+
 // cuTensorMapEncodeTiled, resolved from the driver at run time (no link-time libcuda dependency).
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -461,11 +622,44 @@ int launch_op(const GemmParams& q, cudaStream_t stream) {
                                  tiles_m, tiles_n, (float)p.alpha[0], (float)p.beta[0]);
 }
 
+int launch_tn(const GemmParams& p, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)TN_STAGES * STAGE + 1024 + 128;
+  const int tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BN - 1) / BN;
+  const long long total = (long long)tiles_m * tiles_n * p.batch;
+  if (total > 0x7fffffffLL) return BLB200_E_UNSUPPORTED;
+  alignas(64) CUtensorMap map_a, map_b;
+  static thread_local FloatMapCache maps;
+  int rc = maps.get(&map_a, p.a, p.k, p.m, p.lda, p.sa, p.batch, true);
+  if (rc != BLB200_OK) return rc;
+  rc = maps.get(&map_b, p.b, p.k, p.n, p.ldb, p.sb, p.batch, true);
+  if (rc != BLB200_OK) return rc;
+  auto kern = sgemm_tma_tn_kernel;
+  static thread_local int configured_for = -1;
+  int cur = 0;
+  cudaGetDevice(&cur);
+  if (configured_for != cur) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured_for = cur;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)total);
+  cfg.blockDim = dim3(TN_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, kern, map_a, map_b, (float*)p.c, (long long)p.sc, (long long)p.ldc, p.m, p.n, p.k,
+                                 tiles_m, tiles_n, (float)p.alpha[0], (float)p.beta[0]);
+}
+
 }  // namespace
 
 bool sgemm_tma_supported(const GemmParams& p, int dtype) {
   if (dtype != BLB200_S) return false;
-  if (p.op_a != BLB200_N && p.op_b == BLB200_N) return false;  // TN: neither operand has an output dimension fastest
   if (has_hints(p) || p.splits > 1) return false;
   if (p.m < 64 || p.n < 64 || p.k < 1) return false;
   if (p.batch > 1 && (p.sa <= 0 || p.sb <= 0)) return false;  // a broadcast operand has no item stride to map
@@ -475,7 +669,7 @@ bool sgemm_tma_supported(const GemmParams& p, int dtype) {
 
 int launch_sgemm_tma(const GemmParams& p, int dtype, cudaStream_t stream) {
   if (!sgemm_tma_supported(p, dtype)) return BLB200_E_UNSUPPORTED;
-  const int rc = (p.op_a != BLB200_N) ? launch_op<true, true>(p, stream)
+  const int rc = (p.op_a != BLB200_N) ? (p.op_b == BLB200_N ? launch_tn(p, stream) : launch_op<true, true>(p, stream))
                                       : (p.op_b == BLB200_N) ? launch_op<true>(p, stream) : launch_op<false>(p, stream);
   if (rc == BLB200_OK) note_launch("sgemm_tma");
   return rc;

@@ -265,10 +265,34 @@ def test_tma_fed_sgemm_tiles(bl, ob):
         C, kern = run_device(bl, p, A, B, C0)
         assert kern == "sgemm_tma", kern
         assert_parity(p, A, B, C0, C, what="dispatched TT 256x128x512")
-        p = oracle.make_problem("s", "T", "N", 256, 128, 512, 2, alpha=1.0, beta=0.0)  # TN is not taken
+    if ob == "N":
+        # A^T B: (even-k, odd-k) partial sums from k-pairs of both operands, four stages, eight warps; odd k,
+        # k shorter than the ring, ragged in both dimensions, beta on and off, several items
+        for (m, n, k, batch, alpha, beta, pad) in [(256, 256, 256, 2, 2.0, 0.5, 8), (200, 136, 70, 3, 2.0, -1.0, 4),
+                                                   (64, 68, 1, 2, 1.0, 1.0, 0), (132, 260, 97, 2, -1.5, 0.0, 4),
+                                                   (1024, 96, 203, 1, 1.0, 1.0, 0), (68, 516, 129, 2, 1.0, 0.0, 0),
+                                                   (128, 128, 1024, 1, 1.0, 0.0, 0)]:
+            p = oracle.make_problem("s", "T", "N", m, n, k, batch, lda=r4(k) + pad, ldb=r4(k) + pad, ldc=r4(m) + pad,
+                                    alpha=alpha, beta=beta)
+            p.stride_a += 4
+            p.stride_b += 8
+            p.stride_c += 12
+            A, B, C0 = make_inputs(p)
+            if beta == 0.0:
+                idx = (np.arange(p.batch)[:, None, None] * p.stride_c + np.arange(n)[None, :, None] * p.ldc
+                       + np.arange(m)[None, None, :]).ravel()
+                C0[idx] = np.nan
+            C, kern = run_device(bl, p, A, B, C0, kernel="sgemm_tma")
+            assert kern == "sgemm_tma"
+            C0chk = np.where(np.isnan(C0), 0.0, C0) if beta == 0.0 else C0
+            bad, worst = oracle.check(p, A, B, C0chk, C)
+            assert bad == 0, f"sgemm_tma TN {m}x{n}x{k}: worst ratio {worst:.3g}"
+            assert oracle.untouched_outside_window(p, C0, C)
+        p = oracle.make_problem("s", "T", "N", 256, 128, 512, 2, alpha=1.0, beta=0.0)
         A, B, C0 = make_inputs(p)
-        with pytest.raises(Exception):
-            run_device(bl, p, A, B, C0, kernel="sgemm_tma")
+        C, kern = run_device(bl, p, A, B, C0)
+        assert kern == "sgemm_tma", kern
+        assert_parity(p, A, B, C0, C, what="dispatched TN 256x128x512")
     # operands that are only float-aligned are not its business
     p = oracle.make_problem("s", "N", ob, 128, 128, 64, 2, lda=129, alpha=1.0, beta=0.0)
     A, B, C0 = make_inputs(p)
