@@ -37,13 +37,12 @@
 // Preconditions (dmma_tma_supported): real double, no structure hints / per-item dims / split-K,
 // 16-byte aligned bases and even ld and batch strides for A and B (tensor-map strides are multiples
 // of 16 bytes), positive batch strides; C needs element alignment only.  No load with cluster multicast is used; the maps cover this GPU's memory.
-#include <cuda.h>
 #include <string.h>
 
 #include <atomic>
 
 #include "common.cuh"
-#include "ptx.cuh"
+#include "tensor_map.cuh"
 
 namespace blb200 {
 namespace {
@@ -59,19 +58,6 @@ __device__ __forceinline__ void dmma(double& c0, double& c1, double a, double b)
   asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
                : "+d"(c0), "+d"(c1)
                : "d"(a), "d"(b));
-}
-
-__device__ __forceinline__ void tma_load_4d(void* dst_smem, const CUtensorMap* map, int x, int y, int z, int w, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::
-          "r"(smem_u32(dst_smem)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar))
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(void* dst_smem, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
-          "r"(smem_u32(dst_smem)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
-      : "memory");
 }
 
 // Row of the warp's 32 owned by lane group g in tile i (see the file comment).
@@ -309,22 +295,6 @@ __global__ void __launch_bounds__(kThreads, 4)
       if (row + 1 < m) pc[1] = out.y;
     }
   }
-}
-
-// cuTensorMapEncodeTiled, resolved from the driver at run time (no link-time libcuda dependency).
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return (EncodeTiledFn)p;
-  }();
-  return fn;
 }
 
 enum MapKind { kMapKMajor = 0, kMapRows16 = 1, kMapRowGroups = 2 };

@@ -25,18 +25,6 @@
 namespace blb200 {
 namespace {
 
-__device__ __forceinline__ void ffma2(uint64_t& d, uint64_t a, uint64_t b) {
-  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
-}
-__device__ __forceinline__ uint64_t dup2(float f) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(f));
-  return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-
 constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3, THREADS = 256;
 constexpr int A_STAGE = BK * BM * 4, B_STAGE = BK * BN * 4;  // 16 KiB each
 

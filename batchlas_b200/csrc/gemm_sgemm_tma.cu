@@ -30,11 +30,10 @@
 // load with cluster multicast is used; the maps cover this GPU's memory only.  Every wait is bounded;
 // a wait that runs out records code 501, and the CTA leaves as a unit after giving the copies it
 // still has in flight a bounded chance to land.
-#include <cuda.h>
 #include <string.h>
 
 #include "common.cuh"
-#include "ptx.cuh"
+#include "tensor_map.cuh"
 
 namespace blb200 {
 namespace {
@@ -44,31 +43,6 @@ enum WaitCode { kSgemmTmaWaitFull = 501 };
 constexpr int BM = 128, BN = 128, BK = 32, STAGES = 3, THREADS = 128, WARPS = THREADS / 32;
 constexpr int A_STAGE = BK * BM * 4, B_STAGE = BK * BN * 4, STAGE = A_STAGE + B_STAGE;  // 16 + 16 KiB
 constexpr int RG = 4;  // groups of 4 rows per lane
-
-__device__ __forceinline__ void ffma2(uint64_t& d, uint64_t a, uint64_t b) {
-  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
-}
-__device__ __forceinline__ uint64_t dup2(float f) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(f));
-  return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ void tma_load_3d(void* dst_smem, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
-          "r"(smem_u32(dst_smem)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
-      : "memory");
-}
-// Release-acquire counter bump in shared memory: the warp that reads WARPS - 1 (mod WARPS) knows
-// that every other warp of the CTA has finished reading the stage as well.
-__device__ __forceinline__ uint32_t smem_add_acq_rel(uint32_t* p, uint32_t v) {
-  uint32_t old;
-  asm volatile("atom.acq_rel.cta.shared.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(smem_u32(p)), "r"(v) : "memory");
-  return old;
-}
 
 // OUT_T: the kernel computes the transpose of the caller's C (see the file comment on op pair TT): its rows
 // are the caller's columns, and the epilogue transposes the tile through shared memory.
@@ -506,22 +480,6 @@ __global__ void __launch_bounds__(TN_THREADS, 1)
       ccol[row] = out;
     }
   }
-}
-
-// cuTensorMapEncodeTiled, resolved from the driver at run time (no link-time libcuda dependency).
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return (EncodeTiledFn)p;
-  }();
-  return fn;
 }
 
 // 3-D map (rows, cols, items) over a column-major float operand, zero fill past the bounds.

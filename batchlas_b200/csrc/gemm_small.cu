@@ -39,7 +39,7 @@
 #include <string.h>
 
 #include "common.cuh"
-#include "ptx.cuh"
+#include "tensor_map.cuh"
 
 namespace blb200 {
 namespace {
@@ -260,21 +260,6 @@ constexpr int kHalfBytes64 = 32 * 64 * 4;             // one operand, half of K:
 constexpr int kSlotBytes64 = 2 * kHalfBytes64;        // A half + B half
 constexpr int kMatElems64 = 64 * 64;
 
-// Packed FP32 FMA (Blackwell FFMA2): d.lo += a.lo*b.lo, d.hi += a.hi*b.hi, each an IEEE fused
-// multiply-add.  One instruction issues two FMAs, which matters because the 8 x 8 register block is
-// issue-bound with scalar FFMA (64 FMAs + 16 fragment floats + addressing per k per lane).
-__device__ __forceinline__ void ffma2(uint64_t& d, uint64_t a, uint64_t b) {
-  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
-}
-__device__ __forceinline__ uint64_t dup2(float f) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(f));
-  return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-
 // How the 64 accumulators of a lane are paired for FFMA2.  Pairs must be adjacent in the operand
 // that shared memory delivers as float4 along the output dimension:
 //   kRowPairs  A M-major: a float4 holds 4 consecutive rows  -> acc pairs (row 2p, 2p+1), B value duplicated
@@ -393,30 +378,9 @@ __device__ __forceinline__ void mma64_half(const unsigned char* __restrict__ As,
   }
 }
 
-// tiled TMA load of one (32 k) x (64 rows) x (1 item) box; x0 = first k (0 or 32), z = batch item.
-__device__ __forceinline__ void tma_load_3d(void* dst_smem, const CUtensorMap* map, int x0, int y0, int z,
-                                            uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
-          "r"(smem_u32(dst_smem)), "l"(map), "r"(x0), "r"(y0), "r"(z), "r"(smem_u32(bar))
-      : "memory");
-}
-
-// L2 prefetch hints: an untiled run, and one (32 k) x (64 rows) x (1 item) box of a tensor map.
+// L2 prefetch hint for an untiled run (tensor_map.cuh has the one for a box of a tensor map).
 __device__ __forceinline__ void bulk_prefetch_l2(const void* src_gmem, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_gmem), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* map, int x0, int y0, int z) {
-  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(map), "r"(x0), "r"(y0), "r"(z)
-               : "memory");
-}
-
-// Release-acquire counter bump in shared memory: whoever reads an odd old value knows that the
-// other warp of its pair has finished reading the slot as well.
-__device__ __forceinline__ uint32_t smem_add_acq_rel(uint32_t* p, uint32_t v) {
-  uint32_t old;
-  asm volatile("atom.acq_rel.cta.shared.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(smem_u32(p)), "r"(v) : "memory");
-  return old;
 }
 
 // Pair p's q-th half-item lives in slot p * SPP + q % SPP (round q / SPP; SPP = slots per pair);
@@ -575,22 +539,6 @@ __global__ void __launch_bounds__(64 * PAIRS, 1)
       }
     }
   }
-}
-
-// cuTensorMapEncodeTiled, resolved from the driver at run time (no link-time libcuda dependency).
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return (EncodeTiledFn)p;
-  }();
-  return fn;
 }
 
 // 3-D map over `batch` K-major 64 x 64 float matrices: dims (k, row, item), box 32 x 64 x 1,
