@@ -180,13 +180,18 @@ static int launch_tile_kernel(const GemmParams& p, int dtype, cudaStream_t strea
   if (sgemm128_supported(p, dtype) && sgemm128_preferred(p)) {
     // the same 128 x 128 tile in two forms: from k = 256 on the TMA-fed one is the faster (256^3: 51.0
     // against 47.4 TFLOP/s, 1024^3: 56.6 against 51.6), below that its deeper ring does not fill (128^3: 37.9 against 42.7)
-    if (p.k >= 256 && sgemm_tma_supported(p, dtype)) return launch_sgemm_tma(p, dtype, stream);
+    if (p.k >= 256 && sgemm_tma_supported(p, dtype)) {
+      const int rc = launch_sgemm_tma(p, dtype, stream);
+      if (rc != BLB200_E_INTERNAL) return rc;  // a driver that refuses the tensor map: the cp.async form takes it
+    }
     return launch_sgemm128(p, dtype, stream);
   }
   // float with A transposed and long k, on the TMA-fed 128 x 128 tile: A^T B^T as the transposed product (1024^3:
   // 57.1 against 39.9 TFLOP/s on the 64 x 64 tiles; 256^3: 52.1 against 38.4), A^T B by k-pairs (1024^3: 48.3 against 39.8)
-  if (dtype == BLB200_S && p.op_a != BLB200_N && p.k >= 256 && sgemm128_preferred(p) && sgemm_tma_supported(p, dtype))
-    return launch_sgemm_tma(p, dtype, stream);
+  if (dtype == BLB200_S && p.op_a != BLB200_N && p.k >= 256 && sgemm128_preferred(p) && sgemm_tma_supported(p, dtype)) {
+    const int rc = launch_sgemm_tma(p, dtype, stream);
+    if (rc != BLB200_E_INTERNAL) return rc;
+  }
   if (tiled_supported(p, dtype)) return launch_tiled(p, dtype, stream);
   return generic_fallback ? launch_generic(p, dtype, stream) : BLB200_E_UNSUPPORTED;
 }
