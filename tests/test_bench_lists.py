@@ -8,7 +8,10 @@ import pytest
 
 import bench
 
-REF = "/root/reference/include/util/minibench.hh"
+# the reference checkout, when there is one: BATCHLAS_SOURCE_DIR, else a `reference` folder beside this repository
+_ROOT = os.environ.get("BATCHLAS_SOURCE_DIR") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
+REF = os.path.join(_ROOT, "include", "util", "minibench.hh")
 
 
 def test_cube_list_is_well_formed():
